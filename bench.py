@@ -1,0 +1,399 @@
+#!/usr/bin/env python
+"""Benchmark of the MXFP / minifloat fake-quantisation hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Headline (one JSON line on stdout, printed by rank 0): minifloat quantize_dequantize, E5M2,
+fp32 [8192, 8192] per GPU with the value distribution of benchmark configuration 2 (seeded
+synthetic data), reported as algorithmic GB/s (8 bytes per element) summed over all GPUs.
+One "step" is one pass of the fused kernel over the whole tensor.  Input (256 MiB) plus output
+(256 MiB) exceed the 126 MB L2, so every step streams from HBM.
+
+Extra keys: `roofline` (achieved GB/s of the kernel against the measured HBM copy peak), `e2e`
+(same metric through the host-buffer pipeline, copies inside the timed region), `cpu_baseline`
+(the C oracle on the host cores), `clocks`, `gpu_launches`, and `extras` with the other
+configurations (MXFP extract / compose at configurations 1 and 3).
+
+`--impl reference` times the CPU restatement of the reference's path (the oracle) with all host
+threads on the same configuration.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "minifloat_quantize_dequantize_GBps"
+UNIT = "GB/s"
+SHAPE = (8192, 8192)
+BYTES_PER_ELT = 8                      # fp32 in + fp32 out
+WORKLOAD = "cfg2: minifloat quantize_dequantize E5M2 (rn, is_finite) fp32 [8192,8192] per GPU"
+
+
+def measured_peaks() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock / throttle reasons of one GPU with NVML while a region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.02):
+        self.index, self.period = index, period_s
+        self.samples: list[tuple[float, int, int]] = []
+        self.sm_max = None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.sm_max = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h) if hasattr(nv, "nvmlDeviceGetCurrentClocksEventReasons") \
+                    else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.samples.append((time.perf_counter(), mhz, reasons))
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def start(self):
+        if self.nv is not None:
+            self._thr = threading.Thread(target=self._loop, daemon=True)
+            self._thr.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thr is not None:
+            self._thr.join(timeout=2)
+
+    def summary(self, t0: float, t1: float) -> dict:
+        if self.nv is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable"]}
+        inside = [s for s in self.samples if t0 <= s[0] <= t1] or self.samples[-3:]
+        names = {0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+                 0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+                 0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting"}
+        bits = 0
+        for s in inside:
+            bits |= s[2]
+        reasons = [n for b, n in names.items() if bits & b and n != "gpu_idle"]
+        return {"sm_mhz": statistics.median(s[1] for s in inside) if inside else None, "sm_max_mhz": self.sm_max,
+                "reasons": reasons, "samples": len(inside)}
+
+
+def dist_setup(n_gpus: int):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        return dist, rank, world, local
+    return None, 0, 1, 0
+
+
+def cpu_baseline(sample_rows: int = 8192, reps: int = 3) -> dict:
+    """The C oracle (all host threads) on the same workload; median of `reps` passes."""
+    import oracle
+    from mase_triton_b200 import synthetic
+    from types import SimpleNamespace
+    meta = SimpleNamespace(exp_bits=5, frac_bits=2, is_finite=True, round_mode="rn")
+    x = synthetic.cfg2_minifloat_fp32(rows=slice(0, sample_rows))
+    oracle.quantize_dequantize_minifloat(x[:64], meta)
+    ts = []
+    for _ in range(reps):
+        t = time.perf_counter()
+        oracle.quantize_dequantize_minifloat(x, meta)
+        ts.append(time.perf_counter() - t)
+    t = statistics.median(ts)
+    return {"value": round(x.numel() * BYTES_PER_ELT / t / 1e9, 3), "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
+            "sample": f"{sample_rows}x{x.shape[1]} fp32 rows of the workload, median of {reps} passes of the C oracle ({t * 1e3:.1f} ms each)"}
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    from mase_triton_b200 import synthetic
+    from types import SimpleNamespace
+    meta = SimpleNamespace(exp_bits=5, frac_bits=2, is_finite=True, round_mode="rn")
+    x = synthetic.cfg2_minifloat_fp32()
+    for _ in range(max(1, args.warmup)):
+        oracle.quantize_dequantize_minifloat(x[:1024], meta)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.quantize_dequantize_minifloat(x, meta)
+    dt = (time.perf_counter() - t0) / args.steps
+    v = round(x.numel() * BYTES_PER_ELT / dt / 1e9, 3)
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "note": "CPU restatement of the reference's PyTorch path (C oracle, OpenMP); one tensor, host cores only"},
+            "cpu_baseline": {"value": v, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
+                             "sample": "each step is one full [8192,8192] pass"},
+            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def time_steps(fn, steps: int, stream=None) -> list[float]:
+    """Per-step device times in ms, CUDA events on the launching stream."""
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    ev[0].record()
+    for i in range(steps):
+        fn()
+        ev[i + 1].record()
+    torch.cuda.synchronize()
+    return [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
+
+
+def extras_single_gpu(dev, steps: int, warmup: int, peak: float) -> dict:
+    """MXFP extract / compose on configurations 1 and 3 (device-resident, CUDA-event timed)."""
+    from mase_triton_b200 import synthetic
+    from mase_triton_b200.mxfp import kernels as mxk
+    from mase_triton_b200.mxfp.meta import MXFP8_E4M3_fn, OCP_MXFP4_E2M1
+    out = {}
+    for name, gen, meta, s_in, nsets in (("cfg1_mxfp8_fp32_4096x4096", synthetic.cfg1_mxfp8_fp32, MXFP8_E4M3_fn, 4, 4),
+                                         ("cfg3_mxfp4_bf16_16384x8192", synthetic.cfg3_mxfp4_bf16, OCP_MXFP4_E2M1, 2, 1)):
+        x = gen().to(dev).flatten()
+        xs = [x] + [x.clone() for _ in range(nsets - 1)]      # rotate buffers so small tensors cannot sit in L2
+        n = x.numel()
+        i = [0]
+
+        def ext():
+            i[0] += 1
+            return mxk.extract_mxfp_components(xs[i[0] % nsets], meta)
+        for _ in range(warmup):
+            ext()
+        t_ext = statistics.median(time_steps(ext, steps))
+        se = [mxk.extract_mxfp_components(v, meta) for v in xs]
+
+        def comp():
+            i[0] += 1
+            s, e = se[i[0] % nsets]
+            return mxk.compose_mxfp_tensor(s, e, meta, x.dtype)
+        for _ in range(warmup):
+            comp()
+        t_cmp = statistics.median(time_steps(comp, steps))
+
+        def qdq():
+            i[0] += 1
+            return mxk.quantize_dequantize(xs[i[0] % nsets], meta, x.dtype)
+        for _ in range(warmup):
+            qdq()
+        t_qdq = statistics.median(time_steps(qdq, steps))
+        b_ext = n * (s_in + 1 + 1 / 32)
+        b_cmp = n * (1 + 1 / 32 + s_in)
+        out[name] = {
+            "extract_GBps": round(b_ext / t_ext / 1e6, 1), "extract_frac_of_peak": round(b_ext / t_ext / 1e6 / peak, 3),
+            "compose_GBps": round(b_cmp / t_cmp / 1e6, 1), "compose_frac_of_peak": round(b_cmp / t_cmp / 1e6 / peak, 3),
+            "extract_plus_compose_GBps": round((b_ext + b_cmp) / (t_ext + t_cmp) / 1e6, 1),
+            "fused_qdq_GBps": round(n * 2 * s_in / t_qdq / 1e6, 1),
+            "ms": {"extract": round(t_ext, 4), "compose": round(t_cmp, 4), "fused_qdq": round(t_qdq, 4)},
+            "buffer_sets_rotated": nsets,
+        }
+        del xs, se, x
+        torch.cuda.empty_cache()
+    return out
+
+
+def small_cases():
+    """Small single-kernel cases for profiling: name -> (builder returning (launch_fn, algorithmic bytes)).
+    Inputs plus outputs are larger than L2 and well under 1 GB."""
+    from mase_triton_b200 import synthetic
+    from mase_triton_b200.minifloat import kernels as mfk
+    from mase_triton_b200.minifloat.meta import FP8_E5M2_fn
+    from mase_triton_b200.mxfp import kernels as mxk
+    from mase_triton_b200.mxfp.meta import MXFP8_E4M3_fn, OCP_MXFP4_E2M1
+    dev = torch.device("cuda", 0)
+
+    def minifloat_qdq_f32():
+        x = synthetic.cfg2_minifloat_fp32(shape=(4096, 8192)).to(dev)
+        out = torch.empty_like(x)
+        return (lambda: mfk.quantize_dequantize(x, FP8_E5M2_fn, torch.float32, out=out)), x.numel() * 8
+
+    def mx_case(gen, shape, meta, s_in, which):
+        x = gen(shape=shape).to(dev).flatten()
+        n = x.numel()
+        if which == "extract":
+            return (lambda: mxk.extract_mxfp_components(x, meta)), n * (s_in + 1 + 1 / 32)
+        if which == "compose":
+            s, e = mxk.extract_mxfp_components(x, meta)
+            return (lambda: mxk.compose_mxfp_tensor(s, e, meta, x.dtype)), n * (s_in + 1 + 1 / 32)
+        out = torch.empty_like(x)
+        return (lambda: mxk.quantize_dequantize(x, meta, x.dtype, out=out)), n * 2 * s_in
+
+    cases = {"minifloat_qdq_f32": minifloat_qdq_f32}
+    for which in ("extract", "compose", "qdq"):
+        cases[f"mxfp8_{which}_f32"] = (lambda w=which: mx_case(synthetic.cfg1_mxfp8_fp32, (8192, 8192), MXFP8_E4M3_fn, 4, w))
+        cases[f"mxfp4_{which}_bf16"] = (lambda w=which: mx_case(synthetic.cfg3_mxfp4_bf16, (8192, 8192), OCP_MXFP4_E2M1, 2, w))
+    return cases
+
+
+def run_case(name: str, steps: int, warmup: int) -> None:
+    cases = small_cases()
+    if name not in cases:
+        raise SystemExit(f"unknown case {name}; choose from {sorted(cases)}")
+    fn, nbytes = cases[name]()
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = time_steps(fn, steps)
+    t = statistics.median(ts)
+    peak, kind = measured_peaks()
+    print(json.dumps({"case": name, "steps": steps, "median_ms": round(t, 5), "GBps": round(nbytes / t / 1e6, 1),
+                      "frac_of_peak": round(nbytes / t / 1e6 / peak, 4), "peak": peak, "peak_source": kind}), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the configuration 1 / 3 side measurements")
+    ap.add_argument("--case", default=None, help="run one small single-kernel case (for profiling) and exit")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.case is not None:
+        run_case(args.case, args.steps, args.warmup)
+        return
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    dist, rank, world, local = dist_setup(args.gpus)
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+
+    from mase_triton_b200 import _lib, synthetic
+    from mase_triton_b200.hostpath import HostPipeline
+    from mase_triton_b200.minifloat import kernels as mfk
+    from mase_triton_b200.minifloat.meta import FP8_E5M2_fn
+    _lib.load()
+    peak, peak_kind = measured_peaks()
+
+    x_host = synthetic.cfg2_minifloat_fp32().pin_memory()
+    n = x_host.numel()
+    x = x_host.to(dev, non_blocking=True)
+    out = torch.empty_like(x)
+    torch.cuda.synchronize()
+
+    def step():
+        mfk.quantize_dequantize(x, FP8_E5M2_fn, torch.float32, out=out)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier(device_ids=[local])
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    t0 = time.perf_counter()
+    per_step = time_steps(step, args.steps)
+    barrier()
+    t1 = time.perf_counter()
+    total_ms = sum(per_step)
+    if dist is not None:
+        t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    value = world * n * BYTES_PER_ELT / (ms_per_step * 1e-3) / 1e9
+    kern_ms = statistics.mean(per_step)
+    achieved = n * BYTES_PER_ELT / (kern_ms * 1e-3) / 1e9
+
+    # end to end: pinned host input -> device -> kernel -> pinned host output, every step
+    out_host = torch.empty_like(x_host).pin_memory()
+    pipe = HostPipeline(lambda a, b: mfk.quantize_dequantize(a, FP8_E5M2_fn, torch.float32, out=b), dev, chunk_rows=512)
+    e2e_steps = max(3, min(args.steps, 10))
+    pipe.run(x_host, out_host)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches_before = pipe.launches
+    e0.record()
+    for _ in range(e2e_steps):
+        pipe.run(x_host, out_host)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    e2e_launches = pipe.launches - launches_before
+    if dist is not None:
+        t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = world * n * BYTES_PER_ELT / (e2e_ms / e2e_steps * 1e-3) / 1e9
+    sampler.stop()
+    clocks = sampler.summary(t0, t1)
+    # the e2e result must equal the device-resident one
+    e2e_ok = bool(torch.equal(out_host.view(torch.int32), out.cpu().view(torch.int32)))
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "l2": "inputs larger than L2 (256 MiB in + 256 MiB out per step)",
+                       "bytes_per_element": BYTES_PER_ELT, "elements_per_gpu": n, "parallelism": f"rows x{world} (independent shards, no collective)"},
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(achieved / peak, 4), "traffic": None, "peak_source": f"{peak_kind} HBM copy bandwidth",
+                         "kernel": "ew_vec_kernel<4,4,4,4,QdqOp<f32,f32,E5M2>>", "launch_ms": round(kern_ms, 5)},
+            "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": n * 4, "d2h_bytes_per_step": n * 4,
+                    "steps": e2e_steps, "ms_per_step": round(e2e_ms / e2e_steps, 3), "matches_device_result": e2e_ok,
+                    "path": "HostPipeline: pinned host -> 512-row chunks over 3 streams -> pinned host"},
+            "gpu_launches": args.steps, "e2e_gpu_launches": e2e_launches,
+            "clocks": clocks,
+        }
+        if world == 1:
+            try:
+                line["cpu_baseline"] = cpu_baseline()
+            except Exception as exc:      # the baseline must never hide the GPU result
+                line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": None, "kind": "port", "sample": f"failed: {exc}"}
+        if world == 1 and not args.no_extras:
+            del x, out
+            torch.cuda.empty_cache()
+            try:
+                line["extras"] = extras_single_gpu(dev, max(5, min(args.steps, 50)), args.warmup, peak)
+            except Exception as exc:
+                line["extras"] = {"error": str(exc)}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier(device_ids=[local])
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

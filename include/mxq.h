@@ -1,0 +1,105 @@
+/*
+ * libmxq — C ABI of the B200 (sm_100a) MXFP / minifloat fake-quantisation library.
+ *
+ * mase-triton is pure Python: it has no FFI of its own.  The functions below are
+ * the seam its Python host code would bind in place of its Triton kernel hosts
+ * (module mase_triton.{minifloat,mxfp}.kernels); each declaration cites the
+ * reference function it replaces.  Every pointer is a DEVICE pointer on the
+ * current CUDA device; `stream` is a cudaStream_t passed as void*.  The library
+ * never allocates or frees device memory and never synchronises: the caller
+ * owns every buffer and keeps it alive until the stream work has run.
+ *
+ * All functions return MXQ_OK (0) or a negative MXQ_E* code; none throws or traps.
+ */
+#ifndef MXQ_H_
+#define MXQ_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element dtypes of floating-point tensors */
+#define MXQ_F32 0
+#define MXQ_BF16 1
+#define MXQ_F16 2
+
+/* rounding modes of MinifloatMeta.round_mode / MXFPMeta.round_mode */
+#define MXQ_RN 0 /* "rn": half to even */
+#define MXQ_RU 1 /* "ru": away from zero on the magnitude */
+#define MXQ_RD 2 /* "rd": truncate the 15-bit mantissa */
+#define MXQ_RZ 3 /* "rz": truncate the 23-bit mantissa */
+
+#define MXQ_OK 0
+#define MXQ_EINVAL -1   /* bad argument (null pointer, bad dtype, bad format, n % block_size != 0) */
+#define MXQ_ELAUNCH -2  /* the CUDA launch failed; see mxq_last_cuda_error() */
+#define MXQ_ESIZE -3    /* problem size outside what the entry point supports */
+
+/* Library version (major * 1000 + minor). */
+int mxq_version(void);
+/* Text for an MXQ_* status. */
+const char* mxq_status_string(int status);
+/* cudaGetErrorString of the last failed launch made through this library on this thread. */
+const char* mxq_last_cuda_error(void);
+
+/*
+ * Minifloat extract: floating tensor -> one uint16 code per element.
+ * Replaces minifloat.kernels.extract_minifloat_component
+ * (src/mase_triton/minifloat/kernels/cast.py:148-170); results follow the
+ * reference's PyTorch path (src/mase_triton/minifloat/fake.py:7-78) bit for bit.
+ * bf16/fp16 inputs are widened exactly inside the kernel (the reference casts to
+ * fp32 first, minifloat/functional/cast.py:27).
+ */
+int mxq_minifloat_extract(const void* x, int x_dtype, uint16_t* codes, int64_t n,
+                          int exp_bits, int frac_bits, int is_finite, int round_mode, void* stream);
+
+/*
+ * Minifloat compose: uint16 codes -> floating tensor of out_dtype.
+ * Replaces minifloat.kernels.compose_minifloat_component
+ * (src/mase_triton/minifloat/kernels/cast.py:263-288); follows fake.py:81-125.
+ */
+int mxq_minifloat_compose(const uint16_t* codes, void* out, int out_dtype, int64_t n,
+                          int exp_bits, int frac_bits, int is_finite, void* stream);
+
+/*
+ * Fused minifloat quantize_dequantize (extract + compose without the uint16
+ * intermediate). Replaces the two launches behind
+ * minifloat.functional.quantize_dequantize (src/mase_triton/minifloat/functional/cast.py:72-90).
+ */
+int mxq_minifloat_qdq(const void* x, int x_dtype, void* out, int out_dtype, int64_t n,
+                      int exp_bits, int frac_bits, int is_finite, int round_mode, void* stream);
+
+/*
+ * MXFP extract: flat floating tensor of n elements (n % block_size == 0) ->
+ * scales[n / block_size] (E8M0 bytes) and elements[n] (one code per byte).
+ * Replaces mxfp.kernels.extract_mxfp_components including its _find_block_max
+ * pre-pass (src/mase_triton/mxfp/kernels/cast.py:15-21,126-160); follows
+ * src/mase_triton/mxfp/fake.py:11-59.
+ */
+int mxq_mxfp_extract(const void* x, int x_dtype, uint8_t* scales, uint8_t* elements, int64_t n,
+                     int block_size, int exp_bits, int frac_bits, int is_finite, int round_mode,
+                     void* stream);
+
+/*
+ * MXFP compose: (scales, elements) -> flat floating tensor of out_dtype.
+ * Replaces mxfp.kernels.compose_mxfp_tensor (src/mase_triton/mxfp/kernels/cast.py:237-272);
+ * follows src/mase_triton/mxfp/fake.py:62-79.
+ */
+int mxq_mxfp_compose(const uint8_t* scales, const uint8_t* elements, void* out, int out_dtype,
+                     int64_t n, int block_size, int exp_bits, int frac_bits, int is_finite,
+                     void* stream);
+
+/*
+ * Fused MXFP quantize_dequantize (one pass, no scales/elements written).
+ * Replaces the extract + compose pair behind mxfp.functional.quantize_dequantize
+ * (src/mase_triton/mxfp/functional/cast.py:103-129) for a flat tensor.
+ */
+int mxq_mxfp_qdq(const void* x, int x_dtype, void* out, int out_dtype, int64_t n,
+                 int block_size, int exp_bits, int frac_bits, int is_finite, int round_mode,
+                 void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MXQ_H_ */

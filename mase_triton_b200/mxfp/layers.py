@@ -1,0 +1,120 @@
+"""``MXFPLinearPTQ`` (reference: ``src/mase_triton/mxfp/layers.py:11-211``).
+
+A post-training-quantised linear layer.  With ``Wq`` the weight lives as uint8 Parameters
+``w_scales`` ``[out*in/B, 1]`` and ``w_elements`` ``[out*in/B, B]`` (blocks along ``in_features``) plus
+the plain attribute ``w_tensor_meta``; with ``Bq`` the bias likewise (blocks along dim 0).
+Parameter names, constructor arguments and class methods match the reference.
+"""
+
+from __future__ import annotations
+
+from typing import Literal
+
+import torch
+from torch import Tensor, nn
+
+from .._ptq_base import PTQLinearBase
+from . import functional as MXFP_F
+from .meta import MXFPMeta, MXFPTensorMeta
+
+LayerType = Literal["XWB", "XWBq", "XWqB", "XWqBq", "XqWB", "XqWBq", "XqWqB", "XqWqBq"]
+
+
+def _all_given(*items) -> bool:
+    return all(i is not None for i in items)
+
+
+class MXFPLinearPTQ(PTQLinearBase):
+    _code_tensors = ("w_scales", "w_elements", "b_scales", "b_elements")
+    _meta_follows = {"w_tensor_meta": "w_scales", "b_tensor_meta": "b_scales"}
+
+    def __init__(
+        self,
+        weight: Tensor,
+        bias: Tensor | None,
+        x_mxfp_meta: MXFPMeta | None,
+        w_mxfp_meta: MXFPMeta | None,
+        b_mxfp_meta: MXFPMeta | None,
+        layer_type: LayerType,
+        backend: Literal["separate", "fused"] = "fused",
+        dtype: torch.dtype | None = None,
+        device: torch.device | None = None,
+        w_scales: Tensor | None = None,
+        w_elements: Tensor | None = None,
+        w_tensor_meta: MXFPTensorMeta | None = None,
+        b_scales: Tensor | None = None,
+        b_elements: Tensor | None = None,
+        b_tensor_meta: MXFPTensorMeta | None = None,
+    ):
+        super().__init__()
+        assert weight is None or weight.ndim == 2
+        assert bias is None or bias.ndim == 1
+        assert (weight is not None) ^ _all_given(w_scales, w_elements, w_tensor_meta)
+        if bias is not None and _all_given(b_scales, b_elements, b_tensor_meta):
+            raise ValueError("Either bias or b_scales, b_elements, b_tensor_meta must be None, not both.")
+        out_features, in_features = w_tensor_meta.shape if weight is None else weight.shape
+        assert bias is None or bias.shape[0] == out_features
+
+        self.in_features, self.out_features = in_features, out_features
+        self.x_mxfp_meta, self.w_mxfp_meta, self.b_mxfp_meta = x_mxfp_meta, w_mxfp_meta, b_mxfp_meta
+        self.layer_type = layer_type
+        self.backend = backend
+        self.dtype, self.device = dtype, device
+
+        self.weight = self.w_scales = self.w_elements = self.w_tensor_meta = None
+        self.bias = self.b_scales = self.b_elements = self.b_tensor_meta = None
+
+        if "Wq" in layer_type:
+            if w_scales is None:
+                w_scales, w_elements, w_tensor_meta = MXFP_F.extract_mxfp_components(weight, block_dim=1, mxfp_meta=w_mxfp_meta)
+            self.w_scales, self.w_elements = self._frozen(w_scales), self._frozen(w_elements)
+            self.w_tensor_meta = w_tensor_meta
+        else:
+            assert weight is not None
+            self.weight = self._frozen(weight.to(dtype=dtype, device=device))
+
+        if "Bq" in layer_type:
+            if bias is not None and b_scales is None:
+                b_scales, b_elements, b_tensor_meta = MXFP_F.extract_mxfp_components(bias, block_dim=0, mxfp_meta=b_mxfp_meta)
+            if b_scales is not None:
+                self.b_scales, self.b_elements = self._frozen(b_scales), self._frozen(b_elements)
+                self.b_tensor_meta = b_tensor_meta
+        elif bias is not None:
+            self.bias = self._frozen(bias.to(dtype=dtype, device=device))
+
+    @torch.no_grad()
+    def forward(self, input: Tensor) -> Tensor:
+        return MXFP_F.mxfp_linear(
+            x=input, x_meta=self.x_mxfp_meta,
+            w=self.weight, w_scales=self.w_scales, w_elements=self.w_elements, w_tensor_meta=self.w_tensor_meta,
+            b=self.bias, b_scales=self.b_scales, b_elements=self.b_elements, b_tensor_meta=self.b_tensor_meta,
+            layer_type=self.layer_type, backend=self.backend,
+        )
+
+    def extra_repr(self) -> str:
+        return (f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, "
+                f"layer_type={self.layer_type}, w_mxfp_meta={self.w_mxfp_meta}, x_mxfp_meta={self.x_mxfp_meta}, "
+                f"b_mxfp_meta={self.b_mxfp_meta}")
+
+    @classmethod
+    def from_linear(cls, layer: nn.Linear, x_mxfp_meta: MXFPMeta | None, w_mxfp_meta: MXFPMeta | None,
+                    b_mxfp_meta: MXFPMeta | None, layer_type: LayerType, backend: Literal["separate", "fused"]):
+        """Quantise an existing ``nn.Linear`` (its tensors are cloned, the layer is left untouched)."""
+        assert isinstance(layer, nn.Linear), "layer must be an instance of nn.Linear"
+        with torch.no_grad():
+            return cls(weight=layer.weight.clone(), bias=None if layer.bias is None else layer.bias.clone(),
+                       x_mxfp_meta=x_mxfp_meta, w_mxfp_meta=w_mxfp_meta, b_mxfp_meta=b_mxfp_meta,
+                       layer_type=layer_type, backend=backend)
+
+    @classmethod
+    def from_quantized(cls, w_scales: Tensor | None, w_elements: Tensor | None, w_tensor_meta: MXFPTensorMeta | None,
+                       bias: Tensor | None, b_scales: Tensor | None, b_elements: Tensor | None,
+                       b_tensor_meta: MXFPTensorMeta | None, x_mxfp_meta: MXFPMeta | None,
+                       layer_type: Literal["XWqB", "XWqBq", "XqWqB", "XqWqBq"], backend: Literal["separate", "fused"]):
+        """Rebuild a layer from stored codes (tensor metas are not part of ``state_dict``)."""
+        assert _all_given(w_scales, w_elements, w_tensor_meta)
+        return cls(weight=None, bias=bias, x_mxfp_meta=x_mxfp_meta, w_mxfp_meta=None, b_mxfp_meta=None,
+                   layer_type=layer_type, backend=backend,
+                   dtype=getattr(torch, w_tensor_meta.dtype), device=torch.device(w_tensor_meta.device),
+                   w_scales=w_scales, w_elements=w_elements, w_tensor_meta=w_tensor_meta,
+                   b_scales=b_scales, b_elements=b_elements, b_tensor_meta=b_tensor_meta)
