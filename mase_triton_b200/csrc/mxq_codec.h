@@ -46,6 +46,21 @@ struct FmtRT {
     MXQ_HD int rm() const { return rm_; }
 };
 
+// Integer adds, subtractions and left shifts written as a * k + b with k read from constant
+// memory: the compiler cannot fold k, so it emits an integer multiply-add, which issues on the
+// fp32/FMA pipe instead of the (saturated) integer ALU pipe.
+#if defined(__CUDACC__)
+static __constant__ int mxq_rt_k[5] = {1, 4, 256, 65536, 1 << 24};
+#endif
+MXQ_HD int rt_k(int i) {
+#if defined(__CUDA_ARCH__)
+    return mxq_rt_k[i];
+#else
+    return i == 0 ? 1 : i == 1 ? 4 : i == 2 ? 256 : i == 3 ? 65536 : (1 << 24);
+#endif
+}
+MXQ_HD int mad_add(int a, int b) { return a * rt_k(0) + b; }           // a + b
+
 template <class F> MXQ_HD int fmt_bias(const F& f) { return (1 << (f.eb() - 1)) - 1; }
 template <class F> MXQ_HD int fmt_emax(const F& f) { return f.fin() ? (1 << f.eb()) - 1 : (1 << f.eb()) - 2; }
 
@@ -121,36 +136,58 @@ MXQ_HD uint32_t encode_f32(uint32_t u, const F& f) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Fast encode core for round-to-nearest formats with exp_bits <= 7.
-//   ar = |x| bits minus ((127 - bias) << 23), as a signed integer: its "exponent field" is the
-//        biased minifloat exponent ye (possibly negative), its low 23 bits the fp32 mantissa.
-// Returns the unsigned magnitude code, WITHOUT the overflow clamp (callers that can overflow
-// apply it) and without sign / flush / Inf / NaN handling.
+// Fast encode core for the round-to-nearest presets (exp_bits <= 5, frac_bits <= 3).
+// Most of the work is moved to the fp32 pipe:
+//   * the mantissa, re-tagged with exponent 0 so it is a float in [1,2), is rounded half-to-even
+//     to frac_bits by adding 2^(23-fb): the low bits of the sum are 2^fb + f with f in [0, 2^fb];
+//   * exponent field and f are merged with OR, which reproduces the reference's lost carry;
+//   * the single subnormal binade is a 9-entry table held in an immediate.
+// qb : bits of the (possibly signed) fp32 value q to encode, its mantissa already cut to 15 bits.
+// Returns the magnitude code; no overflow clamp, sign, Inf or NaN handling.
 // ---------------------------------------------------------------------------------------------
+template <int FB>
+MXQ_HD constexpr uint64_t subnormal_table() {
+    // entry k (4 bits): code of the biased-exponent-0 binade whose rounded mantissa field is k
+    uint64_t t = 0;
+    for (int k = 1; k <= (1 << FB); ++k) {
+        const uint64_t c = (k == (1 << FB)) ? (1u << (FB - 1)) : (uint64_t)((k | (1 << FB)) >> 1);
+        t |= c << (4 * k);
+    }
+    return t;
+}
+
+MXQ_HD float add_rn(float a, float b) {
+#if defined(__CUDA_ARCH__)
+    return __fadd_rn(a, b);
+#else
+    volatile float r = a + b; return r;
+#endif
+}
+
 template <class F>
-MXQ_HD int encode_mag_rn(int ar, const F& f) {
-    const int fb = f.fb();
-    const int sh = 23 - fb;
-    // mantissa: drop the low 8 bits, round half-to-even at bit sh; a carry stays inside fr
-    const int t = ar & 0x007FFF00;
-    const int lsb = (ar >> (sh - 8)) & 0x100;
-    const int fr = (t + (((1 << (sh - 9)) - 1) << 8) + lsb) >> sh;          // 0 .. 2^fb
-    // exponent field shifted into place; OR (not add) keeps the reference's lost carry
-    int code = ((ar >> sh) & ~((1 << fb) - 1)) | fr;
-    // ye < 0 leaves a negative number here: underflow -> 0
-    code = code < 0 ? 0 : code;
-    // ye == 0: the single subnormal binade
-    if ((unsigned)ar < 0x00800000u && fr != 0) code = (fr | (1 << fb)) >> 1;
+MXQ_HD int encode_mag_fp(uint32_t qb, const F& f) {
+    constexpr int fb = F{}.fb(), eb = F{}.eb();
+    static_assert(fb >= 1 && fb <= 3 && eb <= 5, "table-driven subnormal path covers the built-in presets");
+    constexpr int sh = 23 - fb;
+    constexpr int bias = (1 << (eb - 1)) - 1;
+    constexpr uint32_t cbits = (uint32_t)(127 + 23 - fb) << 23;           // 2^(23-fb)
+    const float m = bits_f32((qb & 0x007FFFFFu) | 0x3F800000u);
+    const int fr = mad_add((int)f32_bits(add_rn(m, bits_f32(cbits))), -(int)(cbits + (1u << fb)));   // 0 .. 2^fb
+    int code = mad_add((int)(((qb >> sh) & (0xFFu << fb)) | (uint32_t)fr), -((127 - bias) << fb));
+    code = code < 0 ? 0 : code;                                            // biased exponent < 0
+    if ((qb & 0x7FFFFFFFu) < ((uint32_t)(128 - bias) << 23))               // biased exponent <= 0
+        code = (int)((subnormal_table<fb>() >> (code * rt_k(1))) & 0xFu);
+    (void)f;
     return code;
 }
 
-// Minifloat encode, fast path (RN, exp_bits <= 7): full semantics incl. overflow, Inf/NaN, flush.
+// Minifloat encode, fast path (RN presets, is_finite): full semantics incl. overflow, Inf/NaN, flush.
 template <class F>
 MXQ_HD uint32_t encode_f32_fast(uint32_t u, const F& f) {
     const int eb = f.eb(), fb = f.fb();
-    const int bias = fmt_bias(f), emax = fmt_emax(f);
-    uint32_t a = u & 0x7FFFFFFFu;
+    const int emax = fmt_emax(f);
     const uint32_t sign = 1u << (eb + fb);
+    uint32_t a = u & 0x7FFFFFFFu;
     if (a >= 0x7F800000u) {                       // Inf / NaN: rare
         const bool is_nan = a > 0x7F800000u;
         if (!f.fin()) {
@@ -163,14 +200,19 @@ MXQ_HD uint32_t encode_f32_fast(uint32_t u, const F& f) {
         a = (126u << 23) | m;
         u = is_nan ? a : ((u & 0x80000000u) | a);
     }
-    if (a < 0x00800000u)                          // fp32 zero / subnormal: flushed, keeps x<0
-        return ((u >> 31) && a != 0) ? sign : 0u;
-    int code = encode_mag_rn((int)a - ((127 - bias) << 23), f);
+    // an fp32 subnormal has exponent field 0 and encodes as magnitude 0 by itself
+    int code = encode_mag_fp(a & 0xFFFFFF00u, f);
     const int cmax = (emax << fb) | ((1 << fb) - 1);
-    // ye > emax saturates; ye == emax with a rounding carry already lost it through the OR
-    if ((int)(a >> 23) - 127 + bias > emax) code = cmax;
-    return (uint32_t)code | ((u >> 31) ? sign : 0u);
+    code = code > cmax ? cmax : code;             // emax is odd: a carry at emax was already dropped
+    // x < 0 (false for -0.0; NaN was given a clear sign above)
+    return (uint32_t)code | (u > 0x80000000u ? sign : 0u);
 }
+
+// Minifloat quantize-dequantize of one value, fast path: same result as
+// decode_f32_fast(encode_f32_fast(u)) with the sign taken straight from x + 0.0
+// (which is +0.0 for x = -0.0 and keeps the sign of everything else).
+template <class F>
+MXQ_HD uint32_t qdq_f32_fast(uint32_t u, const F& f);
 
 // ---------------------------------------------------------------------------------------------
 // Minifloat decode to fp32 bits (minifloat/fake.py:81-125). NaN results are 0x7FC00000 with the
@@ -214,6 +256,24 @@ MXQ_HD uint32_t decode_f32_fast(uint32_t code, const F& f) {
     uint32_t y = f32_bits(mul_rn(bits_f32(mag << (23 - fb)), bits_f32((uint32_t)(254 - fmt_bias(f)) << 23)));
     if (!f.fin() && (mag >> fb) == (1u << eb) - 1u) y = (mag & ((1u << fb) - 1u)) ? 0x7FC00000u : 0x7F800000u;
     return y | sign;
+}
+
+template <class F>
+MXQ_HD uint32_t qdq_f32_fast(uint32_t u, const F& f) {
+    const int eb = f.eb(), fb = f.fb();
+    uint32_t a = u & 0x7FFFFFFFu;
+    uint32_t sign = f32_bits(add_rn(bits_f32(u), 0.0f)) & 0x80000000u;
+    if (a >= 0x7F800000u) {                       // Inf / NaN: rare; same rule as encode_f32_fast
+        const bool is_nan = a > 0x7F800000u;
+        a = (126u << 23) | (is_nan ? ((a & 0x7FFFFFu) | 0x400000u) : 0u);
+        sign = is_nan ? 0u : (u & 0x80000000u);
+    }
+    int code = encode_mag_fp(a & 0xFFFFFF00u, f);
+    const int cmax = (fmt_emax(f) << fb) | ((1 << fb) - 1);
+    code = code > cmax ? cmax : code;
+    const float v = mul_rn(bits_f32((uint32_t)(code * rt_k(0)) << (23 - fb)), bits_f32((uint32_t)(254 - fmt_bias(f)) << 23));
+    (void)eb;
+    return f32_bits(v) | sign;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -279,20 +339,30 @@ MXQ_HD uint32_t mx_encode(uint32_t u, int se, const F& f) {
     return encode_f32(q, f) & 0xFFu;
 }
 
-// Fast MXFP element encode (RN, finite block, -127 <= se <= 127):
-//   rebase = (se + 127 - bias) << 23 precomputed per block.
+// Flush-to-zero of subnormal operands: x * 1.0 with the .ftz modifier (sign is kept).
+MXQ_HD float flush_subnormal(float x) {
+#if defined(__CUDA_ARCH__)
+    float r;
+    asm("mul.ftz.f32 %0, %1, 0f3F800000;" : "=f"(r) : "f"(x));
+    return r;
+#else
+    return ((f32_bits(x) & 0x7F800000u) == 0u) ? bits_f32(f32_bits(x) & 0x80000000u) : x;
+#endif
+}
+// Fast MXFP element encode (RN presets, finite block).
+//   inv_scale = 2^-se as an fp32 value (se in [-127, 127] for a finite block).
+// The quotient is formed by a real fp32 multiply (exact for a power of two, rounded like the
+// reference's division when it lands in the subnormal range), so "bits above 0x80000000" says
+// exactly "negative and non-zero after the reference's flush".
+// mx_quotient_bits: the quotient plus (+0.0), so that its sign bit alone says "negative and non-zero".
+MXQ_HD uint32_t mx_quotient_bits(uint32_t u, float inv_scale) {
+    return f32_bits(add_rn(mul_rn(flush_subnormal(bits_f32(u & 0xFFFFFF00u)), inv_scale), 0.0f));
+}
 template <class F>
-MXQ_HD uint32_t mx_encode_fast(uint32_t u, int rebase, const F& f) {
-    const uint32_t a = u & 0x7FFFFFFFu;
-    const int ar = (int)a - rebase;
-    int code = encode_mag_rn(ar, f);
-    const bool normal_in = a >= 0x00800000u;
-    // the quotient's own exponent field is (ar >> 23) + 127 - bias; it is non-zero in fp32 iff
-    // that exceeds -23, or equals -23 with a non-zero mantissa
-    const bool q_nonzero = ar > (fmt_bias(f) - 150) * (1 << 23);
-    if (!normal_in) code = 0;
-    if ((u >> 31) && normal_in && q_nonzero) code |= 1 << (f.eb() + f.fb());
-    return (uint32_t)code & 0xFFu;
+MXQ_HD uint32_t mx_encode_fast(uint32_t u, float inv_scale, const F& f) {
+    const uint32_t qb = mx_quotient_bits(u, inv_scale);
+    const uint32_t code = (uint32_t)encode_mag_fp(qb, f);
+    return code | ((qb >> (31 - f.eb() - f.fb())) & (1u << (f.eb() + f.fb())));
 }
 
 // MXFP compose of one element (mxfp/fake.py:71-78): decode(code) * 2^(scale-127) in fp32.

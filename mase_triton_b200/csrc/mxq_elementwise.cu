@@ -44,6 +44,9 @@ struct KBF16 {
 struct KF16 {
     static constexpr int size = 2;
     static __device__ __forceinline__ uint32_t to_bits(uint32_t raw) {
+        // a NaN keeps its sign and payload (quieted), as the x86 conversion does; the GPU's own
+        // conversion would return the canonical 0x7FFFFFFF
+        if ((raw & 0x7FFFu) > 0x7C00u) return ((raw & 0x8000u) << 16) | 0x7FC00000u | ((raw & 0x3FFu) << 13);
         return __float_as_uint(__half2float(__ushort_as_half((unsigned short)raw)));
     }
     static __device__ __forceinline__ uint32_t from_bits(uint32_t b) {
@@ -105,98 +108,20 @@ template <class K> __device__ __forceinline__ void store_elem_bits(void* base, i
 constexpr int kThreads = 256;
 
 // ------------------------------------------------------------------------------------------------
-// minifloat: vectorised element-wise kernel. Op maps (raw in) -> (raw out).
-// ------------------------------------------------------------------------------------------------
-template <int IN_SZ, int OUT_SZ, int V, int U, class Op>
-__global__ void __launch_bounds__(kThreads) ew_vec_kernel(const void* __restrict__ in, void* __restrict__ out,
-                                                          int64_t n_vec, Op op) {
-    const int64_t tile = (int64_t)blockIdx.x * (kThreads * U) + threadIdx.x;
-    Pack<V * IN_SZ> p[U];
-#pragma unroll
-    for (int j = 0; j < U; ++j) {
-        const int64_t idx = tile + j * kThreads;
-        if (idx < n_vec) p[j] = load_pack<V * IN_SZ>(reinterpret_cast<const char*>(in) + idx * (V * IN_SZ));
-    }
-#pragma unroll
-    for (int j = 0; j < U; ++j) {
-        const int64_t idx = tile + j * kThreads;
-        if (idx < n_vec) {
-            Pack<V * OUT_SZ> o;
-#pragma unroll
-            for (int i = 0; i < V; ++i) pack_set<OUT_SZ>(o, i, op(pack_get<IN_SZ>(p[j], i)));
-            store_pack<V * OUT_SZ>(reinterpret_cast<char*>(out) + idx * (V * OUT_SZ), o);
-        }
-    }
-}
-
-// scalar version for tails and unaligned buffers
-template <int IN_SZ, int OUT_SZ, class Op>
-__global__ void __launch_bounds__(kThreads) ew_scalar_kernel(const void* __restrict__ in, void* __restrict__ out,
-                                                             int64_t first, int64_t n, Op op) {
-    const int64_t i = first + (int64_t)blockIdx.x * kThreads + threadIdx.x;
-    if (i >= n) return;
-    uint32_t raw;
-    if constexpr (IN_SZ == 4) raw = reinterpret_cast<const uint32_t*>(in)[i];
-    else raw = reinterpret_cast<const uint16_t*>(in)[i];
-    const uint32_t r = op(raw);
-    if constexpr (OUT_SZ == 4) reinterpret_cast<uint32_t*>(out)[i] = r;
-    else reinterpret_cast<uint16_t*>(out)[i] = (uint16_t)r;
-}
-
-template <class KIn, class F, bool FAST> struct ExtractOp {
-    F f;
-    __device__ __forceinline__ uint32_t operator()(uint32_t raw) const {
-        const uint32_t u = KIn::to_bits(raw);
-        if constexpr (FAST) return encode_f32_fast(u, f); else return encode_f32(u, f);
-    }
-};
-template <class KOut, class F, bool FAST> struct ComposeOp {
-    F f;
-    __device__ __forceinline__ uint32_t operator()(uint32_t raw) const {
-        if constexpr (FAST) return KOut::from_bits(decode_f32_fast(raw, f)); else return KOut::from_bits(decode_f32(raw, f));
-    }
-};
-template <class KIn, class KOut, class F, bool FAST> struct QdqOp {
-    F f;
-    __device__ __forceinline__ uint32_t operator()(uint32_t raw) const {
-        const uint32_t u = KIn::to_bits(raw);
-        if constexpr (FAST) return KOut::from_bits(decode_f32_fast(encode_f32_fast(u, f), f));
-        else return KOut::from_bits(decode_f32(encode_f32(u, f), f));
-    }
-};
-
-template <int IN_SZ, int OUT_SZ, class Op>
-static int launch_ew(const void* in, void* out, int64_t n, Op op, cudaStream_t st) {
-    constexpr int WIDE = IN_SZ > OUT_SZ ? IN_SZ : OUT_SZ;
-    constexpr int V = 16 / WIDE;
-    constexpr int U = 4;
-    const bool aligned = ((reinterpret_cast<uintptr_t>(in) % (V * IN_SZ)) == 0) && ((reinterpret_cast<uintptr_t>(out) % (V * OUT_SZ)) == 0);
-    const int64_t n_vec = aligned ? n / V : 0;
-    if (n_vec > 0) {
-        const int64_t grid = (n_vec + kThreads * U - 1) / (kThreads * U);
-        ew_vec_kernel<IN_SZ, OUT_SZ, V, U, Op><<<(unsigned)grid, kThreads, 0, st>>>(in, out, n_vec, op);
-    }
-    const int64_t first = n_vec * V;
-    if (first < n) {
-        const int64_t grid = (n - first + kThreads - 1) / kThreads;
-        ew_scalar_kernel<IN_SZ, OUT_SZ, Op><<<(unsigned)grid, kThreads, 0, st>>>(in, out, first, n, op);
-    }
-    return check_launch();
-}
-
-// ------------------------------------------------------------------------------------------------
-// MXFP, block size 32: fast kernels
+// helpers shared by the fast kernels
 // ------------------------------------------------------------------------------------------------
 // Per-block header computed once per block by one lane and handed to the others by shuffle:
-//   bits 31..23 : (se + 127 - bias), the exponent rebase of the element encoder
-//   bit  0      : block holds Inf/NaN (generic path)
+//   bits 30..23 : exponent field of 2^-se, so (header & 0x7F800000) IS the fp32 factor 2^-se
 //   bits 15..8  : the E8M0 scale byte
+//   bit  0      : block holds Inf/NaN (generic path)
 template <class F>
 __device__ __forceinline__ uint32_t block_header(uint32_t amax_bits, const F& f) {
     uint32_t sbyte;
     const int se = shared_exponent(amax_bits, f, &sbyte);
     const uint32_t special = amax_bits >= 0x7F800000u ? 1u : 0u;
-    return ((uint32_t)(se + 127 - fmt_bias(f)) << 23) | (sbyte << 8) | special;
+    // an all-flushed block (exponent field 0) encodes to zeros whatever the factor: use 1.0
+    const uint32_t inv_field = ((amax_bits >> 23) == 0u || special) ? 127u : (uint32_t)(127 - se);
+    return (inv_field << 23) | (sbyte << 8) | special;
 }
 
 __device__ __forceinline__ float scale_from_byte(uint32_t s) {
@@ -204,80 +129,277 @@ __device__ __forceinline__ float scale_from_byte(uint32_t s) {
     return __uint_as_float(s == 0u ? 0x00400000u : (s << 23));
 }
 
-template <class KIn, class KOut, class F, int U, bool WRITE_CODES>
-__global__ void __launch_bounds__(kThreads) mxfp_b32_quant_kernel(const void* __restrict__ x, uint8_t* __restrict__ scales,
-                                                                  uint8_t* __restrict__ elements, void* __restrict__ out,
-                                                                  int64_t n_vec, F f) {
+__device__ __forceinline__ float max_abs_nan(float a, float b) {
+    float r;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(fabsf(a)), "f"(fabsf(b)));
+    return r;
+}
+
+// fp32 bits of max |x| over the V elements of a 16-byte pack; any NaN wins
+template <class K>
+__device__ __forceinline__ uint32_t pack_absmax_bits(const Pack<16>& p) {
+    if constexpr (K::size == 4) {
+        const float m = max_abs_nan(max_abs_nan(__uint_as_float(p.w[0]), __uint_as_float(p.w[1])),
+                                    max_abs_nan(__uint_as_float(p.w[2]), __uint_as_float(p.w[3])));
+        return __float_as_uint(m);
+    } else if constexpr (std::is_same<K, KBF16>::value) {
+        __nv_bfloat162 m = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&p.w[0]));
+#pragma unroll
+        for (int i = 1; i < 4; ++i) m = __hmax2_nan(m, __habs2(*reinterpret_cast<const __nv_bfloat162*>(&p.w[i])));
+        const uint32_t mw = *reinterpret_cast<uint32_t*>(&m);
+        return __float_as_uint(max_abs_nan(__uint_as_float(mw << 16), __uint_as_float(mw & 0xFFFF0000u)));
+    } else {
+        __half2 m = __habs2(*reinterpret_cast<const __half2*>(&p.w[0]));
+#pragma unroll
+        for (int i = 1; i < 4; ++i) m = __hmax2_nan(m, __habs2(*reinterpret_cast<const __half2*>(&p.w[i])));
+        const float2 mf = __half22float2(m);
+        return __float_as_uint(max_abs_nan(mf.x, mf.y));
+    }
+}
+
+// V fp32 results -> V * K::size bytes at dst. `plain` promises that no result is NaN, so the
+// packed hardware conversions can be used for 16-bit outputs.
+template <class K, int V>
+__device__ __forceinline__ void store_results(void* dst, const uint32_t (&y)[V], bool plain) {
+    if constexpr (K::size == 4) {
+#pragma unroll
+        for (int i = 0; i < V; i += 4) {
+            Pack<16> o{{y[i], y[i + 1], y[i + 2], y[i + 3]}};
+            store_pack<16>(reinterpret_cast<char*>(dst) + 4 * i, o);
+        }
+    } else {
+        Pack<2 * V> o;
+        if (plain) {
+#pragma unroll
+            for (int i = 0; i < V; i += 2) {
+                if constexpr (std::is_same<K, KBF16>::value) {
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(y[i]), __uint_as_float(y[i + 1]));
+                    o.w[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+                } else {
+                    const __half2 h = __floats2half2_rn(__uint_as_float(y[i]), __uint_as_float(y[i + 1]));
+                    o.w[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < V; ++i) pack_set<2>(o, i, K::from_bits(y[i]));
+        }
+        store_pack<2 * V>(dst, o);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// minifloat: vectorised element-wise kernel.
+//   KIn / KOut : storage kinds (KF32 / KBF16 / KF16 floating, KU16 codes)
+//   Op         : maps the fp32 bits of a floating input (or the raw code of a KU16 input) to the
+//                fp32 bits of a floating output (or the raw code of a KU16 output)
+//   PLAIN      : the op never yields NaN, so 16-bit outputs may use the packed conversions
+// ------------------------------------------------------------------------------------------------
+template <class K, int BYTES>
+__device__ __forceinline__ uint32_t pack_elem(const Pack<BYTES>& p, int i) {
+    if constexpr (std::is_same<K, KU16>::value) return pack_get<2>(p, i);
+    else return pack_bits<K>(p, i);
+}
+
+template <class KIn, class KOut, int V, int U, bool PLAIN, bool FULL, class Op>
+__device__ __forceinline__ void ew_tile(const char* __restrict__ src, char* __restrict__ dst, int64_t left, const Op& op) {
+    // src / dst already point at this thread's first vector; `left` = vectors from there to the end
+    constexpr int IB = V * KIn::size, OB = V * KOut::size;
+    Pack<IB> p[U];
+#pragma unroll
+    for (int j = 0; j < U; ++j)
+        if (FULL || j * kThreads < left) p[j] = load_pack<IB>(src + (size_t)j * kThreads * IB);
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+        if (!FULL && j * kThreads >= left) continue;
+        uint32_t y[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) y[i] = op(pack_elem<KIn>(p[j], i));
+        char* d = dst + (size_t)j * kThreads * OB;
+        if constexpr (std::is_same<KOut, KU16>::value) {
+            Pack<OB> o;
+#pragma unroll
+            for (int i = 0; i < V; ++i) pack_set<2>(o, i, y[i]);
+            store_pack<OB>(d, o);
+        } else {
+            store_results<KOut, V>(d, y, PLAIN);
+        }
+    }
+}
+
+template <class KIn, class KOut, int V, int U, bool PLAIN, class Op>
+__global__ void __launch_bounds__(kThreads) ew_vec_kernel(const void* __restrict__ in, void* __restrict__ out,
+                                                          int64_t n_vec, Op op) {
+    const int64_t first = (int64_t)blockIdx.x * (kThreads * U) + threadIdx.x;
+    const char* src = reinterpret_cast<const char*>(in) + first * (V * KIn::size);
+    char* dst = reinterpret_cast<char*>(out) + first * (V * KOut::size);
+    if ((int64_t)(blockIdx.x + 1) * (kThreads * U) <= n_vec) ew_tile<KIn, KOut, V, U, PLAIN, true>(src, dst, 0, op);
+    else ew_tile<KIn, KOut, V, U, PLAIN, false>(src, dst, n_vec - first, op);
+}
+
+// scalar version for tails and unaligned buffers
+template <class KIn, class KOut, class Op>
+__global__ void __launch_bounds__(kThreads) ew_scalar_kernel(const void* __restrict__ in, void* __restrict__ out,
+                                                             int64_t first, int64_t n, Op op) {
+    const int64_t i = first + (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (i >= n) return;
+    uint32_t v;
+    if constexpr (std::is_same<KIn, KU16>::value) v = reinterpret_cast<const uint16_t*>(in)[i];
+    else v = load_elem_bits<KIn>(in, i);
+    const uint32_t r = op(v);
+    if constexpr (std::is_same<KOut, KU16>::value) reinterpret_cast<uint16_t*>(out)[i] = (uint16_t)r;
+    else store_elem_bits<KOut>(out, i, r);
+}
+
+template <class F, bool FAST> struct ExtractOp {
+    F f;
+    __device__ __forceinline__ uint32_t operator()(uint32_t u) const {
+        if constexpr (FAST) return encode_f32_fast(u, f); else return encode_f32(u, f);
+    }
+};
+template <class F, bool FAST> struct ComposeOp {
+    F f;
+    __device__ __forceinline__ uint32_t operator()(uint32_t code) const {
+        if constexpr (FAST) return decode_f32_fast(code, f); else return decode_f32(code, f);
+    }
+};
+template <class F, bool FAST> struct QdqOp {
+    F f;
+    __device__ __forceinline__ uint32_t operator()(uint32_t u) const {
+        if constexpr (FAST) return qdq_f32_fast(u, f);
+        else return decode_f32(encode_f32(u, f), f);
+    }
+};
+
+template <class KIn, class KOut, bool PLAIN, class Op>
+static int launch_ew(const void* in, void* out, int64_t n, Op op, cudaStream_t st) {
+    constexpr int WIDE = KIn::size > KOut::size ? KIn::size : KOut::size;
+    constexpr int V = 16 / WIDE;
+    constexpr int U = 4;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(in) % (V * KIn::size)) == 0) && ((reinterpret_cast<uintptr_t>(out) % (V * KOut::size)) == 0);
+    const int64_t n_vec = aligned ? n / V : 0;
+    if (n_vec > 0) {
+        const int64_t grid = (n_vec + kThreads * U - 1) / (kThreads * U);
+        ew_vec_kernel<KIn, KOut, V, U, PLAIN, Op><<<(unsigned)grid, kThreads, 0, st>>>(in, out, n_vec, op);
+    }
+    const int64_t first = n_vec * V;
+    if (first < n) {
+        const int64_t grid = (n - first + kThreads - 1) / kThreads;
+        ew_scalar_kernel<KIn, KOut, Op><<<(unsigned)grid, kThreads, 0, st>>>(in, out, first, n, op);
+    }
+    return check_launch();
+}
+
+// ------------------------------------------------------------------------------------------------
+// MXFP, block size 32: fast kernels
+// ------------------------------------------------------------------------------------------------
+// four magnitude codes (one per byte) plus the sign bits taken from the top bytes of the quotients
+template <class F>
+__device__ __forceinline__ uint32_t pack4_codes(const uint32_t* mag, const uint32_t* qb, const F& f) {
+    constexpr int sp = F{}.eb() + F{}.fb();                 // sign position inside the code byte
+    uint32_t w = (uint32_t)((int)mag[3] * rt_k(4) + ((int)mag[2] * rt_k(3) + ((int)mag[1] * rt_k(2) + (int)mag[0])));
+    const uint32_t s01 = __byte_perm(qb[0], qb[1], 0x0073);
+    const uint32_t s23 = __byte_perm(qb[2], qb[3], 0x0073);
+    const uint32_t sg = __byte_perm(s01, s23, 0x5410);
+    if constexpr (sp == 7) w |= sg & 0x80808080u;
+    else w |= (sg >> (7 - sp)) & (0x01010101u << sp);
+    (void)f;
+    return w;
+}
+
+template <class KIn, class F, int U, bool WRITE_CODES, bool FULL>
+__device__ __forceinline__ void mxfp_b32_quant_tile(const char* __restrict__ src, uint8_t* __restrict__ scales,
+                                                    char* __restrict__ dst, int64_t first, int64_t left, const F& f) {
     constexpr int V = 16 / KIn::size;     // elements per lane per access: 4 (fp32) or 8 (16-bit)
     constexpr int G = 32 / V;             // lanes that share one 32-element block: 8 or 4
     static_assert(U <= G, "one lane of the group per in-flight access");
+    constexpr int OB = WRITE_CODES ? V : 16;
     const int lane = threadIdx.x & 31;
     const int sub = lane & (G - 1);
-    const int64_t tile = (int64_t)blockIdx.x * (kThreads * U) + threadIdx.x;
 
     Pack<16> p[U];
     uint32_t amax[U];
 #pragma unroll
     for (int j = 0; j < U; ++j) {
-        const int64_t idx = tile + j * kThreads;
-        if (idx < n_vec) p[j] = load_pack<16>(reinterpret_cast<const char*>(x) + idx * 16);
+        if (FULL || j * kThreads < left) p[j] = load_pack<16>(src + (size_t)j * kThreads * 16);
         else p[j] = Pack<16>{{0u, 0u, 0u, 0u}};
     }
 #pragma unroll
     for (int j = 0; j < U; ++j) {
-        uint32_t m = 0;
+        float m = __uint_as_float(pack_absmax_bits<KIn>(p[j]));
 #pragma unroll
-        for (int i = 0; i < V; ++i) m = max(m, pack_bits<KIn>(p[j], i) & 0x7FFFFFFFu);
-#pragma unroll
-        for (int o = 1; o < G; o <<= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
-        amax[j] = m;
+        for (int o = 1; o < G; o <<= 1) m = max_abs_nan(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+        amax[j] = __float_as_uint(m);
     }
     // lane `sub` of each group derives the header of access `sub`
     uint32_t mine = amax[0];
 #pragma unroll
     for (int j = 1; j < U; ++j) mine = (sub == j) ? amax[j] : mine;
     const uint32_t hdr = block_header(mine, f);
-    if (WRITE_CODES && sub < U) {
-        const int64_t idx = tile + sub * kThreads;
-        if (idx < n_vec) scales[idx / G] = (uint8_t)(hdr >> 8);
-    }
+    if (WRITE_CODES && sub < U && (FULL || sub * kThreads < left))
+        scales[(first + sub * kThreads) / G] = (uint8_t)(hdr >> 8);
 #pragma unroll
     for (int j = 0; j < U; ++j) {
         const uint32_t h = __shfl_sync(0xFFFFFFFFu, hdr, (lane & ~(G - 1)) + j);
-        const int64_t idx = tile + j * kThreads;
-        if (idx >= n_vec) continue;
-        uint32_t code[V];
+        if (!FULL && j * kThreads >= left) continue;
+        char* d = dst + (size_t)j * kThreads * OB;
         if (!(h & 1u)) {
-            const int rebase = (int)(h & 0xFF800000u);
-#pragma unroll
-            for (int i = 0; i < V; ++i) code[i] = mx_encode_fast(pack_bits<KIn>(p[j], i), rebase, f);
-        } else {
-#pragma unroll
-            for (int i = 0; i < V; ++i) code[i] = mx_encode(pack_bits<KIn>(p[j], i), 128, f);
-        }
-        if constexpr (WRITE_CODES) {
-            Pack<V> o;
-#pragma unroll
-            for (int i = 0; i < V; ++i) pack_set<1>(o, i, code[i]);
-            store_pack<V>(elements + idx * V, o);
-        } else {
-            const uint32_t sb = (h >> 8) & 0xFFu;
-            const float sf = scale_from_byte(sb);
-            constexpr int OB = V * KOut::size;      // 16 or 32 bytes per lane
-            Pack<(OB > 16 ? 16 : OB)> o[OB > 16 ? 2 : 1];
+            const float inv = __uint_as_float(h & 0x7F800000u);
+            uint32_t qb[V], mag[V];
 #pragma unroll
             for (int i = 0; i < V; ++i) {
-                uint32_t y;
-                if (sb != 255u) y = __float_as_uint(__fmul_rn(__uint_as_float(decode_f32_fast(code[i], f)), sf));
-                else y = mx_decode(code[i], sf, f);
-                constexpr int per = (OB > 16 ? 16 : OB) / KOut::size;
-                pack_set<KOut::size>(o[i / per], i % per, KOut::from_bits(y));
+                qb[i] = mx_quotient_bits(pack_bits<KIn>(p[j], i), inv);
+                mag[i] = (uint32_t)encode_mag_fp(qb[i], f);
             }
-            char* dst = reinterpret_cast<char*>(out) + idx * OB;
-            store_pack<(OB > 16 ? 16 : OB)>(dst, o[0]);
-            if constexpr (OB > 16) store_pack<16>(dst + 16, o[1]);
+            if constexpr (WRITE_CODES) {
+                Pack<V> o;
+#pragma unroll
+                for (int i = 0; i < V; i += 4) o.w[i >> 2] = pack4_codes(&mag[i], &qb[i], f);
+                store_pack<V>(d, o);
+            } else {
+                const uint32_t sb = (h >> 8) & 0xFFu;       // never 255 for a finite block
+                const float sf = scale_from_byte(sb);
+                const float unbias = __uint_as_float((uint32_t)(254 - fmt_bias(f)) << 23);
+                uint32_t y[V];
+#pragma unroll
+                for (int i = 0; i < V; ++i) {
+                    const float v = __fmul_rn(__uint_as_float((uint32_t)((int)mag[i] * rt_k(0)) << (23 - f.fb())), unbias);
+                    y[i] = __float_as_uint(__fmul_rn(v, sf)) | (qb[i] & 0x80000000u);
+                }
+                store_results<KIn, V>(d, y, true);
+            }
+        } else {
+            uint32_t code[V];
+#pragma unroll
+            for (int i = 0; i < V; ++i) code[i] = mx_encode(pack_bits<KIn>(p[j], i), 128, f);
+            if constexpr (WRITE_CODES) {
+                Pack<V> o;
+#pragma unroll
+                for (int i = 0; i < V; ++i) pack_set<1>(o, i, code[i]);
+                store_pack<V>(d, o);
+            } else {
+                const float sf = scale_from_byte((h >> 8) & 0xFFu);
+                uint32_t y[V];
+#pragma unroll
+                for (int i = 0; i < V; ++i) y[i] = mx_decode(code[i], sf, f);
+                store_results<KIn, V>(d, y, false);
+            }
         }
     }
+}
+
+template <class KIn, class F, int U, bool WRITE_CODES>
+__global__ void __launch_bounds__(kThreads) mxfp_b32_quant_kernel(const void* __restrict__ x, uint8_t* __restrict__ scales,
+                                                                  uint8_t* __restrict__ elements, void* __restrict__ out,
+                                                                  int64_t n_vec, F f) {
+    constexpr int V = 16 / KIn::size;
+    const int64_t first = (int64_t)blockIdx.x * (kThreads * U) + threadIdx.x;
+    const char* src = reinterpret_cast<const char*>(x) + first * 16;
+    char* dst = WRITE_CODES ? reinterpret_cast<char*>(elements) + first * V : reinterpret_cast<char*>(out) + first * 16;
+    if ((int64_t)(blockIdx.x + 1) * (kThreads * U) <= n_vec)
+        mxfp_b32_quant_tile<KIn, F, U, WRITE_CODES, true>(src, scales, dst, first, 0, f);
+    else
+        mxfp_b32_quant_tile<KIn, F, U, WRITE_CODES, false>(src, scales, dst, first, n_vec - first, f);
 }
 
 template <class KOut, class F, int U>
@@ -302,16 +424,15 @@ __global__ void __launch_bounds__(kThreads) mxfp_b32_compose_kernel(const uint8_
         const int64_t idx = tile + j * kThreads;
         if (idx >= n_vec) continue;
         const float sf = scale_from_byte(sb[j]);
-        Pack<16> o;
+        const bool plain = sb[j] != 255u;
+        uint32_t y[V];
 #pragma unroll
         for (int i = 0; i < V; ++i) {
             const uint32_t code = pack_get<1>(c[j], i);
-            uint32_t y;
-            if (sb[j] != 255u) y = __float_as_uint(__fmul_rn(__uint_as_float(decode_f32_fast(code, f)), sf));
-            else y = mx_decode(code, sf, f);
-            pack_set<KOut::size>(o, i, KOut::from_bits(y));
+            if (plain) y[i] = __float_as_uint(__fmul_rn(__uint_as_float(decode_f32_fast(code, f)), sf));
+            else y[i] = mx_decode(code, sf, f);
         }
-        store_pack<16>(reinterpret_cast<char*>(out) + idx * 16, o);
+        store_results<KOut, V>(reinterpret_cast<char*>(out) + idx * 16, y, plain);
     }
 }
 
@@ -385,9 +506,9 @@ extern "C" int mxq_minifloat_extract(const void* x, int x_dtype, uint16_t* codes
     with_kind(x_dtype, [&](auto kin) {
         using KIn = decltype(kin);
         const bool fast = with_preset(eb, fb, is_finite, rm, [&](auto f) {
-            rc = launch_ew<KIn::size, 2>(x, codes, n, ExtractOp<KIn, decltype(f), true>{f}, st);
+            rc = launch_ew<KIn, KU16, true>(x, codes, n, ExtractOp<decltype(f), true>{f}, st);
         });
-        if (!fast) rc = launch_ew<KIn::size, 2>(x, codes, n, ExtractOp<KIn, FmtRT, false>{FmtRT{eb, fb, is_finite, rm}}, st);
+        if (!fast) rc = launch_ew<KIn, KU16, false>(x, codes, n, ExtractOp<FmtRT, false>{FmtRT{eb, fb, is_finite, rm}}, st);
     });
     return rc;
 }
@@ -402,9 +523,9 @@ extern "C" int mxq_minifloat_compose(const uint16_t* codes, void* out, int out_d
     with_kind(out_dtype, [&](auto kout) {
         using KOut = decltype(kout);
         const bool fast = with_preset(eb, fb, is_finite, RM_RN, [&](auto f) {
-            rc = launch_ew<2, KOut::size>(codes, out, n, ComposeOp<KOut, decltype(f), true>{f}, st);
+            rc = launch_ew<KU16, KOut, true>(codes, out, n, ComposeOp<decltype(f), true>{f}, st);
         });
-        if (!fast) rc = launch_ew<2, KOut::size>(codes, out, n, ComposeOp<KOut, FmtRT, false>{FmtRT{eb, fb, is_finite, 0}}, st);
+        if (!fast) rc = launch_ew<KU16, KOut, false>(codes, out, n, ComposeOp<FmtRT, false>{FmtRT{eb, fb, is_finite, 0}}, st);
     });
     return rc;
 }
@@ -421,10 +542,10 @@ extern "C" int mxq_minifloat_qdq(const void* x, int x_dtype, void* out, int out_
         with_kind(out_dtype, [&](auto kout) {
             using KOut = decltype(kout);
             const bool fast = with_preset(eb, fb, is_finite, rm, [&](auto f) {
-                rc = launch_ew<KIn::size, KOut::size>(x, out, n, QdqOp<KIn, KOut, decltype(f), true>{f}, st);
+                rc = launch_ew<KIn, KOut, true>(x, out, n, QdqOp<decltype(f), true>{f}, st);
             });
             if (!fast)
-                rc = launch_ew<KIn::size, KOut::size>(x, out, n, QdqOp<KIn, KOut, FmtRT, false>{FmtRT{eb, fb, is_finite, rm}}, st);
+                rc = launch_ew<KIn, KOut, false>(x, out, n, QdqOp<FmtRT, false>{FmtRT{eb, fb, is_finite, rm}}, st);
         });
     });
     return rc;
@@ -448,7 +569,7 @@ static int mxfp_quant_dispatch(const void* x, int x_dtype, uint8_t* scales, uint
                     constexpr int U = 4;
                     const int64_t n_vec = n / V;
                     const int64_t grid = (n_vec + kThreads * U - 1) / (kThreads * U);
-                    mxfp_b32_quant_kernel<KIn, KOut, decltype(f), U, WRITE_CODES><<<(unsigned)grid, kThreads, 0, st>>>(
+                    mxfp_b32_quant_kernel<KIn, decltype(f), U, WRITE_CODES><<<(unsigned)grid, kThreads, 0, st>>>(
                         x, scales, elements, out, n_vec, f);
                     rc = check_launch();
                 });

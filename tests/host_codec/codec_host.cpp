@@ -27,6 +27,14 @@ extern "C" int hc_minifloat_encode(const uint32_t* bits, uint16_t* out, int64_t 
     return 0;
 }
 
+extern "C" int hc_minifloat_qdq(const uint32_t* bits, uint32_t* out, int64_t n, int eb, int fb, int fin, int rm, int fast) {
+    if (fast && with_preset(eb, fb, fin, rm, [&](auto f) { for (int64_t i = 0; i < n; ++i) out[i] = qdq_f32_fast(bits[i], f); }))
+        return 1;
+    FmtRT f{eb, fb, fin, rm};
+    for (int64_t i = 0; i < n; ++i) out[i] = decode_f32(encode_f32(bits[i], f), f);
+    return 0;
+}
+
 extern "C" int hc_minifloat_decode(const uint16_t* codes, uint32_t* out, int64_t n, int eb, int fb, int fin, int fast) {
     if (fast && with_preset(eb, fb, fin, RM_RN, [&](auto f) { for (int64_t i = 0; i < n; ++i) out[i] = decode_f32_fast(codes[i], f); }))
         return 1;
@@ -44,10 +52,12 @@ static void mx_extract_blocks(const uint32_t* bits, uint8_t* scales, uint8_t* el
         const int se = shared_exponent(amax, f, &sbyte);
         scales[b] = (uint8_t)sbyte;
         const bool special = amax >= 0x7F800000u;
-        const int rebase = (int)((uint32_t)(se + 127 - fmt_bias(f)) << 23);
+        // 2^-se; an all-flushed block (se = 128 or -127) encodes to zeros with any finite factor
+        const float inv = bits_f32((amax >> 23) == 0u ? 0x3F800000u : (uint32_t)(127 - se) << 23);
         for (int j = 0; j < B; ++j) {
             const uint32_t u = bits[b * B + j];
-            el[b * B + j] = (uint8_t)((fast && !special) ? mx_encode_fast(u, rebase, f) : mx_encode(u, se, f));
+            if constexpr (F::kStatic) el[b * B + j] = (uint8_t)((fast && !special) ? mx_encode_fast(u, inv, f) : mx_encode(u, se, f));
+            else el[b * B + j] = (uint8_t)mx_encode(u, se, f);
         }
     }
 }

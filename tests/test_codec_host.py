@@ -29,6 +29,7 @@ def hc():
     p, i64, i = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
     L.hc_minifloat_encode.argtypes = [p, p, i64, i, i, i, i, i]
     L.hc_minifloat_decode.argtypes = [p, p, i64, i, i, i, i]
+    L.hc_minifloat_qdq.argtypes = [p, p, i64, i, i, i, i, i]
     L.hc_mxfp_extract.argtypes = [p, p, p, i64, i, i, i, i, i, i]
     L.hc_mxfp_compose.argtypes = [p, p, p, i64, i, i, i, i, i]
     L.hc_log2_roundup_count.argtypes = [i]
@@ -63,6 +64,18 @@ def test_minifloat_encode_fast(hc, name):
         allv = torch.arange(-(2**15), 2**15, dtype=torch.int32).to(torch.int16).view(dt).float()
         got, _ = _encode(hc, allv, eb, fb, True, "rn", fast=True)
         assert_bits_equal(got, oracle.extract_minifloat_component(allv, mf_meta(eb, fb)), f"{name} all {dt}")
+
+
+@pytest.mark.parametrize("name", list(PRESETS))
+def test_minifloat_qdq_fast(hc, name):
+    eb, fb = PRESETS[name]
+    xs = [adversarial_fp32(1 << 18, seed=11)]
+    xs += [torch.arange(-(2**15), 2**15, dtype=torch.int32).to(torch.int16).view(dt).float() for dt in (torch.bfloat16, torch.float16)]
+    for x in xs:
+        x = x.contiguous()
+        out = torch.empty(x.numel(), dtype=torch.int32)
+        assert hc.hc_minifloat_qdq(x.data_ptr(), out.data_ptr(), x.numel(), eb, fb, 1, 0, 1) == 1
+        assert_bits_equal(out.view(torch.float32), oracle.quantize_dequantize_minifloat(x, mf_meta(eb, fb)), name)
 
 
 @pytest.mark.parametrize("eb,fb", list(PRESETS.values()) + [(8, 7), (5, 10), (3, 4), (1, 1), (7, 8), (10, 5)])
