@@ -15,7 +15,7 @@ from pathlib import Path
 
 CSRC = Path(__file__).resolve().parent / "csrc"
 LIB = CSRC / "libmxq.so"
-SOURCES = ["mxq_api.cu", "mxq_elementwise.cu"]
+SOURCES = ["mxq_api.cu", "mxq_elementwise.cu", "mxq_gemm.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--threads", "4"]
 
@@ -54,7 +54,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             print(out)
         if p.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src}:\n{out}")
-    link = [_nvcc(), "-shared", "-o", str(LIB), *map(str, objs), "-lcuda"]
+    link = [_nvcc(), "-shared", "-o", str(LIB), *map(str, objs)]
     r = subprocess.run(link, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")

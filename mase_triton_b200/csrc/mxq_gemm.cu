@@ -1,0 +1,436 @@
+// Block-scaled MX GEMM for sm_100a: out[M,N] = dequant(A)[M,K] * dequant(B)[N,K]^T (+ bias).
+//
+// Both operands are MXFP tensors with 32-element blocks along K.  The kernel feeds the 5th-gen
+// tensor cores directly with the quantised data:
+//   * operand codes (one byte per element, OCP E4M3 or E5M2 as the hardware reads them) are staged
+//     by TMA (cp.async.bulk.tensor, 128-byte swizzle) into a 4-stage shared-memory ring;
+//   * the E8M0 block scales of a 128 x 128(K) tile are one 512-byte chunk, brought in with a bulk copy
+//     and moved shared -> tensor memory with tcgen05.cp;
+//   * one elected thread issues tcgen05.mma.kind::mxf8f6f4.block_scale (M=128, N=256, K=32), four
+//     per K tile; the fp32 accumulator (128 lanes x 256 columns) lives in tensor memory;
+//   * four epilogue warps read it back with tcgen05.ld, add the bias, convert and store.
+// Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer (also owns the TMEM allocation),
+// warps 2..5 = epilogue.  Every wait on an mbarrier is bounded; a wait that runs out records a
+// code in the caller's status word and the CTA unwinds (TMEM is freed) instead of spinning.
+//
+// Operand layout in HBM (produced by the pack kernel in this file):
+//   codes : [rows, K] bytes, K contiguous
+//   sf    : [ceil(rows/128)][ceil(K/128)][512] bytes; inside a chunk the scale of row r (0..127) and
+//           K block b (0..3) sits at (r % 32) * 16 + (r / 32) * 4 + b  -- the order tcgen05.cp
+//           (32x128b.warpx4) expects.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cmath>
+#include <mutex>
+
+#include "../../include/mxq.h"
+#include "mxq_codec.h"
+#include "mxq_internal.h"
+
+namespace mxq {
+namespace gemm {
+
+constexpr int BM = 128, BN = 256, BK = 128, STAGES = 4;
+constexpr int A_BYTES = BM * BK;                 // 16 KiB
+constexpr int B_BYTES = BN * BK;                 // 32 KiB
+constexpr int SFA_BYTES = 512, SFB_BYTES = 1024, SF_REGION = 2048;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SF_REGION;         // 50 KiB, multiple of 1024
+constexpr int TX_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+constexpr int BAR_BYTES = 256;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + slack to align the ring to 1024
+constexpr int TMEM_COLS = 512;
+constexpr int ACC_COL = 0, SFA_COL = 256, SFB_COL = 260;
+constexpr int THREADS = 192;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+
+// status codes written to the caller's status word when a bounded wait runs out
+enum : int { ST_OK = 0, ST_PRODUCER_TIMEOUT = 1, ST_MMA_TIMEOUT = 2, ST_EPILOGUE_TIMEOUT = 3 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait: false (and a code in *status) when the phase never completes
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+    for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (it > 64) __nanosleep(32);
+    }
+    if (status) atomicCAS(status, 0, code);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// shared-memory matrix descriptors (tcgen05): start address, leading/stride byte offsets in 16-byte
+// units, version 1, layout type in bits 61..63
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
+    return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | ((uint64_t)layout << 61);
+}
+constexpr uint32_t LAYOUT_NONE = 0, LAYOUT_SW128 = 2;
+
+__device__ __forceinline__ void tmem_cp_32x128b(uint32_t taddr, uint64_t desc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void mma_mxf8f6f4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+
+template <int OUT_DT>   // MXQ_F32 / MXQ_BF16 / MXQ_F16
+__global__ void __launch_bounds__(THREADS, 1)
+mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, void* __restrict__ out,
+               const void* __restrict__ bias, int M, int N, int K, uint32_t idesc_base, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t ring = (raw + 1023u) & ~1023u;                    // 1024-aligned operand ring
+    uint8_t* ring_ptr = smem_raw + (ring - raw);
+    const uint32_t bars = ring + STAGES * STAGE_BYTES;               // full[S], empty[S], accum, tmem slot
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ring_ptr + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 1));
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    const uint32_t accum_bar = bars + 8u * (2 * STAGES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_tile = blockIdx.x, m_tile = blockIdx.y;
+    const int KT = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        mbar_init(accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        const uint8_t* sfa_tile = sfa + (size_t)m_tile * KT * 512;
+        const uint8_t* sfb_tile0 = sfb + (size_t)(2 * n_tile) * KT * 512;
+        const uint8_t* sfb_tile1 = sfb + (size_t)(2 * n_tile + 1) * KT * 512;
+        bool ok = true;
+        for (int kt = 0; kt < KT && ok; ++kt) {
+            const int s = kt % STAGES;
+            if (kt >= STAGES) ok = mbar_wait(empty_bar(s), ((kt / STAGES) & 1) ^ 1, status, ST_PRODUCER_TIMEOUT);
+            if (ok && lane == 0) {
+                const uint32_t st = ring + s * STAGE_BYTES;
+                mbar_expect_tx(full_bar(s), TX_BYTES);
+                tma_load_2d(st, &map_a, kt * BK, m_tile * BM, full_bar(s));
+                tma_load_2d(st + A_BYTES, &map_b, kt * BK, n_tile * BN, full_bar(s));
+                bulk_load(st + A_BYTES + B_BYTES, sfa_tile + (size_t)kt * 512, 512, full_bar(s));
+                bulk_load(st + A_BYTES + B_BYTES + 512, sfb_tile0 + (size_t)kt * 512, 512, full_bar(s));
+                bulk_load(st + A_BYTES + B_BYTES + 1024, sfb_tile1 + (size_t)kt * 512, 512, full_bar(s));
+            }
+            __syncwarp();
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        bool ok = true;
+        for (int kt = 0; kt < KT && ok; ++kt) {
+            const int s = kt % STAGES;
+            ok = mbar_wait(full_bar(s), (kt / STAGES) & 1, status, ST_MMA_TIMEOUT);
+            tc_fence_after();
+            if (ok && lane == 0) {
+                const uint32_t st = ring + s * STAGE_BYTES;
+                const uint32_t sf = st + A_BYTES + B_BYTES;
+                tmem_cp_32x128b(tmem_base + SFA_COL, smem_desc(sf, 0, 128, LAYOUT_NONE));
+                tmem_cp_32x128b(tmem_base + SFB_COL, smem_desc(sf + 512, 0, 128, LAYOUT_NONE));
+                tmem_cp_32x128b(tmem_base + SFB_COL + 4, smem_desc(sf + 1024, 0, 128, LAYOUT_NONE));
+                const uint64_t a_desc = smem_desc(st, 16, 1024, LAYOUT_SW128);
+                const uint64_t b_desc = smem_desc(st + A_BYTES, 16, 1024, LAYOUT_SW128);
+#pragma unroll
+                for (uint32_t k = 0; k < BK / 32; ++k) {
+                    // +32 bytes along K inside the 128-byte swizzle span = +2 in the address field;
+                    // scale-factor byte k of each 32-bit TMEM column
+                    const uint32_t idesc = idesc_base | (k << 29) | (k << 4);
+                    mma_mxf8f6f4(tmem_base + ACC_COL, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_base + SFA_COL,
+                                 tmem_base + SFB_COL, (kt > 0 || k > 0) ? 1u : 0u);
+                }
+                mma_commit(empty_bar(s));                 // frees the stage once these MMAs have read it
+            }
+            __syncwarp();
+        }
+        if (lane == 0) mma_commit(accum_bar);             // accumulator complete (or unwinding)
+        __syncwarp();
+    } else {
+        // ---------------- epilogue: TMEM -> registers -> global ----------------
+        const bool ok = mbar_wait(accum_bar, 0, status, ST_EPILOGUE_TIMEOUT);
+        tc_fence_after();
+        const int q = warp & 3;                            // TMEM lane quadrant this warp may access
+        const int row = m_tile * BM + q * 32 + lane;
+        if (ok) {
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + ACC_COL + c * 32, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const int col0 = n_tile * BN + c * 32;
+                if (row >= M || col0 >= N) continue;
+                float v[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+                if (bias != nullptr) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if (col0 + i < N) {
+                            if constexpr (OUT_DT == MXQ_F32) v[i] += reinterpret_cast<const float*>(bias)[col0 + i];
+                            else if constexpr (OUT_DT == MXQ_BF16) v[i] += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[col0 + i]);
+                            else v[i] += __half2float(reinterpret_cast<const __half*>(bias)[col0 + i]);
+                        }
+                    }
+                }
+                const bool whole = (col0 + 32 <= N);
+                if constexpr (OUT_DT == MXQ_F32) {
+                    float* o = reinterpret_cast<float*>(out) + (size_t)row * N + col0;
+                    if (whole && (N % 4 == 0)) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                    } else {
+                        for (int i = 0; i < 32 && col0 + i < N; ++i) o[i] = v[i];
+                    }
+                } else {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        if constexpr (OUT_DT == MXQ_BF16) { const __nv_bfloat162 h = __floats2bfloat162_rn(v[i], v[i + 1]); pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h); }
+                        else { const __half2 h = __floats2half2_rn(v[i], v[i + 1]); pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h); }
+                    }
+                    uint16_t* o = reinterpret_cast<uint16_t*>(out) + (size_t)row * N + col0;
+                    if (whole && (N % 8 == 0)) {
+#pragma unroll
+                        for (int i = 0; i < 16; i += 4) *reinterpret_cast<uint4*>(o + 2 * i) = make_uint4(pk[i], pk[i + 1], pk[i + 2], pk[i + 3]);
+                    } else {
+                        for (int i = 0; i < 32 && col0 + i < N; ++i) o[i] = (uint16_t)(pk[i >> 1] >> (16 * (i & 1)));
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// operand packing: reference codes + scales -> hardware codes + scale chunks
+// ------------------------------------------------------------------------------------------------
+struct PackTables {
+    uint8_t plain[256];     // reference code -> hardware code of the same value
+    uint8_t halved[256];    // reference code -> hardware code of value / 2 (round half to even)
+    uint32_t bad[8];        // bit c set: reference code c has no hardware encoding (block is re-biased)
+};
+
+__global__ void __launch_bounds__(256) mx_pack_kernel(const uint8_t* __restrict__ scales, const uint8_t* __restrict__ elements,
+                                                     uint8_t* __restrict__ hw_codes, uint8_t* __restrict__ hw_sf,
+                                                     int64_t rows, int64_t K, int64_t sf_rows, PackTables t) {
+    __shared__ uint8_t s_plain[256], s_halved[256];
+    s_plain[threadIdx.x] = t.plain[threadIdx.x];
+    s_halved[threadIdx.x] = t.halved[threadIdx.x];
+    __syncthreads();
+    const int64_t kb_per_row = K / 32;
+    const int64_t kb_pad = ((K + 127) / 128) * 4;                  // K blocks per row in the chunked layout
+    const int64_t total = sf_rows * kb_pad;
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;      // one (row, K block) per thread, padding included
+    if (i >= total) return;
+    const int64_t r = i / kb_pad, kb = i % kb_pad;
+    const int64_t chunk = (r / 128) * (kb_pad / 4) + kb / 4;
+    uint8_t* sf_dst = hw_sf + chunk * 512 + ((r % 128) % 32) * 16 + ((r % 128) / 32) * 4 + (kb % 4);
+    if (r >= rows || kb >= kb_per_row) { *sf_dst = 127; return; }   // padding: scale 1.0 (the codes there are TMA zero fill)
+    const int64_t blk = r * kb_per_row + kb;
+    const uint4* src = reinterpret_cast<const uint4*>(elements + blk * 32);
+    uint4 c[2] = {src[0], src[1]};
+    const uint8_t* cb = reinterpret_cast<const uint8_t*>(c);
+    bool any_bad = false;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) any_bad |= (t.bad[cb[j] >> 5] >> (cb[j] & 31)) & 1u;
+    const uint8_t* lut = any_bad ? s_halved : s_plain;
+    uint4 o[2];
+    uint8_t* ob = reinterpret_cast<uint8_t*>(o);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) ob[j] = lut[cb[j]];
+    uint4* dst = reinterpret_cast<uint4*>(hw_codes + blk * 32);
+    dst[0] = o[0];
+    dst[1] = o[1];
+    const uint32_t s = scales[blk];
+    *sf_dst = (uint8_t)((any_bad && s < 255u) ? s + 1u : s);
+}
+
+// exact value -> OCP E4M3 / E5M2 byte (round half to even when the value is not representable)
+static uint8_t hw_encode(double v, int hw_fmt) {
+    const int eb = hw_fmt == 0 ? 4 : 5, fb = hw_fmt == 0 ? 3 : 2, bias = hw_fmt == 0 ? 7 : 15;
+    const uint8_t sign = std::signbit(v) ? 0x80 : 0;
+    double a = std::fabs(v);
+    if (a == 0.0) return sign;
+    int e;
+    std::frexp(a, &e);
+    e -= 1;                                                    // a = m * 2^e, m in [1,2)
+    int E = e + bias;
+    double scaled;                                             // value in units of the last mantissa bit
+    if (E <= 0) { scaled = std::ldexp(a, bias - 1 + fb); E = 0; }          // subnormal: units of 2^(1-bias-fb)
+    else scaled = std::ldexp(a, fb - e) - (1 << fb);                        // fraction field
+    double fl = std::floor(scaled), rem = scaled - fl;
+    int f = (int)fl;
+    if (rem > 0.5 || (rem == 0.5 && (f & 1))) ++f;
+    if (f == (1 << fb)) { f = 0; ++E; }
+    (void)eb;
+    return (uint8_t)(sign | (E << fb) | f);
+}
+
+static bool build_pack_tables(int eb, int fb, PackTables* t, int* hw_fmt) {
+    if (!((eb == 4 && fb == 3) || (eb == 5 && fb == 2) || (eb == 2 && fb == 3) || (eb == 3 && fb == 2) || (eb == 2 && fb == 1))) return false;
+    *hw_fmt = (eb == 5) ? 1 : 0;
+    const double hw_max = *hw_fmt == 0 ? 448.0 : 57344.0;
+    FmtRT f{eb, fb, 1, 0};
+    for (int i = 0; i < 8; ++i) t->bad[i] = 0;
+    for (int c = 0; c < 256; ++c) {
+        const int bits = eb + fb + 1;
+        // bits above the sign bit of the reference format are ignored by its decoder
+        const uint32_t code = (uint32_t)c & ((1u << bits) - 1u);
+        const double v = (double)bits_f32(decode_f32(code, f));
+        const bool bad = std::fabs(v) > hw_max;
+        if (bad) t->bad[c >> 5] |= 1u << (c & 31);
+        t->plain[c] = bad ? 0 : hw_encode(v, *hw_fmt);
+        t->halved[c] = hw_encode(v * 0.5, *hw_fmt);
+    }
+    return true;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+static bool make_operand_map(CUtensorMap* map, const void* codes, int64_t rows, int64_t K, int box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)K};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(codes), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int OUT_DT>
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const uint8_t* sfa, const uint8_t* sfb, void* out,
+                       const void* bias, int M, int N, int K, uint32_t idesc, int* status, cudaStream_t st) {
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] { attr_err = cudaFuncSetAttribute(mx_gemm_kernel<OUT_DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); });
+    if (attr_err != cudaSuccess) { set_last_cuda_error(attr_err); return MXQ_ELAUNCH; }
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    mx_gemm_kernel<OUT_DT><<<grid, THREADS, SMEM_BYTES, st>>>(ma, mb, sfa, sfb, out, bias, M, N, K, idesc, status);
+    return check_launch();
+}
+
+}  // namespace gemm
+}  // namespace mxq
+
+using namespace mxq;
+
+extern "C" int64_t mxq_mx_sf_bytes(int64_t rows, int64_t K) {
+    if (rows < 0 || K < 0) return MXQ_EINVAL;
+    // row tiles are padded to a multiple of two so a 256-wide N tile always finds both of its chunks
+    const int64_t row_tiles = ((rows + 255) / 256) * 2;
+    return row_tiles * ((K + 127) / 128) * 512;
+}
+
+extern "C" int mxq_mx_pack_operand(const uint8_t* scales, const uint8_t* elements, int64_t rows, int64_t K, int eb, int fb,
+                                   uint8_t* hw_codes, uint8_t* hw_sf, int* hw_format, void* stream) {
+    if (rows <= 0 || K <= 0 || K % 32 != 0 || !scales || !elements || !hw_codes || !hw_sf || !hw_format) return MXQ_EINVAL;
+    if ((reinterpret_cast<uintptr_t>(elements) | reinterpret_cast<uintptr_t>(hw_codes)) % 16 != 0) return MXQ_EINVAL;
+    gemm::PackTables t;
+    if (!gemm::build_pack_tables(eb, fb, &t, hw_format)) return MXQ_EINVAL;
+    const int64_t sf_rows = ((rows + 255) / 256) * 256;
+    const int64_t total = sf_rows * (((K + 127) / 128) * 4);
+    gemm::mx_pack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(scales, elements, hw_codes, hw_sf, rows, K, sf_rows, t);
+    return check_launch();
+}
+
+extern "C" int mxq_mx_gemm(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw_format, const uint8_t* b_codes,
+                           const uint8_t* b_sf, int b_hw_format, void* out, int out_dtype, const void* bias, int64_t M,
+                           int64_t N, int64_t K, int* status, void* stream) {
+    if (M <= 0 || N <= 0 || K <= 0 || K % 32 != 0 || M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return MXQ_EINVAL;
+    if (!a_codes || !a_sf || !b_codes || !b_sf || !out) return MXQ_EINVAL;
+    if ((a_hw_format | b_hw_format) & ~1) return MXQ_EINVAL;
+    if ((reinterpret_cast<uintptr_t>(a_codes) | reinterpret_cast<uintptr_t>(b_codes) | reinterpret_cast<uintptr_t>(a_sf) |
+         reinterpret_cast<uintptr_t>(b_sf) | reinterpret_cast<uintptr_t>(out)) % 16 != 0) return MXQ_EINVAL;
+    CUtensorMap ma, mb;
+    if (!gemm::make_operand_map(&ma, a_codes, M, K, gemm::BM) || !gemm::make_operand_map(&mb, b_codes, N, K, gemm::BN)) return MXQ_ELAUNCH;
+    // instruction descriptor: A/B formats, K-major operands, N >> 3, E8M0 scales, M >> 4
+    const uint32_t idesc = ((uint32_t)a_hw_format << 7) | ((uint32_t)b_hw_format << 10) | ((uint32_t)(gemm::BN >> 3) << 17) |
+                           (1u << 23) | ((uint32_t)(gemm::BM >> 4) << 24);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (out_dtype == MXQ_F32) return gemm::launch_gemm<MXQ_F32>(ma, mb, a_sf, b_sf, out, bias, (int)M, (int)N, (int)K, idesc, status, st);
+    if (out_dtype == MXQ_BF16) return gemm::launch_gemm<MXQ_BF16>(ma, mb, a_sf, b_sf, out, bias, (int)M, (int)N, (int)K, idesc, status, st);
+    if (out_dtype == MXQ_F16) return gemm::launch_gemm<MXQ_F16>(ma, mb, a_sf, b_sf, out, bias, (int)M, (int)N, (int)K, idesc, status, st);
+    return MXQ_EINVAL;
+}

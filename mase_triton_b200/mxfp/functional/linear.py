@@ -15,6 +15,7 @@ from torch import Tensor
 
 from ..._linear_common import check_backend, parse_layer_type
 from ..meta import MXFPMeta, MXFPTensorMeta
+from .. import gemm as _gemm
 from .cast import compose_mxfp_tensor, quantize_dequantize
 
 LayerType = Literal["XWB", "XWBq", "XWqB", "XWqBq", "XqWB", "XqWBq", "XqWqB", "XqWqBq"]
@@ -48,6 +49,14 @@ def mxfp_linear(
         bias = compose_mxfp_tensor(b_scales, b_elements, b_tensor_meta) if b is not None else None
     else:
         bias = b
+    if (backend == "fused" and kind.x_quantised and kind.w_quantised and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16, torch.float32)
+            and _gemm.supported(x_meta) and _gemm.supported(w_tensor_meta.meta) and w_tensor_meta.block_dim in (1, -1)
+            and len(w_tensor_meta.shape) == 2 and x.shape[-1] % 32 == 0 and x.numel() > 0):
+        # both operands stay quantised: block-scaled tensor-core GEMM, fp32 accumulation
+        wq = _gemm.packed_weight(w_scales, w_elements, w_tensor_meta.shape, w_tensor_meta.meta)
+        xq = _gemm.quantize_pack(x, x_meta)
+        out = _gemm.mx_gemm(xq, wq, x.dtype, bias)
+        return out.reshape(*x.shape[:-1], wq.rows)
     if kind.x_quantised:
         x = quantize_dequantize(x, block_dim=-1, mxfp_meta=x_meta)       # same bits as extract + compose
     weight = compose_mxfp_tensor(w_scales, w_elements, w_tensor_meta) if kind.w_quantised else w

@@ -1,0 +1,115 @@
+"""Host side of the block-scaled tensor-core GEMM (``csrc/mxq_gemm.cu``).
+
+``PackedOperand`` is an MXFP tensor re-encoded for the tensor cores: one hardware E4M3/E5M2 byte
+per element plus E8M0 scales in the chunked order the kernel's ``tcgen05.cp`` expects.  Weights
+are packed once and cached; activations are quantised and packed per call.  The reference has no
+counterpart: its ``backend="fused"`` raises ``NotImplementedError``
+(``src/mase_triton/mxfp/functional/linear.py:62-63``).
+"""
+
+from __future__ import annotations
+
+import ctypes
+from collections import OrderedDict
+from dataclasses import dataclass
+
+import torch
+from torch import Tensor
+
+from .. import _lib
+from . import kernels
+from .meta import MXFPMeta
+
+_STATUS: dict[torch.device, Tensor] = {}
+_STATUS_TEXT = {1: "TMA producer wait ran out", 2: "MMA issuer wait ran out", 3: "epilogue wait ran out"}
+
+
+@dataclass
+class PackedOperand:
+    codes: Tensor        # uint8 [rows, K], hardware element codes
+    sf: Tensor           # uint8, hardware scale-factor chunks
+    hw_format: int       # 0 = E4M3, 1 = E5M2
+    rows: int
+    K: int
+
+
+def supported(meta: MXFPMeta | None) -> bool:
+    """Formats the tensor-core path takes: 32-element blocks, is_finite element formats."""
+    return meta is not None and meta.block_size == 32 and meta.element_is_finite and meta.scale_exp_bits == 8
+
+
+def status_word(device: torch.device) -> Tensor:
+    """Device int32 the kernel writes a non-zero code into if one of its bounded waits runs out."""
+    device = torch.device(device)
+    if device not in _STATUS:
+        _STATUS[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _STATUS[device]
+
+
+def check_status(device: torch.device) -> None:
+    """Synchronising check of the status word (used by tests and debugging)."""
+    code = int(status_word(device).item())
+    if code != 0:
+        status_word(device).zero_()
+        raise _lib.MXQError(f"mx_gemm kernel reported: {_STATUS_TEXT.get(code, code)}")
+
+
+def pack_operand(scales: Tensor, elements: Tensor, rows: int, K: int, meta: MXFPMeta) -> PackedOperand:
+    """Reference ``(scales, elements)`` of a ``[rows, K]`` tensor blocked along K -> ``PackedOperand``."""
+    _lib.require_cuda(elements, "pack_operand")
+    assert supported(meta) and K % 32 == 0 and elements.numel() == rows * K and scales.numel() == rows * K // 32
+    scales, elements = scales.contiguous(), elements.contiguous()
+    L = _lib.load()
+    dev = elements.device
+    codes = torch.empty((rows, K), dtype=torch.uint8, device=dev)
+    sf = torch.empty((L.mxq_mx_sf_bytes(rows, K),), dtype=torch.uint8, device=dev)
+    fmt = ctypes.c_int(0)
+    with torch.cuda.device(dev):
+        rc = L.mxq_mx_pack_operand(scales.data_ptr(), elements.data_ptr(), rows, K, meta.element_exp_bits, meta.element_frac_bits,
+                                   codes.data_ptr(), sf.data_ptr(), ctypes.addressof(fmt), _lib.stream_ptr(dev))
+    _lib.check(rc, "mxq_mx_pack_operand")
+    return PackedOperand(codes, sf, fmt.value, rows, K)
+
+
+def quantize_pack(x: Tensor, meta: MXFPMeta) -> PackedOperand:
+    """Quantise a ``[..., K]`` activation along its last dim and pack it."""
+    K = x.shape[-1]
+    rows = x.numel() // K
+    scales, elements = kernels.extract_mxfp_components(x.reshape(-1), meta)
+    return pack_operand(scales, elements, rows, K, meta)
+
+
+_WEIGHT_CACHE: "OrderedDict[tuple, PackedOperand]" = OrderedDict()
+
+
+def packed_weight(w_scales: Tensor, w_elements: Tensor, shape: tuple[int, int], meta: MXFPMeta) -> PackedOperand:
+    """Packed form of a quantised weight, cached on the identity and version of its code tensors."""
+    key = (w_elements.data_ptr(), w_scales.data_ptr(), w_elements._version, w_scales._version, tuple(shape), meta, w_elements.device)
+    hit = _WEIGHT_CACHE.get(key)
+    if hit is None:
+        hit = pack_operand(w_scales, w_elements, shape[0], shape[1], meta)
+        _WEIGHT_CACHE[key] = hit
+        while len(_WEIGHT_CACHE) > 64:
+            _WEIGHT_CACHE.popitem(last=False)
+    else:
+        _WEIGHT_CACHE.move_to_end(key)
+    return hit
+
+
+def mx_gemm(a: PackedOperand, b: PackedOperand, out_dtype: torch.dtype, bias: Tensor | None = None,
+            out: Tensor | None = None) -> Tensor:
+    """``a [M,K] @ b[N,K]^T (+ bias)`` on the tensor cores; returns ``[M, N]`` of ``out_dtype``."""
+    assert a.K == b.K and out_dtype in _lib.DTYPE_ID
+    dev = a.codes.device
+    if out is None:
+        out = torch.empty((a.rows, b.rows), dtype=out_dtype, device=dev)
+    if bias is not None:
+        bias = bias.to(out_dtype).contiguous()
+        assert bias.numel() == b.rows
+    with torch.cuda.device(dev):
+        rc = _lib.load().mxq_mx_gemm(a.codes.data_ptr(), a.sf.data_ptr(), a.hw_format, b.codes.data_ptr(), b.sf.data_ptr(),
+                                     b.hw_format, out.data_ptr(), _lib.DTYPE_ID[out_dtype],
+                                     None if bias is None else bias.data_ptr(), a.rows, b.rows, a.K,
+                                     status_word(dev).data_ptr(), _lib.stream_ptr(dev))
+    _lib.check(rc, "mxq_mx_gemm")
+    return out

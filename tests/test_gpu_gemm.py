@@ -1,0 +1,105 @@
+"""The block-scaled tensor-core GEMM against "dequantise, then fp32 matmul" on the same operands."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import oracle
+from mase_triton_b200.mxfp import functional as MX
+from mase_triton_b200.mxfp import gemm as G
+from mase_triton_b200.mxfp import kernels as mxk
+from mase_triton_b200.mxfp.layers import MXFPLinearPTQ
+from mase_triton_b200.mxfp.meta import MXFP8_E4M3_fn, MXFP8_E5M2_fn, OCP_MXFP4_E2M1, OCP_MXFP6_E2M3, OCP_MXFP6_E3M2
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+ALL = [MXFP8_E4M3_fn, MXFP8_E5M2_fn, OCP_MXFP6_E2M3, OCP_MXFP6_E3M2, OCP_MXFP4_E2M1]
+
+
+def dequant(x: torch.Tensor, meta) -> torch.Tensor:
+    s, e = mxk.extract_mxfp_components(x.reshape(-1), meta)
+    return mxk.compose_mxfp_tensor(s, e, meta, torch.float32).reshape(x.shape)
+
+
+def within_tolerance(y: torch.Tensor, y32: torch.Tensor) -> bool:
+    """|y - y32| <= 2^-7 |y32| + 2^-7 rms(y32): one bf16 ulp plus accumulation-order slack."""
+    tol = 2.0**-7 * y32.abs() + 2.0**-7 * y32.pow(2).mean().sqrt()
+    return bool(((y.float() - y32).abs() <= tol).all())
+
+
+def test_pack_tables_preserve_values(lib):
+    """Packing then reading the hardware bytes back as OCP FP8 gives the reference values
+    (times 2 where a block was re-biased)."""
+    torch.manual_seed(3)
+    x = (torch.randn(256, 256, device=DEV) * 4).to(torch.bfloat16)
+    for meta in ALL:
+        s, e = mxk.extract_mxfp_components(x.reshape(-1), meta)
+        p = G.pack_operand(s, e, 256, 256, meta)
+        hw_dtype = torch.float8_e4m3fn if p.hw_format == 0 else torch.float8_e5m2
+        vals = p.codes.view(hw_dtype).float()
+        # un-chunk the scale factors: chunk (rt, kt) byte (r%32)*16 + (r/32)*4 + kb
+        sf = p.sf.view(-1, 2, 32, 4, 4)[:2]                  # [row tile, k tile, r%32, r/32, kb]
+        sf = sf.permute(0, 3, 2, 1, 4).reshape(256, 8)       # [row, k block]
+        scale = torch.exp2(sf.float() - 127).repeat_interleave(32, dim=1)
+        ref = dequant(x, meta)
+        # halving a re-biased block is exact except for elements 2^-14 (E4M3) below the block maximum
+        blockmax = ref.abs().reshape(256, 8, 32).amax(dim=2, keepdim=True).expand(256, 8, 32).reshape(256, 256)
+        assert bool(((vals * scale - ref).abs() <= blockmax * 2.0**-16).all()), meta.tag
+        assert not vals.isnan().any()
+        if meta in (OCP_MXFP6_E2M3, OCP_MXFP6_E3M2, OCP_MXFP4_E2M1):
+            assert torch.equal(vals * scale, ref), meta.tag
+
+
+@pytest.mark.parametrize("shape", [(128, 256, 128), (128, 256, 512), (256, 512, 1024), (200, 300, 160), (1, 8, 32), (384, 1024, 4096)])
+def test_gemm_e4m3_shapes(lib, shape):
+    M, N, K = shape
+    torch.manual_seed(M + N + K)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (0.05 * torch.randn(N, K, device=DEV)).to(torch.bfloat16)
+    a = G.quantize_pack(x, MXFP8_E4M3_fn)
+    b = G.quantize_pack(w, MXFP8_E4M3_fn)
+    y32 = dequant(x, MXFP8_E4M3_fn) @ dequant(w, MXFP8_E4M3_fn).t()
+    for dt in (torch.float32, torch.bfloat16, torch.float16):
+        y = G.mx_gemm(a, b, dt)
+        G.check_status(DEV)
+        assert y.shape == (M, N) and y.dtype == dt
+        assert within_tolerance(y, y32), f"{shape} {dt}: max err {(y.float() - y32).abs().max().item()}"
+    bias = torch.randn(N, device=DEV).to(torch.bfloat16)
+    yb = G.mx_gemm(a, b, torch.bfloat16, bias)
+    G.check_status(DEV)
+    assert within_tolerance(yb, y32 + bias.float())
+
+
+@pytest.mark.parametrize("x_meta", ALL, ids=lambda m: m.tag)
+@pytest.mark.parametrize("w_meta", ALL, ids=lambda m: m.tag)
+def test_gemm_format_pairs(lib, x_meta, w_meta):
+    torch.manual_seed(5)
+    M, N, K = 256, 512, 512
+    x = (torch.randn(M, K, device=DEV) * 3).to(torch.bfloat16)
+    w = (0.02 * torch.randn(N, K, device=DEV)).to(torch.bfloat16)
+    y = G.mx_gemm(G.quantize_pack(x, x_meta), G.quantize_pack(w, w_meta), torch.bfloat16)
+    G.check_status(DEV)
+    y32 = dequant(x, x_meta) @ dequant(w, w_meta).t()
+    assert within_tolerance(y, y32)
+
+
+def test_fused_linear_matches_separate(lib):
+    """Benchmark configuration 4 at reduced M: x bf16 ~ N(0,1), W ~ N(0, 0.02), MXFP8 E4M3 both."""
+    torch.manual_seed(0)
+    M, N, K = 1024, 14336, 4096
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    fc = torch.nn.Linear(K, N, bias=False, device=DEV, dtype=torch.bfloat16)
+    with torch.no_grad():
+        fc.weight.copy_((0.02 * torch.randn(N, K, device=DEV)).to(torch.bfloat16))
+    sep = MXFPLinearPTQ.from_linear(fc, MXFP8_E4M3_fn, MXFP8_E4M3_fn, None, "XqWqB", "separate")
+    fus = MXFPLinearPTQ.from_linear(fc, MXFP8_E4M3_fn, MXFP8_E4M3_fn, None, "XqWqB", "fused")
+    y_sep, y_fus = sep(x), fus(x)
+    G.check_status(DEV)
+    y32 = dequant(x, MXFP8_E4M3_fn) @ dequant(fc.weight.detach(), MXFP8_E4M3_fn).t()
+    assert within_tolerance(y_fus, y32)
+    rel = ((y_fus.float() - y_sep.float()).abs().mean() / y_sep.float().abs().mean()).item()
+    assert rel < 5e-3, rel
+    # 3-D activations keep their leading dims
+    y3 = fus(x.reshape(4, 256, K))
+    assert y3.shape == (4, 256, N) and torch.equal(y3.reshape(M, N), y_fus)
