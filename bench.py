@@ -251,7 +251,27 @@ def small_cases():
         out = torch.empty_like(x)
         return (lambda: mxk.quantize_dequantize(x, meta, x.dtype, out=out)), n * 2 * s_in
 
+    def gemm_case(M, N, K, which):
+        from mase_triton_b200.mxfp import gemm as G
+        from mase_triton_b200.mxfp.layers import MXFPLinearPTQ
+        g = torch.Generator().manual_seed(0)
+        x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(dev)
+        w = (0.02 * torch.randn(N, K, generator=g)).to(torch.bfloat16).to(dev)
+        flops = 2.0 * M * N * K
+        if which == "gemm":            # tensor-core kernel alone, operands already packed
+            a, b = G.quantize_pack(x, MXFP8_E4M3_fn), G.quantize_pack(w, MXFP8_E4M3_fn, G.OPERAND_B)
+            out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+            return (lambda: G.mx_gemm(a, b, torch.bfloat16, out=out)), flops
+        fc = torch.nn.Linear(K, N, bias=False, device=dev, dtype=torch.bfloat16)
+        with torch.no_grad():
+            fc.weight.copy_(w)
+        layer = MXFPLinearPTQ.from_linear(fc, MXFP8_E4M3_fn, MXFP8_E4M3_fn, None, "XqWqB", "fused" if which == "linear" else "separate")
+        return (lambda: layer(x)), flops
+
     cases = {"minifloat_qdq_f32": minifloat_qdq_f32}
+    for which in ("gemm", "linear", "separate"):
+        cases[f"mx_{which}_small"] = (lambda w=which: gemm_case(2048, 4096, 4096, w))
+        cases[f"mx_{which}_cfg4"] = (lambda w=which: gemm_case(8192, 14336, 4096, w))
     for which in ("extract", "compose", "qdq"):
         cases[f"mxfp8_{which}_f32"] = (lambda w=which: mx_case(synthetic.cfg1_mxfp8_fp32, (8192, 8192), MXFP8_E4M3_fn, 4, w))
         cases[f"mxfp4_{which}_bf16"] = (lambda w=which: mx_case(synthetic.cfg3_mxfp4_bf16, (8192, 8192), OCP_MXFP4_E2M1, 2, w))
@@ -269,6 +289,10 @@ def run_case(name: str, steps: int, warmup: int) -> None:
     ts = time_steps(fn, steps)
     t = statistics.median(ts)
     peak, kind = measured_peaks()
+    if name.startswith("mx_gemm") or name.startswith("mx_linear") or name.startswith("mx_separate"):
+        print(json.dumps({"case": name, "steps": steps, "median_ms": round(t, 5), "TFLOPs": round(nbytes / t / 1e9, 1),
+                          "frac_of_4500_nominal_mx": round(nbytes / t / 1e9 / 4500, 4)}), flush=True)
+        return
     print(json.dumps({"case": name, "steps": steps, "median_ms": round(t, 5), "GBps": round(nbytes / t / 1e6, 1),
                       "frac_of_peak": round(nbytes / t / 1e6 / peak, 4), "peak": peak, "peak_source": kind}), flush=True)
 

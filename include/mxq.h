@@ -106,25 +106,31 @@ int mxq_mxfp_qdq(const void* x, int x_dtype, void* out, int out_dtype, int64_t n
  * backend is a stub that raises NotImplementedError (linear.py:62-63).
  */
 
+/* operand roles of the GEMM: the scale-factor array is tiled to the CTA tile of its side */
+#define MXQ_OPERAND_A 0 /* left operand  [M, K]: 256-row scale tiles */
+#define MXQ_OPERAND_B 1 /* right operand [N, K]: 224-row scale tiles */
+
 /* Bytes of the hardware scale-factor array of an operand with `rows` rows and K columns. */
-int64_t mxq_mx_sf_bytes(int64_t rows, int64_t K);
+int64_t mxq_mx_sf_bytes(int64_t rows, int64_t K, int operand);
 
 /*
  * Re-encode an MXFP operand (reference scales [rows*K/32] and elements [rows*K], 32-element blocks
  * along K, as produced by mxq_mxfp_extract) for the tensor cores:
  *   hw_codes [rows*K]  : one OCP E4M3 byte per element (E5M2 when the element format is E5M2)
- *   hw_sf              : E8M0 scales in 512-byte chunks per (128 rows, 128 K), mxq_mx_sf_bytes() long
+ *   hw_sf              : E8M0 scales in 512-byte chunks per (128 rows, 128 K), mxq_mx_sf_bytes() long,
+ *                        tiled for `operand` (MXQ_OPERAND_A or MXQ_OPERAND_B)
  *   *hw_format (host)  : 0 = E4M3, 1 = E5M2
  * FP6/FP4 element values are exactly representable in E4M3. A block holding a value the hardware
  * format cannot encode (reference E4M3 480, reference E5M2 top binade) is stored with its scale
  * raised by one and its elements halved.
  */
 int mxq_mx_pack_operand(const uint8_t* scales, const uint8_t* elements, int64_t rows, int64_t K,
-                        int exp_bits, int frac_bits, uint8_t* hw_codes, uint8_t* hw_sf, int* hw_format,
-                        void* stream);
+                        int exp_bits, int frac_bits, int operand, uint8_t* hw_codes, uint8_t* hw_sf,
+                        int* hw_format, void* stream);
 
 /*
- * out[M,N] = A[M,K] * B[N,K]^T (+ bias[N]) on packed operands, fp32 accumulation in tensor memory.
+ * out[M,N] = A[M,K] * B[N,K]^T (+ bias[N]) on operands packed as MXQ_OPERAND_A / MXQ_OPERAND_B,
+ * fp32 accumulation in tensor memory.
  * out_dtype / bias dtype: MXQ_F32, MXQ_BF16 or MXQ_F16 (bias may be NULL). K % 32 == 0.
  * `status` (device int32, may be NULL, must be zero on entry) receives a non-zero code if a
  * bounded wait inside the kernel ran out; the output is then undefined.

@@ -3,20 +3,25 @@
 // Both operands are MXFP tensors with 32-element blocks along K.  The kernel feeds the 5th-gen
 // tensor cores directly with the quantised data:
 //   * operand codes (one byte per element, OCP E4M3 or E5M2 as the hardware reads them) are staged
-//     by TMA (cp.async.bulk.tensor, 128-byte swizzle) into a 4-stage shared-memory ring;
-//   * the E8M0 block scales of a 128 x 128(K) tile are one 512-byte chunk, brought in with a bulk copy
-//     and moved shared -> tensor memory with tcgen05.cp;
-//   * one elected thread issues tcgen05.mma.kind::mxf8f6f4.block_scale (M=128, N=256, K=32), four
-//     per K tile; the fp32 accumulator (128 lanes x 256 columns) lives in tensor memory;
-//   * four epilogue warps read it back with tcgen05.ld, add the bias, convert and store.
+//     by TMA (cp.async.bulk.tensor, 128-byte swizzle) into a shared-memory ring;
+//   * the E8M0 block scales of a (tile rows) x 128(K) slab are 512-byte chunks brought in with a
+//     bulk copy and moved shared -> tensor memory with tcgen05.cp;
+//   * one elected thread issues tcgen05.mma.kind::mxf8f6f4.block_scale (M=128, N=224, K=32); the
+//     fp32 accumulators (one or two 128-lane x 224-column blocks) live in tensor memory;
+//   * four epilogue warps read them back with tcgen05.ld, add the bias, convert and store.
+// The CTA tile is 256 x 224 (128 x 224 when M <= 128): two accumulators fill the 512 TMEM columns
+// and raise the flops per byte pulled from L2, which is what bounds this kernel.  CTAs are
+// persistent (one per SM, tiles dealt round-robin in an L2-friendly order): the TMA producer runs
+// ahead into the next tile while the epilogue drains tensor memory.
 // Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer (also owns the TMEM allocation),
 // warps 2..5 = epilogue.  Every wait on an mbarrier is bounded; a wait that runs out records a
 // code in the caller's status word and the CTA unwinds (TMEM is freed) instead of spinning.
 //
 // Operand layout in HBM (produced by the pack kernel in this file):
 //   codes : [rows, K] bytes, K contiguous
-//   sf    : [ceil(rows/128)][ceil(K/128)][512] bytes; inside a chunk the scale of row r (0..127) and
-//           K block b (0..3) sits at (r % 32) * 16 + (r / 32) * 4 + b  -- the order tcgen05.cp
+//   sf    : [ceil(rows/T)][ceil(K/128)][2][512] bytes, T = 256 for the A operand and 224 for B; chunk
+//           h holds tile-local rows 128h .. 128h+127; inside a chunk the scale of local row r and
+//           K block b (0..3) sits at (r % 32) * 16 + (r / 32) * 4 + b -- the order tcgen05.cp
 //           (32x128b.warpx4) expects.
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -34,18 +39,25 @@
 namespace mxq {
 namespace gemm {
 
-constexpr int BM = 128, BN = 256, BK = 128, STAGES = 4;
-constexpr int A_BYTES = BM * BK;                 // 16 KiB
-constexpr int B_BYTES = BN * BK;                 // 32 KiB
-constexpr int SFA_BYTES = 512, SFB_BYTES = 1024, SF_REGION = 2048;
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SF_REGION;         // 50 KiB, multiple of 1024
-constexpr int TX_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+constexpr int BN = 224, BK = 128;
+constexpr int A_TILE_ROWS = 256;                 // rows per scale-factor tile of the A operand
+constexpr int B_BYTES = BN * BK;                 // 28 KiB
+constexpr int SF_REGION = 2048;                  // A chunks (<= 1024) + B chunks (1024)
 constexpr int BAR_BYTES = 256;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + slack to align the ring to 1024
 constexpr int TMEM_COLS = 512;
-constexpr int ACC_COL = 0, SFA_COL = 256, SFB_COL = 260;
+constexpr int SFA_COL = 448, SFB_COL = 456;      // accumulators occupy columns [0, 448)
 constexpr int THREADS = 192;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
+constexpr int GROUP_M = 8;                       // tiles are dealt in groups of 8 row tiles x all column tiles
+
+template <int MH> struct Cfg {
+    static constexpr int BM = 128 * MH;
+    static constexpr int A_BYTES = BM * BK;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SF_REGION;       // multiple of 1024
+    static constexpr int STAGES = MH == 2 ? 3 : 4;
+    static constexpr int TX_BYTES = A_BYTES + B_BYTES + MH * 512 + 1024;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;   // + slack to align the ring
+};
 
 // status codes written to the caller's status word when a bounded wait runs out
 enum : int { ST_OK = 0, ST_PRODUCER_TIMEOUT = 1, ST_MMA_TIMEOUT = 2, ST_EPILOGUE_TIMEOUT = 3 };
@@ -124,28 +136,92 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 
-template <int OUT_DT>   // MXQ_F32 / MXQ_BF16 / MXQ_F16
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// tile index -> (row tile, column tile): groups of GROUP_M row tiles sweep all column tiles, so the
+// CTAs running at the same time share a few A tiles and re-use B tiles out of L2
+__device__ __forceinline__ void tile_coords(int t, int MT, int NT, int& mt, int& nt) {
+    const int per_group = GROUP_M * NT;
+    const int g = t / per_group, r = t % per_group;
+    const int gm = min(GROUP_M, MT - g * GROUP_M);
+    mt = g * GROUP_M + r % gm;
+    nt = r / gm;
+}
+
+template <int OUT_DT>
+__device__ __forceinline__ void store_chunk(void* __restrict__ out, const void* __restrict__ bias, const uint32_t (&r)[32],
+                                            int row, int col0, int M, int N) {
+    if (row >= M || col0 >= N) return;
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+    const bool whole = (col0 + 32 <= N);
+    if (bias != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            if (whole || col0 + i < N) {
+                if constexpr (OUT_DT == MXQ_F32) v[i] += reinterpret_cast<const float*>(bias)[col0 + i];
+                else if constexpr (OUT_DT == MXQ_BF16) v[i] += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[col0 + i]);
+                else v[i] += __half2float(reinterpret_cast<const __half*>(bias)[col0 + i]);
+            }
+        }
+    }
+    if constexpr (OUT_DT == MXQ_F32) {
+        float* o = reinterpret_cast<float*>(out) + (size_t)row * N + col0;
+        if (whole && (N % 4 == 0)) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) if (col0 + i < N) o[i] = v[i];
+        }
+    } else {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+            if constexpr (OUT_DT == MXQ_BF16) { const __nv_bfloat162 h = __floats2bfloat162_rn(v[i], v[i + 1]); pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h); }
+            else { const __half2 h = __floats2half2_rn(v[i], v[i + 1]); pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h); }
+        }
+        uint16_t* o = reinterpret_cast<uint16_t*>(out) + (size_t)row * N + col0;
+        if (whole && (N % 8 == 0)) {
+#pragma unroll
+            for (int i = 0; i < 16; i += 4) *reinterpret_cast<uint4*>(o + 2 * i) = make_uint4(pk[i], pk[i + 1], pk[i + 2], pk[i + 3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) if (col0 + i < N) o[i] = (uint16_t)(pk[i >> 1] >> (16 * (i & 1)));
+        }
+    }
+}
+
+template <int OUT_DT, int MH>   // OUT_DT: MXQ_F32 / MXQ_BF16 / MXQ_F16; MH: 128-row accumulators per CTA tile
 __global__ void __launch_bounds__(THREADS, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, void* __restrict__ out,
                const void* __restrict__ bias, int M, int N, int K, uint32_t idesc_base, int* status) {
+    using C = Cfg<MH>;
+    constexpr int STAGES = C::STAGES;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t ring = (raw + 1023u) & ~1023u;                    // 1024-aligned operand ring
     uint8_t* ring_ptr = smem_raw + (ring - raw);
-    const uint32_t bars = ring + STAGES * STAGE_BYTES;               // full[S], empty[S], accum, tmem slot
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ring_ptr + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 1));
+    const uint32_t bars = ring + STAGES * C::STAGE_BYTES;            // full[S], empty[S], accum_full, tmem_empty, tmem slot
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ring_ptr + STAGES * C::STAGE_BYTES + 8 * (2 * STAGES + 2));
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
     const uint32_t accum_bar = bars + 8u * (2 * STAGES);
+    const uint32_t tmem_empty_bar = bars + 8u * (2 * STAGES + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_tile = blockIdx.x, m_tile = blockIdx.y;
     const int KT = (K + BK - 1) / BK;
+    const int MT = (M + C::BM - 1) / C::BM, NT = (N + BN - 1) / BN;
+    const int num_tiles = MT * NT;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         mbar_init(accum_bar, 1);
+        mbar_init(tmem_empty_bar, 4);                                // one arrival per epilogue warp
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -160,102 +236,93 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
-        const uint8_t* sfa_tile = sfa + (size_t)m_tile * KT * 512;
-        const uint8_t* sfb_tile0 = sfb + (size_t)(2 * n_tile) * KT * 512;
-        const uint8_t* sfb_tile1 = sfb + (size_t)(2 * n_tile + 1) * KT * 512;
         bool ok = true;
-        for (int kt = 0; kt < KT && ok; ++kt) {
-            const int s = kt % STAGES;
-            if (kt >= STAGES) ok = mbar_wait(empty_bar(s), ((kt / STAGES) & 1) ^ 1, status, ST_PRODUCER_TIMEOUT);
-            if (ok && lane == 0) {
-                const uint32_t st = ring + s * STAGE_BYTES;
-                mbar_expect_tx(full_bar(s), TX_BYTES);
-                tma_load_2d(st, &map_a, kt * BK, m_tile * BM, full_bar(s));
-                tma_load_2d(st + A_BYTES, &map_b, kt * BK, n_tile * BN, full_bar(s));
-                bulk_load(st + A_BYTES + B_BYTES, sfa_tile + (size_t)kt * 512, 512, full_bar(s));
-                bulk_load(st + A_BYTES + B_BYTES + 512, sfb_tile0 + (size_t)kt * 512, 512, full_bar(s));
-                bulk_load(st + A_BYTES + B_BYTES + 1024, sfb_tile1 + (size_t)kt * 512, 512, full_bar(s));
+        uint32_t it = 0;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            int mt, nt;
+            tile_coords(tile, MT, NT, mt, nt);
+            // A scale tiles are 256 rows (2 chunks); a 128-row CTA tile uses one of the two chunks
+            const uint8_t* sfa_tile = (MH == 2) ? sfa + (size_t)mt * KT * 1024 : sfa + (size_t)(mt >> 1) * KT * 1024 + (mt & 1) * 512;
+            const uint8_t* sfb_tile = sfb + (size_t)nt * KT * 1024;
+            for (int kt = 0; kt < KT && ok; ++kt, ++it) {
+                const int s = it % STAGES;
+                if (it >= STAGES) ok = mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, status, ST_PRODUCER_TIMEOUT);
+                if (ok && lane == 0) {
+                    const uint32_t st = ring + s * C::STAGE_BYTES;
+                    mbar_expect_tx(full_bar(s), C::TX_BYTES);
+                    tma_load_2d(st, &map_a, kt * BK, mt * C::BM, full_bar(s));
+                    tma_load_2d(st + C::A_BYTES, &map_b, kt * BK, nt * BN, full_bar(s));
+                    bulk_load(st + C::A_BYTES + B_BYTES, sfa_tile + (size_t)kt * 1024, MH * 512, full_bar(s));
+                    bulk_load(st + C::A_BYTES + B_BYTES + 1024, sfb_tile + (size_t)kt * 1024, 1024, full_bar(s));
+                }
+                __syncwarp();
             }
-            __syncwarp();
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         bool ok = true;
-        for (int kt = 0; kt < KT && ok; ++kt) {
-            const int s = kt % STAGES;
-            ok = mbar_wait(full_bar(s), (kt / STAGES) & 1, status, ST_MMA_TIMEOUT);
+        uint32_t it = 0, tcount = 0;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+            // the epilogue must have drained the accumulators of the previous tile
+            if (tcount > 0) ok = mbar_wait(tmem_empty_bar, (tcount - 1) & 1, status, ST_MMA_TIMEOUT);
             tc_fence_after();
-            if (ok && lane == 0) {
-                const uint32_t st = ring + s * STAGE_BYTES;
-                const uint32_t sf = st + A_BYTES + B_BYTES;
-                tmem_cp_32x128b(tmem_base + SFA_COL, smem_desc(sf, 0, 128, LAYOUT_NONE));
-                tmem_cp_32x128b(tmem_base + SFB_COL, smem_desc(sf + 512, 0, 128, LAYOUT_NONE));
-                tmem_cp_32x128b(tmem_base + SFB_COL + 4, smem_desc(sf + 1024, 0, 128, LAYOUT_NONE));
-                const uint64_t a_desc = smem_desc(st, 16, 1024, LAYOUT_SW128);
-                const uint64_t b_desc = smem_desc(st + A_BYTES, 16, 1024, LAYOUT_SW128);
+            for (int kt = 0; kt < KT && ok; ++kt, ++it) {
+                const int s = it % STAGES;
+                ok = mbar_wait(full_bar(s), (it / STAGES) & 1, status, ST_MMA_TIMEOUT);
+                tc_fence_after();
+                if (ok && lane == 0) {
+                    const uint32_t st = ring + s * C::STAGE_BYTES;
+                    const uint32_t sf = st + C::A_BYTES + B_BYTES;
 #pragma unroll
-                for (uint32_t k = 0; k < BK / 32; ++k) {
-                    // +32 bytes along K inside the 128-byte swizzle span = +2 in the address field;
-                    // scale-factor byte k of each 32-bit TMEM column
-                    const uint32_t idesc = idesc_base | (k << 29) | (k << 4);
-                    mma_mxf8f6f4(tmem_base + ACC_COL, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_base + SFA_COL,
-                                 tmem_base + SFB_COL, (kt > 0 || k > 0) ? 1u : 0u);
-                }
-                mma_commit(empty_bar(s));                 // frees the stage once these MMAs have read it
-            }
-            __syncwarp();
-        }
-        if (lane == 0) mma_commit(accum_bar);             // accumulator complete (or unwinding)
-        __syncwarp();
-    } else {
-        // ---------------- epilogue: TMEM -> registers -> global ----------------
-        const bool ok = mbar_wait(accum_bar, 0, status, ST_EPILOGUE_TIMEOUT);
-        tc_fence_after();
-        const int q = warp & 3;                            // TMEM lane quadrant this warp may access
-        const int row = m_tile * BM + q * 32 + lane;
-        if (ok) {
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + ACC_COL + c * 32, r);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                const int col0 = n_tile * BN + c * 32;
-                if (row >= M || col0 >= N) continue;
-                float v[32];
+                    for (int h = 0; h < MH; ++h) tmem_cp_32x128b(tmem_base + SFA_COL + 4 * h, smem_desc(sf + 512 * h, 0, 128, LAYOUT_NONE));
+                    tmem_cp_32x128b(tmem_base + SFB_COL, smem_desc(sf + 1024, 0, 128, LAYOUT_NONE));
+                    tmem_cp_32x128b(tmem_base + SFB_COL + 4, smem_desc(sf + 1536, 0, 128, LAYOUT_NONE));
+                    const uint64_t b_desc = smem_desc(st + C::A_BYTES, 16, 1024, LAYOUT_SW128);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-                if (bias != nullptr) {
+                    for (uint32_t k = 0; k < BK / 32; ++k) {
+                        // +32 bytes along K inside the 128-byte swizzle span = +2 in the address field;
+                        // scale-factor byte k of each 32-bit TMEM column
+                        const uint32_t idesc = idesc_base | (k << 29) | (k << 4);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        if (col0 + i < N) {
-                            if constexpr (OUT_DT == MXQ_F32) v[i] += reinterpret_cast<const float*>(bias)[col0 + i];
-                            else if constexpr (OUT_DT == MXQ_BF16) v[i] += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[col0 + i]);
-                            else v[i] += __half2float(reinterpret_cast<const __half*>(bias)[col0 + i]);
+                        for (int h = 0; h < MH; ++h) {
+                            const uint64_t a_desc = smem_desc(st + h * 16384, 16, 1024, LAYOUT_SW128);
+                            mma_mxf8f6f4(tmem_base + h * BN, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_base + SFA_COL + 4 * h,
+                                         tmem_base + SFB_COL, (kt > 0 || k > 0) ? 1u : 0u);
                         }
                     }
+                    mma_commit(empty_bar(s));             // frees the stage once these MMAs have read it
                 }
-                const bool whole = (col0 + 32 <= N);
-                if constexpr (OUT_DT == MXQ_F32) {
-                    float* o = reinterpret_cast<float*>(out) + (size_t)row * N + col0;
-                    if (whole && (N % 4 == 0)) {
+                __syncwarp();
+            }
+            if (lane == 0) mma_commit(accum_bar);         // accumulators of this tile complete (or unwinding)
+            __syncwarp();
+        }
+    } else {
+        // ---------------- epilogue: TMEM -> registers -> global ----------------
+        const int q = warp & 3;                            // TMEM lane quadrant this warp may access
+        bool ok = true;
+        uint32_t tcount = 0;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+            int mt, nt;
+            tile_coords(tile, MT, NT, mt, nt);
+            ok = mbar_wait(accum_bar, tcount & 1, status, ST_EPILOGUE_TIMEOUT);
+            tc_fence_after();
+            if (!ok) break;
 #pragma unroll
-                        for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-                    } else {
-                        for (int i = 0; i < 32 && col0 + i < N; ++i) o[i] = v[i];
+            for (int h = 0; h < MH; ++h) {
+                const int row = mt * C::BM + h * 128 + q * 32 + lane;
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + h * BN + c * 32, r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (h == MH - 1 && c == BN / 32 - 1) {
+                        // last read of this tile's accumulators: hand tensor memory back to the MMA warp
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(tmem_empty_bar);
                     }
-                } else {
-                    uint32_t pk[16];
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        if constexpr (OUT_DT == MXQ_BF16) { const __nv_bfloat162 h = __floats2bfloat162_rn(v[i], v[i + 1]); pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h); }
-                        else { const __half2 h = __floats2half2_rn(v[i], v[i + 1]); pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h); }
-                    }
-                    uint16_t* o = reinterpret_cast<uint16_t*>(out) + (size_t)row * N + col0;
-                    if (whole && (N % 8 == 0)) {
-#pragma unroll
-                        for (int i = 0; i < 16; i += 4) *reinterpret_cast<uint4*>(o + 2 * i) = make_uint4(pk[i], pk[i + 1], pk[i + 2], pk[i + 3]);
-                    } else {
-                        for (int i = 0; i < 32 && col0 + i < N; ++i) o[i] = (uint16_t)(pk[i >> 1] >> (16 * (i & 1)));
-                    }
+                    store_chunk<OUT_DT>(out, bias, r, row, nt * BN + c * 32, M, N);
                 }
             }
         }
@@ -279,20 +346,25 @@ struct PackTables {
 
 __global__ void __launch_bounds__(256) mx_pack_kernel(const uint8_t* __restrict__ scales, const uint8_t* __restrict__ elements,
                                                      uint8_t* __restrict__ hw_codes, uint8_t* __restrict__ hw_sf,
-                                                     int64_t rows, int64_t K, int64_t sf_rows, PackTables t) {
+                                                     int64_t rows, int64_t K, int tile_rows, PackTables t) {
     __shared__ uint8_t s_plain[256], s_halved[256];
     s_plain[threadIdx.x] = t.plain[threadIdx.x];
     s_halved[threadIdx.x] = t.halved[threadIdx.x];
     __syncthreads();
     const int64_t kb_per_row = K / 32;
-    const int64_t kb_pad = ((K + 127) / 128) * 4;                  // K blocks per row in the chunked layout
-    const int64_t total = sf_rows * kb_pad;
-    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;      // one (row, K block) per thread, padding included
+    const int64_t KT = (K + 127) / 128;
+    const int64_t n_tiles = (rows + tile_rows - 1) / tile_rows;
+    // one (tile, chunk-local row, K block) per thread, padding included: every byte of hw_sf is written
+    const int64_t total = n_tiles * 256 * KT * 4;
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
     if (i >= total) return;
-    const int64_t r = i / kb_pad, kb = i % kb_pad;
-    const int64_t chunk = (r / 128) * (kb_pad / 4) + kb / 4;
-    uint8_t* sf_dst = hw_sf + chunk * 512 + ((r % 128) % 32) * 16 + ((r % 128) / 32) * 4 + (kb % 4);
-    if (r >= rows || kb >= kb_per_row) { *sf_dst = 127; return; }   // padding: scale 1.0 (the codes there are TMA zero fill)
+    const int64_t kb = i % (KT * 4);
+    const int64_t lr = (i / (KT * 4)) % 256;          // tile-local row 0..255 (rows >= tile_rows are padding)
+    const int64_t tile = i / (KT * 4 * 256);
+    const int64_t r = tile * tile_rows + lr;
+    const int64_t in_chunk = lr % 128;
+    uint8_t* sf_dst = hw_sf + ((tile * KT + kb / 4) * 2 + lr / 128) * 512 + (in_chunk % 32) * 16 + (in_chunk / 32) * 4 + (kb % 4);
+    if (lr >= tile_rows || r >= rows || kb >= kb_per_row) { *sf_dst = 127; return; }   // padding: scale 1.0 (codes there are TMA zero fill)
     const int64_t blk = r * kb_per_row + kb;
     const uint4* src = reinterpret_cast<const uint4*>(elements + blk * 32);
     uint4 c[2] = {src[0], src[1]};
@@ -379,16 +451,38 @@ static bool make_operand_map(CUtensorMap* map, const void* codes, int64_t rows, 
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int OUT_DT>
-static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const uint8_t* sfa, const uint8_t* sfb, void* out,
+static int sm_count() {
+    static int n = 0;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    });
+    return n;
+}
+
+template <int OUT_DT, int MH>
+static int launch_gemm(const uint8_t* a_codes, const uint8_t* b_codes, const uint8_t* sfa, const uint8_t* sfb, void* out,
                        const void* bias, int M, int N, int K, uint32_t idesc, int* status, cudaStream_t st) {
+    using C = Cfg<MH>;
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] { attr_err = cudaFuncSetAttribute(mx_gemm_kernel<OUT_DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); });
+    std::call_once(once, [] { attr_err = cudaFuncSetAttribute(mx_gemm_kernel<OUT_DT, MH>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES); });
     if (attr_err != cudaSuccess) { set_last_cuda_error(attr_err); return MXQ_ELAUNCH; }
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    mx_gemm_kernel<OUT_DT><<<grid, THREADS, SMEM_BYTES, st>>>(ma, mb, sfa, sfb, out, bias, M, N, K, idesc, status);
+    CUtensorMap ma, mb;
+    if (!make_operand_map(&ma, a_codes, M, K, C::BM) || !make_operand_map(&mb, b_codes, N, K, BN)) return MXQ_ELAUNCH;
+    const int tiles = ((M + C::BM - 1) / C::BM) * ((N + BN - 1) / BN);
+    const int grid = tiles < sm_count() ? tiles : sm_count();          // persistent: one CTA per SM
+    mx_gemm_kernel<OUT_DT, MH><<<grid, THREADS, C::SMEM_BYTES, st>>>(ma, mb, sfa, sfb, out, bias, M, N, K, idesc, status);
     return check_launch();
+}
+
+template <int OUT_DT>
+static int launch_gemm_dt(const uint8_t* a_codes, const uint8_t* b_codes, const uint8_t* sfa, const uint8_t* sfb, void* out,
+                          const void* bias, int M, int N, int K, uint32_t idesc, int* status, cudaStream_t st) {
+    if (M <= 128) return launch_gemm<OUT_DT, 1>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, idesc, status, st);
+    return launch_gemm<OUT_DT, 2>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, idesc, status, st);
 }
 
 }  // namespace gemm
@@ -396,22 +490,23 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const uint8
 
 using namespace mxq;
 
-extern "C" int64_t mxq_mx_sf_bytes(int64_t rows, int64_t K) {
-    if (rows < 0 || K < 0) return MXQ_EINVAL;
-    // row tiles are padded to a multiple of two so a 256-wide N tile always finds both of its chunks
-    const int64_t row_tiles = ((rows + 255) / 256) * 2;
-    return row_tiles * ((K + 127) / 128) * 512;
+static int sf_tile_rows(int operand) { return operand == 0 ? gemm::A_TILE_ROWS : gemm::BN; }
+
+extern "C" int64_t mxq_mx_sf_bytes(int64_t rows, int64_t K, int operand) {
+    if (rows < 0 || K < 0 || (operand & ~1)) return MXQ_EINVAL;
+    const int64_t t = sf_tile_rows(operand);
+    return ((rows + t - 1) / t) * ((K + 127) / 128) * 1024;
 }
 
 extern "C" int mxq_mx_pack_operand(const uint8_t* scales, const uint8_t* elements, int64_t rows, int64_t K, int eb, int fb,
-                                   uint8_t* hw_codes, uint8_t* hw_sf, int* hw_format, void* stream) {
-    if (rows <= 0 || K <= 0 || K % 32 != 0 || !scales || !elements || !hw_codes || !hw_sf || !hw_format) return MXQ_EINVAL;
+                                   int operand, uint8_t* hw_codes, uint8_t* hw_sf, int* hw_format, void* stream) {
+    if (rows <= 0 || K <= 0 || K % 32 != 0 || (operand & ~1) || !scales || !elements || !hw_codes || !hw_sf || !hw_format) return MXQ_EINVAL;
     if ((reinterpret_cast<uintptr_t>(elements) | reinterpret_cast<uintptr_t>(hw_codes)) % 16 != 0) return MXQ_EINVAL;
     gemm::PackTables t;
     if (!gemm::build_pack_tables(eb, fb, &t, hw_format)) return MXQ_EINVAL;
-    const int64_t sf_rows = ((rows + 255) / 256) * 256;
-    const int64_t total = sf_rows * (((K + 127) / 128) * 4);
-    gemm::mx_pack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(scales, elements, hw_codes, hw_sf, rows, K, sf_rows, t);
+    const int tile = sf_tile_rows(operand);
+    const int64_t total = ((rows + tile - 1) / tile) * 256 * (((K + 127) / 128) * 4);
+    gemm::mx_pack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(scales, elements, hw_codes, hw_sf, rows, K, tile, t);
     return check_launch();
 }
 
@@ -423,14 +518,12 @@ extern "C" int mxq_mx_gemm(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw
     if ((a_hw_format | b_hw_format) & ~1) return MXQ_EINVAL;
     if ((reinterpret_cast<uintptr_t>(a_codes) | reinterpret_cast<uintptr_t>(b_codes) | reinterpret_cast<uintptr_t>(a_sf) |
          reinterpret_cast<uintptr_t>(b_sf) | reinterpret_cast<uintptr_t>(out)) % 16 != 0) return MXQ_EINVAL;
-    CUtensorMap ma, mb;
-    if (!gemm::make_operand_map(&ma, a_codes, M, K, gemm::BM) || !gemm::make_operand_map(&mb, b_codes, N, K, gemm::BN)) return MXQ_ELAUNCH;
     // instruction descriptor: A/B formats, K-major operands, N >> 3, E8M0 scales, M >> 4
     const uint32_t idesc = ((uint32_t)a_hw_format << 7) | ((uint32_t)b_hw_format << 10) | ((uint32_t)(gemm::BN >> 3) << 17) |
-                           (1u << 23) | ((uint32_t)(gemm::BM >> 4) << 24);
+                           (1u << 23) | ((uint32_t)(128 >> 4) << 24);
     cudaStream_t st = (cudaStream_t)stream;
-    if (out_dtype == MXQ_F32) return gemm::launch_gemm<MXQ_F32>(ma, mb, a_sf, b_sf, out, bias, (int)M, (int)N, (int)K, idesc, status, st);
-    if (out_dtype == MXQ_BF16) return gemm::launch_gemm<MXQ_BF16>(ma, mb, a_sf, b_sf, out, bias, (int)M, (int)N, (int)K, idesc, status, st);
-    if (out_dtype == MXQ_F16) return gemm::launch_gemm<MXQ_F16>(ma, mb, a_sf, b_sf, out, bias, (int)M, (int)N, (int)K, idesc, status, st);
+    if (out_dtype == MXQ_F32) return gemm::launch_gemm_dt<MXQ_F32>(a_codes, b_codes, a_sf, b_sf, out, bias, (int)M, (int)N, (int)K, idesc, status, st);
+    if (out_dtype == MXQ_BF16) return gemm::launch_gemm_dt<MXQ_BF16>(a_codes, b_codes, a_sf, b_sf, out, bias, (int)M, (int)N, (int)K, idesc, status, st);
+    if (out_dtype == MXQ_F16) return gemm::launch_gemm_dt<MXQ_F16>(a_codes, b_codes, a_sf, b_sf, out, bias, (int)M, (int)N, (int)K, idesc, status, st);
     return MXQ_EINVAL;
 }

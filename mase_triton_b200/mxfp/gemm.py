@@ -31,6 +31,7 @@ class PackedOperand:
     hw_format: int       # 0 = E4M3, 1 = E5M2
     rows: int
     K: int
+    operand: int         # 0: packed as the left operand (A), 1: as the right operand (B)
 
 
 def supported(meta: MXFPMeta | None) -> bool:
@@ -54,29 +55,33 @@ def check_status(device: torch.device) -> None:
         raise _lib.MXQError(f"mx_gemm kernel reported: {_STATUS_TEXT.get(code, code)}")
 
 
-def pack_operand(scales: Tensor, elements: Tensor, rows: int, K: int, meta: MXFPMeta) -> PackedOperand:
-    """Reference ``(scales, elements)`` of a ``[rows, K]`` tensor blocked along K -> ``PackedOperand``."""
+OPERAND_A, OPERAND_B = 0, 1
+
+
+def pack_operand(scales: Tensor, elements: Tensor, rows: int, K: int, meta: MXFPMeta, operand: int) -> PackedOperand:
+    """Reference ``(scales, elements)`` of a ``[rows, K]`` tensor blocked along K -> ``PackedOperand``
+    laid out for the left (``OPERAND_A``) or right (``OPERAND_B``) side of the GEMM."""
     _lib.require_cuda(elements, "pack_operand")
     assert supported(meta) and K % 32 == 0 and elements.numel() == rows * K and scales.numel() == rows * K // 32
     scales, elements = scales.contiguous(), elements.contiguous()
     L = _lib.load()
     dev = elements.device
     codes = torch.empty((rows, K), dtype=torch.uint8, device=dev)
-    sf = torch.empty((L.mxq_mx_sf_bytes(rows, K),), dtype=torch.uint8, device=dev)
+    sf = torch.empty((L.mxq_mx_sf_bytes(rows, K, operand),), dtype=torch.uint8, device=dev)
     fmt = ctypes.c_int(0)
     with torch.cuda.device(dev):
         rc = L.mxq_mx_pack_operand(scales.data_ptr(), elements.data_ptr(), rows, K, meta.element_exp_bits, meta.element_frac_bits,
-                                   codes.data_ptr(), sf.data_ptr(), ctypes.addressof(fmt), _lib.stream_ptr(dev))
+                                   operand, codes.data_ptr(), sf.data_ptr(), ctypes.addressof(fmt), _lib.stream_ptr(dev))
     _lib.check(rc, "mxq_mx_pack_operand")
-    return PackedOperand(codes, sf, fmt.value, rows, K)
+    return PackedOperand(codes, sf, fmt.value, rows, K, operand)
 
 
-def quantize_pack(x: Tensor, meta: MXFPMeta) -> PackedOperand:
-    """Quantise a ``[..., K]`` activation along its last dim and pack it."""
+def quantize_pack(x: Tensor, meta: MXFPMeta, operand: int = OPERAND_A) -> PackedOperand:
+    """Quantise a ``[..., K]`` tensor along its last dim and pack it."""
     K = x.shape[-1]
     rows = x.numel() // K
     scales, elements = kernels.extract_mxfp_components(x.reshape(-1), meta)
-    return pack_operand(scales, elements, rows, K, meta)
+    return pack_operand(scales, elements, rows, K, meta, operand)
 
 
 _WEIGHT_CACHE: "OrderedDict[tuple, PackedOperand]" = OrderedDict()
@@ -87,7 +92,7 @@ def packed_weight(w_scales: Tensor, w_elements: Tensor, shape: tuple[int, int], 
     key = (w_elements.data_ptr(), w_scales.data_ptr(), w_elements._version, w_scales._version, tuple(shape), meta, w_elements.device)
     hit = _WEIGHT_CACHE.get(key)
     if hit is None:
-        hit = pack_operand(w_scales, w_elements, shape[0], shape[1], meta)
+        hit = pack_operand(w_scales, w_elements, shape[0], shape[1], meta, OPERAND_B)
         _WEIGHT_CACHE[key] = hit
         while len(_WEIGHT_CACHE) > 64:
             _WEIGHT_CACHE.popitem(last=False)
@@ -99,7 +104,7 @@ def packed_weight(w_scales: Tensor, w_elements: Tensor, shape: tuple[int, int], 
 def mx_gemm(a: PackedOperand, b: PackedOperand, out_dtype: torch.dtype, bias: Tensor | None = None,
             out: Tensor | None = None) -> Tensor:
     """``a [M,K] @ b[N,K]^T (+ bias)`` on the tensor cores; returns ``[M, N]`` of ``out_dtype``."""
-    assert a.K == b.K and out_dtype in _lib.DTYPE_ID
+    assert a.K == b.K and out_dtype in _lib.DTYPE_ID and a.operand == OPERAND_A and b.operand == OPERAND_B
     dev = a.codes.device
     if out is None:
         out = torch.empty((a.rows, b.rows), dtype=out_dtype, device=dev)

@@ -35,12 +35,12 @@ def test_pack_tables_preserve_values(lib):
     x = (torch.randn(256, 256, device=DEV) * 4).to(torch.bfloat16)
     for meta in ALL:
         s, e = mxk.extract_mxfp_components(x.reshape(-1), meta)
-        p = G.pack_operand(s, e, 256, 256, meta)
+        p = G.pack_operand(s, e, 256, 256, meta, G.OPERAND_A)
         hw_dtype = torch.float8_e4m3fn if p.hw_format == 0 else torch.float8_e5m2
         vals = p.codes.view(hw_dtype).float()
         # un-chunk the scale factors: chunk (rt, kt) byte (r%32)*16 + (r/32)*4 + kb
-        sf = p.sf.view(-1, 2, 32, 4, 4)[:2]                  # [row tile, k tile, r%32, r/32, kb]
-        sf = sf.permute(0, 3, 2, 1, 4).reshape(256, 8)       # [row, k block]
+        sf = p.sf.view(1, 2, 2, 32, 4, 4)                    # [row tile(256), k tile, chunk(128 rows), r%32, r/32, kb]
+        sf = sf.permute(0, 2, 4, 3, 1, 5).reshape(256, 8)    # [row, k block]
         scale = torch.exp2(sf.float() - 127).repeat_interleave(32, dim=1)
         ref = dequant(x, meta)
         # halving a re-biased block is exact except for elements 2^-14 (E4M3) below the block maximum
@@ -51,14 +51,15 @@ def test_pack_tables_preserve_values(lib):
             assert torch.equal(vals * scale, ref), meta.tag
 
 
-@pytest.mark.parametrize("shape", [(128, 256, 128), (128, 256, 512), (256, 512, 1024), (200, 300, 160), (1, 8, 32), (384, 1024, 4096)])
+@pytest.mark.parametrize("shape", [(128, 256, 128), (128, 224, 512), (256, 512, 1024), (200, 300, 160), (1, 8, 32), (384, 1024, 4096),
+                                   (2048, 4096, 512), (130, 230, 96), (1000, 2000, 1024)])
 def test_gemm_e4m3_shapes(lib, shape):
     M, N, K = shape
     torch.manual_seed(M + N + K)
     x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
     w = (0.05 * torch.randn(N, K, device=DEV)).to(torch.bfloat16)
     a = G.quantize_pack(x, MXFP8_E4M3_fn)
-    b = G.quantize_pack(w, MXFP8_E4M3_fn)
+    b = G.quantize_pack(w, MXFP8_E4M3_fn, G.OPERAND_B)
     y32 = dequant(x, MXFP8_E4M3_fn) @ dequant(w, MXFP8_E4M3_fn).t()
     for dt in (torch.float32, torch.bfloat16, torch.float16):
         y = G.mx_gemm(a, b, dt)
@@ -78,7 +79,7 @@ def test_gemm_format_pairs(lib, x_meta, w_meta):
     M, N, K = 256, 512, 512
     x = (torch.randn(M, K, device=DEV) * 3).to(torch.bfloat16)
     w = (0.02 * torch.randn(N, K, device=DEV)).to(torch.bfloat16)
-    y = G.mx_gemm(G.quantize_pack(x, x_meta), G.quantize_pack(w, w_meta), torch.bfloat16)
+    y = G.mx_gemm(G.quantize_pack(x, x_meta), G.quantize_pack(w, w_meta, G.OPERAND_B), torch.bfloat16)
     G.check_status(DEV)
     y32 = dequant(x, x_meta) @ dequant(w, w_meta).t()
     assert within_tolerance(y, y32)
