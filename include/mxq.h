@@ -139,6 +139,20 @@ int mxq_mx_gemm(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw_format, co
                 const uint8_t* b_sf, int b_hw_format, void* out, int out_dtype, const void* bias,
                 int64_t M, int64_t N, int64_t K, int* status, void* stream);
 
+/*
+ * mxfp_linear with quantised activation and weight in one call (layer types XqWqB / XqWqBq,
+ * src/mase_triton/mxfp/functional/linear.py:36-64): x [M,K] is quantised to the MXFP format
+ * (x_exp_bits, x_frac_bits; 32-element blocks along K, round to nearest, is_finite), packed as
+ * MXQ_OPERAND_A and multiplied with a weight already packed as MXQ_OPERAND_B.
+ * `scratch` (device, 256-byte aligned, at least mxq_mx_linear_scratch_bytes(M, K) bytes) holds the
+ * quantised activation between the three kernels; its contents are undefined afterwards.
+ */
+int64_t mxq_mx_linear_scratch_bytes(int64_t M, int64_t K);
+int mxq_mx_linear(const void* x, int x_dtype, int64_t M, int64_t K, int x_exp_bits, int x_frac_bits,
+                  const uint8_t* w_codes, const uint8_t* w_sf, int w_hw_format, int64_t N, void* out,
+                  int out_dtype, const void* bias, void* scratch, int64_t scratch_bytes, int* status,
+                  void* stream);
+
 #ifdef __cplusplus
 }
 #endif

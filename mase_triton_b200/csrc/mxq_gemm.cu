@@ -344,8 +344,8 @@ struct PackTables {
     uint32_t bad[8];        // bit c set: reference code c has no hardware encoding (block is re-biased)
 };
 
-__global__ void __launch_bounds__(256) mx_pack_kernel(const uint8_t* __restrict__ scales, const uint8_t* __restrict__ elements,
-                                                     uint8_t* __restrict__ hw_codes, uint8_t* __restrict__ hw_sf,
+__global__ void __launch_bounds__(256) mx_pack_kernel(const uint8_t* __restrict__ scales, const uint8_t* elements,
+                                                     uint8_t* hw_codes, uint8_t* __restrict__ hw_sf,
                                                      int64_t rows, int64_t K, int tile_rows, PackTables t) {
     __shared__ uint8_t s_plain[256], s_halved[256];
     s_plain[threadIdx.x] = t.plain[threadIdx.x];
@@ -366,6 +366,7 @@ __global__ void __launch_bounds__(256) mx_pack_kernel(const uint8_t* __restrict_
     uint8_t* sf_dst = hw_sf + ((tile * KT + kb / 4) * 2 + lr / 128) * 512 + (in_chunk % 32) * 16 + (in_chunk / 32) * 4 + (kb % 4);
     if (lr >= tile_rows || r >= rows || kb >= kb_per_row) { *sf_dst = 127; return; }   // padding: scale 1.0 (codes there are TMA zero fill)
     const int64_t blk = r * kb_per_row + kb;
+    // `elements` and `hw_codes` may be the same buffer: the whole block is read before it is written
     const uint4* src = reinterpret_cast<const uint4*>(elements + blk * 32);
     uint4 c[2] = {src[0], src[1]};
     const uint8_t* cb = reinterpret_cast<const uint8_t*>(c);
@@ -526,4 +527,37 @@ extern "C" int mxq_mx_gemm(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw
     if (out_dtype == MXQ_BF16) return gemm::launch_gemm_dt<MXQ_BF16>(a_codes, b_codes, a_sf, b_sf, out, bias, (int)M, (int)N, (int)K, idesc, status, st);
     if (out_dtype == MXQ_F16) return gemm::launch_gemm_dt<MXQ_F16>(a_codes, b_codes, a_sf, b_sf, out, bias, (int)M, (int)N, (int)K, idesc, status, st);
     return MXQ_EINVAL;
+}
+
+// ------------------------------------------------------------------------------------------------
+// fused-backend linear: quantise the activation, pack it, run the GEMM -- scratch supplied by the caller
+// ------------------------------------------------------------------------------------------------
+static int linear_with_scratch(const void* x, int x_dtype, int64_t M, int64_t K, int x_eb, int x_fb, const uint8_t* w_codes,
+                               const uint8_t* w_sf, int w_hw_format, int64_t N, void* out, int out_dtype, const void* bias,
+                               uint8_t* scratch, int* status, void* stream) {
+    // scratch: [M*K] element codes (re-encoded in place) | [M*K/32] reference scales | packed scale chunks
+    uint8_t* codes = scratch;
+    uint8_t* ref_scales = codes + M * K;
+    uint8_t* sf = ref_scales + ((M * K / 32 + 255) / 256) * 256;
+    int rc = mxq_mxfp_extract(x, x_dtype, ref_scales, codes, M * K, 32, x_eb, x_fb, 1, MXQ_RN, stream);
+    if (rc != MXQ_OK) return rc;
+    int x_hw_format = 0;
+    rc = mxq_mx_pack_operand(ref_scales, codes, M, K, x_eb, x_fb, MXQ_OPERAND_A, codes, sf, &x_hw_format, stream);
+    if (rc != MXQ_OK) return rc;
+    return mxq_mx_gemm(codes, sf, x_hw_format, w_codes, w_sf, w_hw_format, out, out_dtype, bias, M, N, K, status, stream);
+}
+
+extern "C" int64_t mxq_mx_linear_scratch_bytes(int64_t M, int64_t K) {
+    if (M <= 0 || K <= 0 || K % 32 != 0) return MXQ_EINVAL;
+    return M * K + ((M * K / 32 + 255) / 256) * 256 + mxq_mx_sf_bytes(M, K, MXQ_OPERAND_A);
+}
+
+extern "C" int mxq_mx_linear(const void* x, int x_dtype, int64_t M, int64_t K, int x_exp_bits, int x_frac_bits,
+                             const uint8_t* w_codes, const uint8_t* w_sf, int w_hw_format, int64_t N, void* out, int out_dtype,
+                             const void* bias, void* scratch, int64_t scratch_bytes, int* status, void* stream) {
+    if (!x || !w_codes || !w_sf || !out || !scratch || M <= 0 || N <= 0 || K <= 0 || K % 32 != 0) return MXQ_EINVAL;
+    if (reinterpret_cast<uintptr_t>(scratch) % 256 != 0) return MXQ_EINVAL;
+    if (scratch_bytes < mxq_mx_linear_scratch_bytes(M, K)) return MXQ_ESIZE;
+    return linear_with_scratch(x, x_dtype, M, K, x_exp_bits, x_frac_bits, w_codes, w_sf, w_hw_format, N, out, out_dtype, bias,
+                               static_cast<uint8_t*>(scratch), status, stream);
 }

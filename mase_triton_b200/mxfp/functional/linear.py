@@ -54,9 +54,7 @@ def mxfp_linear(
             and len(w_tensor_meta.shape) == 2 and x.shape[-1] % 32 == 0 and x.numel() > 0):
         # both operands stay quantised: block-scaled tensor-core GEMM, fp32 accumulation
         wq = _gemm.packed_weight(w_scales, w_elements, w_tensor_meta.shape, w_tensor_meta.meta)
-        xq = _gemm.quantize_pack(x, x_meta)
-        out = _gemm.mx_gemm(xq, wq, x.dtype, bias)
-        return out.reshape(*x.shape[:-1], wq.rows)
+        return _gemm.mx_linear(x, x_meta, wq, bias)
     if kind.x_quantised:
         x = quantize_dequantize(x, block_dim=-1, mxfp_meta=x_meta)       # same bits as extract + compose
     weight = compose_mxfp_tensor(w_scales, w_elements, w_tensor_meta) if kind.w_quantised else w

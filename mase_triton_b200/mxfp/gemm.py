@@ -10,7 +10,6 @@ counterpart: its ``backend="fused"`` raises ``NotImplementedError``
 from __future__ import annotations
 
 import ctypes
-from collections import OrderedDict
 from dataclasses import dataclass
 
 import torch
@@ -84,21 +83,16 @@ def quantize_pack(x: Tensor, meta: MXFPMeta, operand: int = OPERAND_A) -> Packed
     return pack_operand(scales, elements, rows, K, meta, operand)
 
 
-_WEIGHT_CACHE: "OrderedDict[tuple, PackedOperand]" = OrderedDict()
-
-
 def packed_weight(w_scales: Tensor, w_elements: Tensor, shape: tuple[int, int], meta: MXFPMeta) -> PackedOperand:
-    """Packed form of a quantised weight, cached on the identity and version of its code tensors."""
-    key = (w_elements.data_ptr(), w_scales.data_ptr(), w_elements._version, w_scales._version, tuple(shape), meta, w_elements.device)
-    hit = _WEIGHT_CACHE.get(key)
-    if hit is None:
-        hit = pack_operand(w_scales, w_elements, shape[0], shape[1], meta, OPERAND_B)
-        _WEIGHT_CACHE[key] = hit
-        while len(_WEIGHT_CACHE) > 64:
-            _WEIGHT_CACHE.popitem(last=False)
-    else:
-        _WEIGHT_CACHE.move_to_end(key)
-    return hit
+    """Packed form of a quantised weight.  The result is kept on the ``w_elements`` tensor object itself
+    (so it dies with it and can never be confused with another tensor that re-uses the same address)
+    and is rebuilt when either code tensor was modified in place or replaced."""
+    tag = (w_elements._version, w_scales.data_ptr(), w_scales._version, tuple(shape), meta)
+    cached = getattr(w_elements, "_mxq_packed", None)
+    if cached is None or cached[0] != tag:
+        cached = (tag, pack_operand(w_scales, w_elements, shape[0], shape[1], meta, OPERAND_B))
+        w_elements._mxq_packed = cached
+    return cached[1]
 
 
 def mx_gemm(a: PackedOperand, b: PackedOperand, out_dtype: torch.dtype, bias: Tensor | None = None,
@@ -118,3 +112,40 @@ def mx_gemm(a: PackedOperand, b: PackedOperand, out_dtype: torch.dtype, bias: Te
                                      status_word(dev).data_ptr(), _lib.stream_ptr(dev))
     _lib.check(rc, "mxq_mx_gemm")
     return out
+
+
+_SCRATCH: dict[torch.device, Tensor] = {}
+
+
+def _scratch(device: torch.device, nbytes: int) -> Tensor:
+    """Per-device scratch buffer for the quantised activation, grown on demand and re-used."""
+    buf = _SCRATCH.get(device)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty((nbytes,), dtype=torch.uint8, device=device)
+        _SCRATCH[device] = buf
+    return buf
+
+
+def mx_linear(x: Tensor, x_meta: MXFPMeta, w: PackedOperand, bias: Tensor | None = None, out: Tensor | None = None) -> Tensor:
+    """``quantise(x) @ w^T (+ bias)`` through the single C entry point ``mxq_mx_linear``: activation
+    quantisation, packing and the tensor-core GEMM are enqueued back to back on the current stream."""
+    _lib.require_cuda(x, "mx_linear")
+    assert supported(x_meta) and w.operand == OPERAND_B and x.shape[-1] == w.K
+    if x.dtype not in _lib.DTYPE_ID:
+        x = x.float()
+    x2 = x.reshape(-1, w.K).contiguous()
+    M, dev = x2.shape[0], x2.device
+    L = _lib.load()
+    if out is None:
+        out = torch.empty((M, w.rows), dtype=x2.dtype, device=dev)
+    if bias is not None:
+        bias = bias.to(out.dtype).contiguous()
+    nbytes = L.mxq_mx_linear_scratch_bytes(M, w.K)
+    scratch = _scratch(dev, nbytes)
+    with torch.cuda.device(dev):
+        rc = L.mxq_mx_linear(x2.data_ptr(), _lib.DTYPE_ID[x2.dtype], M, w.K, x_meta.element_exp_bits, x_meta.element_frac_bits,
+                             w.codes.data_ptr(), w.sf.data_ptr(), w.hw_format, w.rows, out.data_ptr(), _lib.DTYPE_ID[out.dtype],
+                             None if bias is None else bias.data_ptr(), scratch.data_ptr(), scratch.numel(),
+                             status_word(dev).data_ptr(), _lib.stream_ptr(dev))
+    _lib.check(rc, "mxq_mx_linear")
+    return out.reshape(*x.shape[:-1], w.rows)
