@@ -153,6 +153,27 @@ int mxq_mx_linear(const void* x, int x_dtype, int64_t M, int64_t K, int x_exp_bi
                   int out_dtype, const void* bias, void* scratch, int64_t scratch_bytes, int* status,
                   void* stream);
 
+/*
+ * mxq_mx_linear for callers that cannot allocate device memory (no counterpart in the reference,
+ * which always allocates through PyTorch).  Same arguments and same result as mxq_mx_linear, but
+ * the scratch is a fixed array of mxq_mx_linear_static_capacity() bytes (8 MiB) that every GPU
+ * loading this library reserves until the process exits.  Meant for hosts such as a real-time
+ * serving loop that gave all device memory to its own arena, a plugin inside a process whose
+ * allocator must not be touched, or work issued while another thread captures a CUDA graph.
+ *   - Returns MXQ_ESIZE when mxq_mx_linear_scratch_bytes(M, K) exceeds the capacity
+ *     (for instance M*K above roughly 7.5 Mi elements).
+ *   - The first call on each device looks up the array's device address (no allocation); make that
+ *     first call outside any stream capture.
+ *   - All calls on a device share the one array and it keeps the previous call's contents (nothing
+ *     needs clearing: each call overwrites all it reads).  Two calls whose kernels can overlap on
+ *     the GPU - different streams without an ordering between them - race on it; serialise them.
+ *   - Calls no cudaMalloc / cudaFree and no allocating library routine.
+ */
+int64_t mxq_mx_linear_static_capacity(void);
+int mxq_mx_linear_static(const void* x, int x_dtype, int64_t M, int64_t K, int x_exp_bits, int x_frac_bits,
+                         const uint8_t* w_codes, const uint8_t* w_sf, int w_hw_format, int64_t N,
+                         void* out, int out_dtype, const void* bias, int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

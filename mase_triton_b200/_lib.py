@@ -28,9 +28,11 @@ SIGNATURES = {
     "mxq_mx_pack_operand": [_p, _p, _i64, _i64, _i, _i, _i, _p, _p, _p, _p],
     "mxq_mx_gemm": [_p, _p, _i, _p, _p, _i, _p, _i, _p, _i64, _i64, _i64, _p, _p],
     "mxq_mx_linear": [_p, _i, _i64, _i64, _i, _i, _p, _p, _i, _i64, _p, _i, _p, _p, _i64, _p, _p],
+    "mxq_mx_linear_static": [_p, _i, _i64, _i64, _i, _i, _p, _p, _i, _i64, _p, _i, _p, _p, _p],
     "mxq_version": [],
 }
-_I64_FUNCS = {"mxq_mx_sf_bytes": [_i64, _i64, _i], "mxq_mx_linear_scratch_bytes": [_i64, _i64]}
+_I64_FUNCS = {"mxq_mx_sf_bytes": [_i64, _i64, _i], "mxq_mx_linear_scratch_bytes": [_i64, _i64],
+              "mxq_mx_linear_static_capacity": []}
 _STRING_FUNCS = {"mxq_status_string": [_i], "mxq_last_cuda_error": []}
 
 _lib = None

@@ -561,3 +561,46 @@ extern "C" int mxq_mx_linear(const void* x, int x_dtype, int64_t M, int64_t K, i
     return linear_with_scratch(x, x_dtype, M, K, x_exp_bits, x_frac_bits, w_codes, w_sf, w_hw_format, N, out, out_dtype, bias,
                                static_cast<uint8_t*>(scratch), status, stream);
 }
+
+// ------------------------------------------------------------------------------------------------
+// the same linear for callers that must not allocate: scratch is a fixed array inside the library
+// ------------------------------------------------------------------------------------------------
+// Some hosts of this code cannot call cudaMalloc at the point where they run a layer: a real-time
+// inference loop that has handed all device memory to its own arena, a plugin loaded into a process
+// whose allocator is off limits, a thread that runs while another thread captures a CUDA graph.
+// For them the scratch of mxq_mx_linear lives here, in device memory reserved when the library is
+// loaded (MXQ_STATIC_SCRATCH_BYTES on every GPU that loads it, until the process exits).
+#define MXQ_STATIC_SCRATCH_BYTES (8ll << 20)
+static __device__ __align__(256) uint8_t g_static_scratch[MXQ_STATIC_SCRATCH_BYTES];
+
+// In host code `g_static_scratch` is only a handle for the symbol, not a device address: the address
+// is looked up once per device, with that device current, and cached.
+static uint8_t* static_scratch_ptr() {
+    static std::mutex mu;
+    static uint8_t* cache[64] = {nullptr};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache[dev] == nullptr) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) { set_last_cuda_error(e); return nullptr; }
+        cache[dev] = static_cast<uint8_t*>(p);
+    }
+    return cache[dev];
+}
+
+extern "C" int64_t mxq_mx_linear_static_capacity(void) { return MXQ_STATIC_SCRATCH_BYTES; }
+
+extern "C" int mxq_mx_linear_static(const void* x, int x_dtype, int64_t M, int64_t K, int x_exp_bits, int x_frac_bits,
+                                    const uint8_t* w_codes, const uint8_t* w_sf, int w_hw_format, int64_t N, void* out,
+                                    int out_dtype, const void* bias, int* status, void* stream) {
+    if (!x || !w_codes || !w_sf || !out || M <= 0 || N <= 0 || K <= 0 || K % 32 != 0) return MXQ_EINVAL;
+    if (mxq_mx_linear_scratch_bytes(M, K) > MXQ_STATIC_SCRATCH_BYTES) return MXQ_ESIZE;   // activation too large for the fixed scratch
+    uint8_t* scratch = static_scratch_ptr();
+    if (scratch == nullptr) return MXQ_ELAUNCH;
+    // every byte of the scratch that the GEMM reads is written by the two kernels before it, so
+    // nothing has to be cleared between calls
+    return linear_with_scratch(x, x_dtype, M, K, x_exp_bits, x_frac_bits, w_codes, w_sf, w_hw_format, N, out, out_dtype, bias,
+                               scratch, status, stream);
+}
