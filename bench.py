@@ -175,12 +175,47 @@ def time_steps(fn, steps: int, stream=None) -> list[float]:
     return [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
 
 
+def graph_time(fn, reps: int, rounds: int = 5) -> float:
+    """Median device time (ms) of one call of `fn`, measured by replaying a CUDA graph of `reps`
+    back-to-back calls: no host launch overhead between kernels, so short kernels are timed honestly."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    try:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(reps):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(rounds):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) / reps)
+        return statistics.median(ts)
+    except Exception:
+        torch.cuda.synchronize()
+        return statistics.median(time_steps(fn, reps))
+
+
 def extras_single_gpu(dev, steps: int, warmup: int, peak: float) -> dict:
-    """MXFP extract / compose on configurations 1 and 3 (device-resident, CUDA-event timed)."""
+    """MXFP extract / compose on configurations 1 and 3, and the MX GEMM / linear on configurations
+    4 and 5 (device-resident; CUDA-graph replays so that host launch gaps are not part of the time)."""
     from mase_triton_b200 import synthetic
+    from mase_triton_b200.mxfp import gemm as G
     from mase_triton_b200.mxfp import kernels as mxk
-    from mase_triton_b200.mxfp.meta import MXFP8_E4M3_fn, OCP_MXFP4_E2M1
+    from mase_triton_b200.mxfp.layers import MXFPLinearPTQ
+    from mase_triton_b200.mxfp.meta import MXFP8_E4M3_fn, OCP_MXFP4_E2M1, OCP_MXFP6_E3M2
     out = {}
+    reps = max(4, min(steps, 20))
     for name, gen, meta, s_in, nsets in (("cfg1_mxfp8_fp32_4096x4096", synthetic.cfg1_mxfp8_fp32, MXFP8_E4M3_fn, 4, 4),
                                          ("cfg3_mxfp4_bf16_16384x8192", synthetic.cfg3_mxfp4_bf16, OCP_MXFP4_E2M1, 2, 1)):
         x = gen().to(dev).flatten()
@@ -191,37 +226,137 @@ def extras_single_gpu(dev, steps: int, warmup: int, peak: float) -> dict:
         def ext():
             i[0] += 1
             return mxk.extract_mxfp_components(xs[i[0] % nsets], meta)
-        for _ in range(warmup):
-            ext()
-        t_ext = statistics.median(time_steps(ext, steps))
+        t_ext = graph_time(ext, reps * nsets)
         se = [mxk.extract_mxfp_components(v, meta) for v in xs]
 
         def comp():
             i[0] += 1
             s, e = se[i[0] % nsets]
             return mxk.compose_mxfp_tensor(s, e, meta, x.dtype)
-        for _ in range(warmup):
-            comp()
-        t_cmp = statistics.median(time_steps(comp, steps))
+        t_cmp = graph_time(comp, reps * nsets)
 
         def qdq():
             i[0] += 1
             return mxk.quantize_dequantize(xs[i[0] % nsets], meta, x.dtype)
-        for _ in range(warmup):
-            qdq()
-        t_qdq = statistics.median(time_steps(qdq, steps))
+        t_qdq = graph_time(qdq, reps * nsets)
         b_ext = n * (s_in + 1 + 1 / 32)
         b_cmp = n * (1 + 1 / 32 + s_in)
         out[name] = {
             "extract_GBps": round(b_ext / t_ext / 1e6, 1), "extract_frac_of_peak": round(b_ext / t_ext / 1e6 / peak, 3),
             "compose_GBps": round(b_cmp / t_cmp / 1e6, 1), "compose_frac_of_peak": round(b_cmp / t_cmp / 1e6 / peak, 3),
             "extract_plus_compose_GBps": round((b_ext + b_cmp) / (t_ext + t_cmp) / 1e6, 1),
+            "extract_plus_compose_frac_of_peak": round((b_ext + b_cmp) / (t_ext + t_cmp) / 1e6 / peak, 3),
             "fused_qdq_GBps": round(n * 2 * s_in / t_qdq / 1e6, 1),
             "ms": {"extract": round(t_ext, 4), "compose": round(t_cmp, 4), "fused_qdq": round(t_qdq, 4)},
-            "buffer_sets_rotated": nsets,
+            "buffer_sets_rotated": nsets, "timing": "CUDA graph replay",
         }
         del xs, se, x
         torch.cuda.empty_cache()
+
+    # configuration 4: x bf16 [8192,4096], W [14336,4096], MXFP8 E4M3 both, bf16 out
+    xc, wc = synthetic.cfg4_linear_operands()
+    xc, wc = xc.to(dev), wc.to(dev)
+    M, K = xc.shape
+    N = wc.shape[0]
+    flops = 2.0 * M * N * K
+    a, b = G.quantize_pack(xc, MXFP8_E4M3_fn), G.quantize_pack(wc, MXFP8_E4M3_fn, G.OPERAND_B)
+    o = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    t_gemm = graph_time(lambda: G.mx_gemm(a, b, torch.bfloat16, out=o), reps)
+    fc = torch.nn.Linear(K, N, bias=False, device=dev, dtype=torch.bfloat16)
+    with torch.no_grad():
+        fc.weight.copy_(wc)
+    fused = MXFPLinearPTQ.from_linear(fc, MXFP8_E4M3_fn, MXFP8_E4M3_fn, None, "XqWqB", "fused")
+    sep = MXFPLinearPTQ.from_linear(fc, MXFP8_E4M3_fn, MXFP8_E4M3_fn, None, "XqWqB", "separate")
+    t_fused = graph_time(lambda: fused(xc), reps)
+    t_sep = graph_time(lambda: sep(xc), max(3, reps // 2))
+    G.check_status(dev)
+    rel = ((fused(xc).float() - sep(xc).float()).abs().mean() / sep(xc).float().abs().mean()).item()
+    out["cfg4_mxfp_linear_8192x14336x4096"] = {
+        "gemm_kernel_TFLOPs": round(flops / t_gemm / 1e9, 1), "fused_linear_TFLOPs": round(flops / t_fused / 1e9, 1),
+        "separate_linear_TFLOPs_reference_style_cublas_bf16": round(flops / t_sep / 1e9, 1),
+        "gemm_frac_of_4500_nominal_mx": round(flops / t_gemm / 1e9 / 4500, 3),
+        "ms": {"gemm": round(t_gemm, 4), "fused_linear": round(t_fused, 4), "separate_linear": round(t_sep, 4)},
+        "mean_rel_diff_fused_vs_separate": round(rel, 5),
+    }
+    del fc, fused, sep, a, b, o, xc, wc
+    torch.cuda.empty_cache()
+
+    # configuration 5: seven projections of one Llama-3-8B-shaped layer, W MXFP6 E3M2, x MXFP8 E4M3, 16x2048 tokens
+    sweep, tot_flops, tot_ms = {}, 0.0, 0.0
+    for pname, n_out, n_in in synthetic.CFG5_PROJECTIONS:
+        w = synthetic.cfg5_weight(pname).to(dev)
+        x5 = synthetic.cfg5_input(n_in).to(dev)
+        fc = torch.nn.Linear(n_in, n_out, bias=False, device=dev, dtype=torch.bfloat16)
+        with torch.no_grad():
+            fc.weight.copy_(w)
+        layer = MXFPLinearPTQ.from_linear(fc, MXFP8_E4M3_fn, OCP_MXFP6_E3M2, None, "XqWqB", "fused")
+        t = graph_time(lambda: layer(x5), max(3, reps // 2))
+        fl = 2.0 * x5.shape[0] * x5.shape[1] * n_in * n_out
+        sweep[pname] = {"ms": round(t, 4), "TFLOPs": round(fl / t / 1e9, 1)}
+        tot_flops += fl
+        tot_ms += t
+        del fc, layer, w, x5
+        torch.cuda.empty_cache()
+    G.check_status(dev)
+    sweep["sweep_TFLOPs"] = round(tot_flops / tot_ms / 1e9, 1)
+    sweep["sweep_ms"] = round(tot_ms, 4)
+    out["cfg5_llama3_8b_layer_fused_linear"] = sweep
+    return out
+
+
+def extras_multi_gpu(dev, dist, rank: int, world: int, local: int, steps: int, peak: float) -> dict:
+    """Sharded runs of configurations 3 (rows) and 4 (output features) on `world` GPUs; every time is the
+    max over ranks of a CUDA-event measurement that starts after a barrier."""
+    from mase_triton_b200 import parallel, synthetic
+    from mase_triton_b200.mxfp import gemm as G
+    from mase_triton_b200.mxfp import kernels as mxk
+    from mase_triton_b200.mxfp.meta import MXFP8_E4M3_fn, OCP_MXFP4_E2M1
+    out = {}
+    reps = max(4, min(steps, 20))
+
+    def max_over_ranks(ms: float) -> float:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(fn) -> float:
+        for _ in range(3):
+            fn()
+        dist.barrier(device_ids=[local])
+        torch.cuda.synchronize()
+        return max_over_ranks(statistics.median(time_steps(fn, reps)))
+
+    # configuration 3: rows split evenly, no collective
+    rows = 16384
+    lo, hi = parallel.shard_bounds(rows, rank, world)
+    x = synthetic.cfg3_mxfp4_bf16(rows=slice(lo, hi)).to(dev).flatten()
+    n_total = rows * 8192
+    t_ext = timed(lambda: mxk.extract_mxfp_components(x, OCP_MXFP4_E2M1))
+    s, e = mxk.extract_mxfp_components(x, OCP_MXFP4_E2M1)
+    t_cmp = timed(lambda: mxk.compose_mxfp_tensor(s, e, OCP_MXFP4_E2M1, torch.bfloat16))
+    b = n_total * (2 + 1 + 1 / 32)
+    out["cfg3_rows_sharded"] = {"extract_GBps_total": round(b / t_ext / 1e6, 1), "compose_GBps_total": round(b / t_cmp / 1e6, 1),
+                                "extract_plus_compose_GBps_total": round(2 * b / (t_ext + t_cmp) / 1e6, 1),
+                                "frac_of_peak_per_gpu": round(2 * b / (t_ext + t_cmp) / 1e6 / peak / world, 3),
+                                "rows_per_gpu": hi - lo, "collective": "none"}
+    del x, s, e
+    torch.cuda.empty_cache()
+
+    # configuration 4: weight split by output feature, activation replicated, outputs all-gathered over NCCL
+    xc, wc = synthetic.cfg4_linear_operands()
+    n0, n1 = parallel.shard_bounds(wc.shape[0], rank, world)
+    xc, wl = xc.to(dev), wc[n0:n1].contiguous().to(dev)
+    M, K, N = xc.shape[0], xc.shape[1], wc.shape[0]
+    a, bq = G.quantize_pack(xc, MXFP8_E4M3_fn), G.quantize_pack(wl, MXFP8_E4M3_fn, G.OPERAND_B)
+    sizes = [q - p for p, q in (parallel.shard_bounds(N, r, world) for r in range(world))]
+    o = torch.empty((M, n1 - n0), dtype=torch.bfloat16, device=dev)
+    t_gemm = timed(lambda: G.mx_gemm(a, bq, torch.bfloat16, out=o))
+    t_all = timed(lambda: parallel.gather_columns(G.mx_gemm(a, bq, torch.bfloat16, out=o), sizes))
+    G.check_status(dev)
+    fl = 2.0 * M * N * K
+    out["cfg4_column_parallel"] = {"gemm_only_TFLOPs_total": round(fl / t_gemm / 1e9, 1), "gemm_plus_allgather_TFLOPs_total": round(fl / t_all / 1e9, 1),
+                                   "ms": {"gemm": round(t_gemm, 4), "gemm_plus_allgather": round(t_all, 4)},
+                                   "out_features_per_gpu": n1 - n0, "collective": "nccl all_gather of bf16 [M, N/g] shards"}
     return out
 
 
@@ -304,6 +439,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the configuration 1 / 3 side measurements")
+    ap.add_argument("--multi-extras", action="store_true",
+                    help="with more than one GPU, also run the sharded configuration 3 / 4 measurements (uses NCCL all-gather)")
     ap.add_argument("--case", default=None, help="run one small single-kernel case (for profiling) and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -413,6 +550,17 @@ def main() -> None:
                 line["extras"] = extras_single_gpu(dev, max(5, min(args.steps, 50)), args.warmup, peak)
             except Exception as exc:
                 line["extras"] = {"error": str(exc)}
+    extras_multi = None
+    if dist is not None and args.multi_extras:
+        del x, out
+        torch.cuda.empty_cache()
+        try:
+            extras_multi = extras_multi_gpu(dev, dist, rank, world, local, max(5, min(args.steps, 50)), peak)
+        except Exception as exc:
+            extras_multi = {"error": str(exc)}
+    if rank == 0:
+        if extras_multi is not None:
+            line["extras"] = extras_multi
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier(device_ids=[local])

@@ -1,0 +1,108 @@
+"""Single-node multi-GPU use of the path: one process per GPU over ``torch.distributed``.
+
+* Quantisation (extract / compose / quantize_dequantize) shards by rows and needs no collective:
+  with blocks along the last dim and ``cols % block_size == 0`` no block spans two rows, and the
+  scales / elements of a row slice are exactly the matching slice of the full result.
+* Linears are column-parallel by output feature: rank r owns rows ``[n0, n1)`` of the weight (a
+  contiguous slice of ``w_elements.view(N, K)`` and ``w_scales.view(N, K/32)``), every rank
+  quantises the (replicated) activation itself, and the ``[M, N/g]`` partial outputs are gathered
+  with one all-gather (NCCL over NVLink on GPUs, gloo in the CPU tests).
+
+The reference has no distributed code; this module is new functionality named by the benchmark
+configurations (row-sharded quantisation, column-parallel linears).
+"""
+
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+from .mxfp.meta import MXFPTensorMeta
+
+
+def shard_bounds(n: int, rank: int, world: int, multiple: int = 1) -> tuple[int, int]:
+    """Half-open range of rank ``rank`` when ``n`` items (in units of ``multiple``) are split as evenly as
+    possible over ``world`` ranks; earlier ranks take the remainder."""
+    assert n % multiple == 0 and 0 <= rank < world
+    units = n // multiple
+    base, rem = divmod(units, world)
+    lo = rank * base + min(rank, rem)
+    hi = lo + base + (1 if rank < rem else 0)
+    return lo * multiple, hi * multiple
+
+
+def shard_rows(x: Tensor, rank: int, world: int) -> Tensor:
+    """Row slice of ``x`` owned by ``rank`` (a view)."""
+    lo, hi = shard_bounds(x.shape[0], rank, world)
+    return x[lo:hi]
+
+
+def shard_quantised_weight(w_scales: Tensor, w_elements: Tensor, w_tensor_meta: MXFPTensorMeta, rank: int, world: int):
+    """Output-feature shard of a weight quantised with blocks along ``in_features``.
+
+    Returns ``(scales, elements, tensor_meta, (n0, n1))`` where the tensors are contiguous slices of the
+    inputs (no copy) shaped like a freshly quantised ``[n1-n0, K]`` weight."""
+    N, K = w_tensor_meta.shape
+    B = w_tensor_meta.meta.block_size
+    assert w_tensor_meta.block_dim in (1, -1) and K % B == 0
+    n0, n1 = shard_bounds(N, rank, world)
+    blocks_per_row = K // B
+    scales = w_scales.reshape(N * blocks_per_row, 1)[n0 * blocks_per_row:n1 * blocks_per_row]
+    elements = w_elements.reshape(N * blocks_per_row, B)[n0 * blocks_per_row:n1 * blocks_per_row]
+    meta = w_tensor_meta.create(shape=(n1 - n0, K))
+    return scales, elements, meta, (n0, n1)
+
+
+def gather_columns(y_local: Tensor, sizes: list[int], group=None) -> Tensor:
+    """All-gather ``[..., n_r]`` partial outputs into ``[..., sum(n_r)]`` on every rank."""
+    world = dist.get_world_size(group)
+    assert len(sizes) == world
+    lead = y_local.shape[:-1]
+    if len(set(sizes)) == 1:
+        # equal shards: one collective into a [world, M, n] buffer, then one strided copy
+        flat = y_local.reshape(-1, sizes[0]).contiguous()
+        buf = torch.empty((world * flat.shape[0], sizes[0]), dtype=flat.dtype, device=flat.device)
+        dist.all_gather_into_tensor(buf, flat, group=group)          # rank r's rows land at [r*M, (r+1)*M)
+        return buf.view(world, flat.shape[0], sizes[0]).permute(1, 0, 2).reshape(*lead, world * sizes[0])
+    # uneven shards: pad every shard to the widest one, gather, drop the padding
+    widest = max(sizes)
+    flat = y_local.reshape(-1, y_local.shape[-1])
+    padded = torch.zeros((flat.shape[0], widest), dtype=flat.dtype, device=flat.device)
+    padded[:, : flat.shape[1]] = flat
+    buf = torch.empty((world * flat.shape[0], widest), dtype=flat.dtype, device=flat.device)
+    dist.all_gather_into_tensor(buf, padded, group=group)
+    buf = buf.view(world, flat.shape[0], widest)
+    return torch.cat([buf[r, :, :n] for r, n in enumerate(sizes)], dim=-1).reshape(*lead, sum(sizes))
+
+
+class ColumnParallelLinear:
+    """Column-parallel wrapper: ``local_forward(x) -> [..., n_r]`` runs this rank's shard (for example an
+    ``MXFPLinearPTQ`` built from :func:`shard_quantised_weight`); ``__call__`` gathers the full output."""
+
+    def __init__(self, local_forward: Callable[[Tensor], Tensor], out_features: int, group=None):
+        self.local_forward = local_forward
+        self.group = group
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        self.sizes = [hi - lo for lo, hi in (shard_bounds(out_features, r, world) for r in range(world))]
+        self.bounds = shard_bounds(out_features, rank, world)
+
+    def __call__(self, x: Tensor, gather: bool = True) -> Tensor:
+        y = self.local_forward(x)
+        assert y.shape[-1] == self.bounds[1] - self.bounds[0]
+        return gather_columns(y, self.sizes, self.group) if gather else y
+
+
+def column_parallel_mxfp_linear(layer, group=None) -> ColumnParallelLinear:
+    """Shard an ``MXFPLinearPTQ`` whose weight is quantised (``Wq``) across the ranks of ``group``."""
+    from .mxfp.layers import MXFPLinearPTQ
+
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    assert layer.w_scales is not None, "column_parallel_mxfp_linear needs a quantised weight"
+    s, e, meta, (n0, n1) = shard_quantised_weight(layer.w_scales.data, layer.w_elements.data, layer.w_tensor_meta, rank, world)
+    bias = None if layer.bias is None else layer.bias.data[n0:n1]
+    local = MXFPLinearPTQ.from_quantized(s.contiguous(), e.contiguous(), meta, bias, None, None, None, layer.x_mxfp_meta,
+                                         layer.layer_type, layer.backend)
+    return ColumnParallelLinear(local, layer.out_features, group)
