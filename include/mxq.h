@@ -129,6 +129,15 @@ int mxq_mx_pack_operand(const uint8_t* scales, const uint8_t* elements, int64_t 
                         int* hw_format, void* stream);
 
 /*
+ * One-pass alternative to mxq_mxfp_extract + mxq_mx_pack_operand for the LEFT operand: quantise
+ * x [M,K] to MXFP8 (E4M3 or E5M2 elements, 32-element blocks along K, round to nearest) directly
+ * into hardware codes and MXQ_OPERAND_A scale chunks. Same bytes as the two-step route.
+ * Returns MXQ_ESIZE for other element formats or unaligned buffers (use the two-step route).
+ */
+int mxq_mx_quantize_pack(const void* x, int x_dtype, int64_t M, int64_t K, int exp_bits, int frac_bits,
+                         uint8_t* hw_codes, uint8_t* hw_sf, int* hw_format, void* stream);
+
+/*
  * out[M,N] = A[M,K] * B[N,K]^T (+ bias[N]) on operands packed as MXQ_OPERAND_A / MXQ_OPERAND_B,
  * fp32 accumulation in tensor memory.
  * out_dtype / bias dtype: MXQ_F32, MXQ_BF16 or MXQ_F16 (bias may be NULL). K % 32 == 0.

@@ -307,9 +307,32 @@ __device__ __forceinline__ uint32_t pack4_codes(const uint32_t* mag, const uint3
     return w;
 }
 
-template <class KIn, class F, int U, bool WRITE_CODES, bool FULL>
+// what the block-32 quantiser writes
+constexpr int MODE_QDQ = 0;      // dequantised values (fused quantize_dequantize)
+constexpr int MODE_CODES = 1;    // reference scales + element codes
+constexpr int MODE_HWPACK = 2;   // tensor-core operand: hardware FP8 codes + scale-factor chunks (left operand)
+
+// Geometry of the scale-factor chunks of a [rows, K] left operand (see mxq_gemm.cu): the block index is
+// split into (row, K block) with a multiply-shift division by K/32.
+struct PackGeom {
+    uint32_t kbpr;     // K / 32
+    uint32_t magic;    // ceil(2^(31+shift) / kbpr)
+    uint32_t shift;
+    uint32_t KT;       // ceil(K / 128)
+};
+
+__device__ __forceinline__ uint32_t sf_chunk_offset(uint32_t blk, const PackGeom& g) {
+    const uint32_t r = (uint32_t)(((uint64_t)blk * g.magic) >> (31 + g.shift));     // blk / kbpr for blk < 2^31
+    const uint32_t kb = blk - r * g.kbpr;
+    const uint32_t lr = r & 255u, rr = lr & 127u;
+    return (((r >> 8) * g.KT + (kb >> 2)) * 2u + (lr >> 7)) * 512u + (rr & 31u) * 16u + (rr >> 5) * 4u + (kb & 3u);
+}
+
+template <class KIn, class F, int U, int MODE, bool FULL>
 __device__ __forceinline__ void mxfp_b32_quant_tile(const char* __restrict__ src, uint8_t* __restrict__ scales,
-                                                    char* __restrict__ dst, int64_t first, int64_t left, const F& f) {
+                                                    char* __restrict__ dst, int64_t first, int64_t left, const F& f,
+                                                    const PackGeom& geom) {
+    constexpr bool WRITE_CODES = (MODE != MODE_QDQ);
     constexpr int V = 16 / KIn::size;     // elements per lane per access: 4 (fp32) or 8 (16-bit)
     constexpr int G = 32 / V;             // lanes that share one 32-element block: 8 or 4
     static_assert(U <= G, "one lane of the group per in-flight access");
@@ -336,7 +359,7 @@ __device__ __forceinline__ void mxfp_b32_quant_tile(const char* __restrict__ src
 #pragma unroll
     for (int j = 1; j < U; ++j) mine = (sub == j) ? amax[j] : mine;
     const uint32_t hdr = block_header(mine, f);
-    if (WRITE_CODES && sub < U && (FULL || sub * kThreads < left))
+    if (MODE == MODE_CODES && sub < U && (FULL || sub * kThreads < left))
         scales[(first + sub * kThreads) / G] = (uint8_t)(hdr >> 8);
 #pragma unroll
     for (int j = 0; j < U; ++j) {
@@ -350,6 +373,27 @@ __device__ __forceinline__ void mxfp_b32_quant_tile(const char* __restrict__ src
             for (int i = 0; i < V; ++i) {
                 qb[i] = mx_quotient_bits(pack_bits<KIn>(p[j], i), inv);
                 mag[i] = (uint32_t)encode_mag_fp(qb[i], f);
+            }
+            if constexpr (MODE == MODE_HWPACK) {
+                // a block holding a magnitude the hardware format reads as NaN/Inf (reference E4M3 0x7F,
+                // reference E5M2 exponent 31) is stored as (scale + 1, elements / 2)
+                constexpr uint32_t hw_max = (F{}.eb() == 4) ? 0x7Eu : 0x7Bu;
+                uint32_t bad = 0;
+#pragma unroll
+                for (int i = 0; i < V; ++i) bad |= (mag[i] > hw_max) ? 1u : 0u;
+                // only the lanes of this block take part: other groups may sit in another branch or be past the end
+                const uint32_t group_mask = ((G == 8) ? 0xFFu : 0xFu) << (lane & ~(G - 1));
+#pragma unroll
+                for (int o = 1; o < G; o <<= 1) bad |= __shfl_xor_sync(group_mask, bad, o);
+                if (bad) {
+#pragma unroll
+                    for (int i = 0; i < V; ++i)
+                        mag[i] = (mag[i] >= (2u << f.fb())) ? mag[i] - (1u << f.fb()) : (mag[i] + ((mag[i] >> 1) & 1u)) >> 1;
+                }
+                if (sub == 0) {
+                    const uint32_t sb = (h >> 8) & 0xFFu;
+                    scales[sf_chunk_offset((uint32_t)((first + (int64_t)j * kThreads) / G), geom)] = (uint8_t)((bad && sb < 255u) ? sb + 1u : sb);
+                }
             }
             if constexpr (WRITE_CODES) {
                 Pack<V> o;
@@ -372,6 +416,12 @@ __device__ __forceinline__ void mxfp_b32_quant_tile(const char* __restrict__ src
             uint32_t code[V];
 #pragma unroll
             for (int i = 0; i < V; ++i) code[i] = mx_encode(pack_bits<KIn>(p[j], i), 128, f);
+            if constexpr (MODE == MODE_HWPACK) {
+                // Inf/NaN block: scale byte 255 is NaN for the tensor cores too; the codes do not matter
+#pragma unroll
+                for (int i = 0; i < V; ++i) code[i] = 0;
+                if (sub == 0) scales[sf_chunk_offset((uint32_t)((first + (int64_t)j * kThreads) / G), geom)] = 255;
+            }
             if constexpr (WRITE_CODES) {
                 Pack<V> o;
 #pragma unroll
@@ -388,18 +438,18 @@ __device__ __forceinline__ void mxfp_b32_quant_tile(const char* __restrict__ src
     }
 }
 
-template <class KIn, class F, int U, bool WRITE_CODES>
+template <class KIn, class F, int U, int MODE>
 __global__ void __launch_bounds__(kThreads) mxfp_b32_quant_kernel(const void* __restrict__ x, uint8_t* __restrict__ scales,
                                                                   uint8_t* __restrict__ elements, void* __restrict__ out,
-                                                                  int64_t n_vec, F f) {
+                                                                  int64_t n_vec, F f, PackGeom geom) {
     constexpr int V = 16 / KIn::size;
     const int64_t first = (int64_t)blockIdx.x * (kThreads * U) + threadIdx.x;
     const char* src = reinterpret_cast<const char*>(x) + first * 16;
-    char* dst = WRITE_CODES ? reinterpret_cast<char*>(elements) + first * V : reinterpret_cast<char*>(out) + first * 16;
+    char* dst = MODE != MODE_QDQ ? reinterpret_cast<char*>(elements) + first * V : reinterpret_cast<char*>(out) + first * 16;
     if ((int64_t)(blockIdx.x + 1) * (kThreads * U) <= n_vec)
-        mxfp_b32_quant_tile<KIn, F, U, WRITE_CODES, true>(src, scales, dst, first, 0, f);
+        mxfp_b32_quant_tile<KIn, F, U, MODE, true>(src, scales, dst, first, 0, f, geom);
     else
-        mxfp_b32_quant_tile<KIn, F, U, WRITE_CODES, false>(src, scales, dst, first, n_vec - first, f);
+        mxfp_b32_quant_tile<KIn, F, U, MODE, false>(src, scales, dst, first, n_vec - first, f, geom);
 }
 
 template <class KOut, class F, int U>
@@ -569,8 +619,8 @@ static int mxfp_quant_dispatch(const void* x, int x_dtype, uint8_t* scales, uint
                     constexpr int U = 4;
                     const int64_t n_vec = n / V;
                     const int64_t grid = (n_vec + kThreads * U - 1) / (kThreads * U);
-                    mxfp_b32_quant_kernel<KIn, decltype(f), U, WRITE_CODES><<<(unsigned)grid, kThreads, 0, st>>>(
-                        x, scales, elements, out, n_vec, f);
+                    mxfp_b32_quant_kernel<KIn, decltype(f), U, WRITE_CODES ? MODE_CODES : MODE_QDQ><<<(unsigned)grid, kThreads, 0, st>>>(
+                        x, scales, elements, out, n_vec, f, PackGeom{});
                     rc = check_launch();
                 });
             };
@@ -643,3 +693,41 @@ extern "C" int mxq_mxfp_compose(const uint8_t* scales, const uint8_t* elements, 
     });
     return rc;
 }
+
+// Quantise a [M, K] activation to MXFP8 (32-element blocks along K) straight into the tensor-core
+// operand layout of mxq_gemm.cu: hardware FP8 codes [M, K] and left-operand scale-factor chunks.
+// One pass over x instead of extract + pack. Declared in mxq_internal.h; returns MXQ_ESIZE when the
+// format / alignment is not covered so the caller can take the two-kernel route.
+namespace mxq {
+int quantize_pack_left_operand(const void* x, int x_dtype, int64_t M, int64_t K, int eb, int fb, uint8_t* hw_codes,
+                               uint8_t* hw_sf, int64_t sf_bytes, int* hw_format, cudaStream_t st) {
+    const bool e4m3 = (eb == 4 && fb == 3), e5m2 = (eb == 5 && fb == 2);
+    if (!(e4m3 || e5m2) || K % 32 != 0 || M * K / 32 >= (1ll << 31)) return MXQ_ESIZE;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(hw_codes)) % 16 != 0) return MXQ_ESIZE;
+    *hw_format = e5m2 ? 1 : 0;
+    // padding rows / K blocks of the chunked scale array must read as 2^0
+    if (cudaMemsetAsync(hw_sf, 127, (size_t)sf_bytes, st) != cudaSuccess) return check_launch();
+    PackGeom g;
+    g.kbpr = (uint32_t)(K / 32);
+    g.shift = 0;
+    while ((1u << g.shift) < g.kbpr) ++g.shift;
+    g.magic = (uint32_t)((((uint64_t)1 << (31 + g.shift)) + g.kbpr - 1) / g.kbpr);
+    g.KT = (uint32_t)((K + 127) / 128);
+    int rc = MXQ_OK;
+    with_kind(x_dtype, [&](auto kin) {
+        using KIn = decltype(kin);
+        constexpr int V = 16 / KIn::size;
+        constexpr int U = 4;
+        const int64_t n_vec = M * K / V;
+        const int64_t grid = (n_vec + kThreads * U - 1) / (kThreads * U);
+        if (e4m3)
+            mxfp_b32_quant_kernel<KIn, FmtCT<4, 3, true, RM_RN>, U, MODE_HWPACK><<<(unsigned)grid, kThreads, 0, st>>>(
+                x, hw_sf, hw_codes, nullptr, n_vec, FmtCT<4, 3, true, RM_RN>{}, g);
+        else
+            mxfp_b32_quant_kernel<KIn, FmtCT<5, 2, true, RM_RN>, U, MODE_HWPACK><<<(unsigned)grid, kThreads, 0, st>>>(
+                x, hw_sf, hw_codes, nullptr, n_vec, FmtCT<5, 2, true, RM_RN>{}, g);
+        rc = check_launch();
+    });
+    return rc;
+}
+}  // namespace mxq

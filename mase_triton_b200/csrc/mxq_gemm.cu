@@ -206,12 +206,12 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t ring = (raw + 1023u) & ~1023u;                    // 1024-aligned operand ring
     uint8_t* ring_ptr = smem_raw + (ring - raw);
-    const uint32_t bars = ring + STAGES * C::STAGE_BYTES;            // full[S], empty[S], accum_full, tmem_empty, tmem slot
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ring_ptr + STAGES * C::STAGE_BYTES + 8 * (2 * STAGES + 2));
+    const uint32_t bars = ring + STAGES * C::STAGE_BYTES;            // full[S], empty[S], accum_full, tmem_empty[2], tmem slot
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ring_ptr + STAGES * C::STAGE_BYTES + 8 * (2 * STAGES + 3));
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
     const uint32_t accum_bar = bars + 8u * (2 * STAGES);
-    const uint32_t tmem_empty_bar = bars + 8u * (2 * STAGES + 1);
+    auto tmem_empty_bar = [&](int h) { return bars + 8u * (2 * STAGES + 1 + h); };   // one per accumulator
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KT = (K + BK - 1) / BK;
@@ -221,7 +221,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         mbar_init(accum_bar, 1);
-        mbar_init(tmem_empty_bar, 4);                                // one arrival per epilogue warp
+        mbar_init(tmem_empty_bar(0), 4);                             // one arrival per epilogue warp
+        mbar_init(tmem_empty_bar(1), 4);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -263,36 +264,38 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         bool ok = true;
         uint32_t it = 0, tcount = 0;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
-            // the epilogue must have drained the accumulators of the previous tile
-            if (tcount > 0) ok = mbar_wait(tmem_empty_bar, (tcount - 1) & 1, status, ST_MMA_TIMEOUT);
-            tc_fence_after();
             for (int kt = 0; kt < KT && ok; ++kt, ++it) {
                 const int s = it % STAGES;
                 ok = mbar_wait(full_bar(s), (it / STAGES) & 1, status, ST_MMA_TIMEOUT);
-                tc_fence_after();
-                if (ok && lane == 0) {
-                    const uint32_t st = ring + s * C::STAGE_BYTES;
-                    const uint32_t sf = st + C::A_BYTES + B_BYTES;
+                const uint32_t st = ring + s * C::STAGE_BYTES;
+                const uint32_t sf = st + C::A_BYTES + B_BYTES;
+                const uint64_t b_desc = smem_desc(st + C::A_BYTES, 16, 1024, LAYOUT_SW128);
 #pragma unroll
-                    for (int h = 0; h < MH; ++h) tmem_cp_32x128b(tmem_base + SFA_COL + 4 * h, smem_desc(sf + 512 * h, 0, 128, LAYOUT_NONE));
-                    tmem_cp_32x128b(tmem_base + SFB_COL, smem_desc(sf + 1024, 0, 128, LAYOUT_NONE));
-                    tmem_cp_32x128b(tmem_base + SFB_COL + 4, smem_desc(sf + 1536, 0, 128, LAYOUT_NONE));
-                    const uint64_t b_desc = smem_desc(st + C::A_BYTES, 16, 1024, LAYOUT_SW128);
+                for (int h = 0; h < MH; ++h) {
+                    // the first MMA into an accumulator overwrites it: the epilogue must have drained that
+                    // accumulator of the previous tile (accumulator 1 is still being read while 0 refills)
+                    if (kt == 0 && tcount > 0 && ok) ok = mbar_wait(tmem_empty_bar(h), (tcount - 1) & 1, status, ST_MMA_TIMEOUT);
+                    tc_fence_after();
+                    if (ok && lane == 0) {
+                        if (h == 0) {
 #pragma unroll
-                    for (uint32_t k = 0; k < BK / 32; ++k) {
-                        // +32 bytes along K inside the 128-byte swizzle span = +2 in the address field;
-                        // scale-factor byte k of each 32-bit TMEM column
-                        const uint32_t idesc = idesc_base | (k << 29) | (k << 4);
+                            for (int hh = 0; hh < MH; ++hh) tmem_cp_32x128b(tmem_base + SFA_COL + 4 * hh, smem_desc(sf + 512 * hh, 0, 128, LAYOUT_NONE));
+                            tmem_cp_32x128b(tmem_base + SFB_COL, smem_desc(sf + 1024, 0, 128, LAYOUT_NONE));
+                            tmem_cp_32x128b(tmem_base + SFB_COL + 4, smem_desc(sf + 1536, 0, 128, LAYOUT_NONE));
+                        }
+                        const uint64_t a_desc = smem_desc(st + h * 16384, 16, 1024, LAYOUT_SW128);
 #pragma unroll
-                        for (int h = 0; h < MH; ++h) {
-                            const uint64_t a_desc = smem_desc(st + h * 16384, 16, 1024, LAYOUT_SW128);
+                        for (uint32_t k = 0; k < BK / 32; ++k) {
+                            // +32 bytes along K inside the 128-byte swizzle span = +2 in the address field;
+                            // scale-factor byte k of each 32-bit TMEM column
+                            const uint32_t idesc = idesc_base | (k << 29) | (k << 4);
                             mma_mxf8f6f4(tmem_base + h * BN, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_base + SFA_COL + 4 * h,
                                          tmem_base + SFB_COL, (kt > 0 || k > 0) ? 1u : 0u);
                         }
+                        if (h == MH - 1) mma_commit(empty_bar(s));     // frees the stage once these MMAs have read it
                     }
-                    mma_commit(empty_bar(s));             // frees the stage once these MMAs have read it
+                    __syncwarp();
                 }
-                __syncwarp();
             }
             if (lane == 0) mma_commit(accum_bar);         // accumulators of this tile complete (or unwinding)
             __syncwarp();
@@ -316,11 +319,11 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     uint32_t r[32];
                     tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + h * BN + c * 32, r);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (h == MH - 1 && c == BN / 32 - 1) {
-                        // last read of this tile's accumulators: hand tensor memory back to the MMA warp
+                    if (c == BN / 32 - 1) {
+                        // last read of this accumulator: hand it back to the MMA warp
                         tc_fence_before();
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(tmem_empty_bar);
+                        if (lane == 0) mbar_arrive(tmem_empty_bar(h));
                     }
                     store_chunk<OUT_DT>(out, bias, r, row, nt * BN + c * 32, M, N);
                 }
@@ -539,7 +542,13 @@ static int linear_with_scratch(const void* x, int x_dtype, int64_t M, int64_t K,
     uint8_t* codes = scratch;
     uint8_t* ref_scales = codes + M * K;
     uint8_t* sf = ref_scales + ((M * K / 32 + 255) / 256) * 256;
-    int rc = mxq_mxfp_extract(x, x_dtype, ref_scales, codes, M * K, 32, x_eb, x_fb, 1, MXQ_RN, stream);
+    int x_fmt = 0;
+    // MXFP8 activations: one pass straight into the operand layout; other formats take extract + pack
+    int rc = quantize_pack_left_operand(x, x_dtype, M, K, x_eb, x_fb, codes, sf, mxq_mx_sf_bytes(M, K, MXQ_OPERAND_A), &x_fmt,
+                                        (cudaStream_t)stream);
+    if (rc == MXQ_OK) return mxq_mx_gemm(codes, sf, x_fmt, w_codes, w_sf, w_hw_format, out, out_dtype, bias, M, N, K, status, stream);
+    if (rc != MXQ_ESIZE) return rc;
+    rc = mxq_mxfp_extract(x, x_dtype, ref_scales, codes, M * K, 32, x_eb, x_fb, 1, MXQ_RN, stream);
     if (rc != MXQ_OK) return rc;
     int x_hw_format = 0;
     rc = mxq_mx_pack_operand(ref_scales, codes, M, K, x_eb, x_fb, MXQ_OPERAND_A, codes, sf, &x_hw_format, stream);
@@ -603,4 +612,11 @@ extern "C" int mxq_mx_linear_static(const void* x, int x_dtype, int64_t M, int64
     // nothing has to be cleared between calls
     return linear_with_scratch(x, x_dtype, M, K, x_exp_bits, x_frac_bits, w_codes, w_sf, w_hw_format, N, out, out_dtype, bias,
                                scratch, status, stream);
+}
+
+extern "C" int mxq_mx_quantize_pack(const void* x, int x_dtype, int64_t M, int64_t K, int exp_bits, int frac_bits,
+                                    uint8_t* hw_codes, uint8_t* hw_sf, int* hw_format, void* stream) {
+    if (!x || !hw_codes || !hw_sf || !hw_format || M <= 0 || K <= 0 || K % 32 != 0) return MXQ_EINVAL;
+    return quantize_pack_left_operand(x, x_dtype, M, K, exp_bits, frac_bits, hw_codes, hw_sf, mxq_mx_sf_bytes(M, K, MXQ_OPERAND_A),
+                                      hw_format, (cudaStream_t)stream);
 }

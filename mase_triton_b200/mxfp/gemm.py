@@ -83,6 +83,23 @@ def quantize_pack(x: Tensor, meta: MXFPMeta, operand: int = OPERAND_A) -> Packed
     return pack_operand(scales, elements, rows, K, meta, operand)
 
 
+def quantize_pack_fused(x: Tensor, meta: MXFPMeta) -> PackedOperand:
+    """One-kernel version of :func:`quantize_pack` for a left operand with MXFP8 elements."""
+    _lib.require_cuda(x, "quantize_pack_fused")
+    K = x.shape[-1]
+    rows = x.numel() // K
+    x2 = x.reshape(rows, K).contiguous()
+    L = _lib.load()
+    codes = torch.empty((rows, K), dtype=torch.uint8, device=x.device)
+    sf = torch.empty((L.mxq_mx_sf_bytes(rows, K, OPERAND_A),), dtype=torch.uint8, device=x.device)
+    fmt = ctypes.c_int(0)
+    with torch.cuda.device(x.device):
+        rc = L.mxq_mx_quantize_pack(x2.data_ptr(), _lib.DTYPE_ID[x2.dtype], rows, K, meta.element_exp_bits, meta.element_frac_bits,
+                                    codes.data_ptr(), sf.data_ptr(), ctypes.addressof(fmt), _lib.stream_ptr(x.device))
+    _lib.check(rc, "mxq_mx_quantize_pack")
+    return PackedOperand(codes, sf, fmt.value, rows, K, OPERAND_A)
+
+
 def packed_weight(w_scales: Tensor, w_elements: Tensor, shape: tuple[int, int], meta: MXFPMeta) -> PackedOperand:
     """Packed form of a quantised weight.  The result is kept on the ``w_elements`` tensor object itself
     (so it dies with it and can never be confused with another tensor that re-uses the same address)

@@ -104,3 +104,17 @@ def test_fused_linear_matches_separate(lib):
     # 3-D activations keep their leading dims
     y3 = fus(x.reshape(4, 256, K))
     assert y3.shape == (4, 256, N) and torch.equal(y3.reshape(M, N), y_fus)
+
+
+@pytest.mark.parametrize("meta", [MXFP8_E4M3_fn, MXFP8_E5M2_fn], ids=lambda m: m.tag)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("shape", [(512, 1024), (300, 160), (1, 32), (2050, 4096)])
+def test_one_pass_quantize_pack_equals_two_step(lib, meta, dtype, shape):
+    torch.manual_seed(shape[0])
+    x = (torch.randn(*shape, device=DEV) * torch.exp2(torch.randint(-6, 6, (shape[0], 1), device=DEV).float())).to(dtype)
+    x[0, :4] = torch.tensor([0.0, -0.0, 1e-30, -1e-30], dtype=dtype)
+    two = G.quantize_pack(x, meta)
+    one = G.quantize_pack_fused(x, meta)
+    assert one.hw_format == two.hw_format
+    assert torch.equal(one.codes, two.codes)
+    assert torch.equal(one.sf, two.sf)
