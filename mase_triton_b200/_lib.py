@@ -11,7 +11,10 @@ from pathlib import Path
 
 import torch
 
-LIB_PATH = Path(__file__).resolve().parent / "csrc" / "libmxq.so"
+import os
+
+# MXQ_LIB overrides the in-tree build (for comparing two builds of the library)
+LIB_PATH = Path(os.environ.get("MXQ_LIB") or (Path(__file__).resolve().parent / "csrc" / "libmxq.so"))
 
 DTYPE_ID = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 ROUND_ID = {"rn": 0, "ru": 1, "rd": 2, "rz": 3}
