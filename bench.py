@@ -114,6 +114,7 @@ def dist_setup(n_gpus: int):
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")     # keep stdout for the one JSON line
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         return dist, rank, world, local
@@ -126,6 +127,7 @@ def cpu_baseline(sample_rows: int = 8192, reps: int = 3) -> dict:
     from mase_triton_b200 import synthetic
     from types import SimpleNamespace
     meta = SimpleNamespace(exp_bits=5, frac_bits=2, is_finite=True, round_mode="rn")
+    oracle.set_num_threads(os.cpu_count() or 1)
     x = synthetic.cfg2_minifloat_fp32(rows=slice(0, sample_rows))
     oracle.quantize_dequantize_minifloat(x[:64], meta)
     ts = []
@@ -146,6 +148,7 @@ def run_reference(args) -> None:
     from mase_triton_b200 import synthetic
     from types import SimpleNamespace
     meta = SimpleNamespace(exp_bits=5, frac_bits=2, is_finite=True, round_mode="rn")
+    oracle.set_num_threads(os.cpu_count() or 1)        # torchrun exports OMP_NUM_THREADS=1
     x = synthetic.cfg2_minifloat_fp32()
     for _ in range(max(1, args.warmup)):
         oracle.quantize_dequantize_minifloat(x[:1024], meta)

@@ -48,6 +48,8 @@ def lib() -> ctypes.CDLL:
         L.mxq_oracle_log2_roundup_count.argtypes = [i]
         L.mxq_oracle_log2_roundup_count.restype = i
         L.mxq_oracle_num_threads.restype = i
+        L.mxq_oracle_set_num_threads.argtypes = [i]
+        L.mxq_oracle_set_num_threads.restype = None
         for name in ("minifloat_extract", "minifloat_compose", "minifloat_qdq", "mxfp_extract", "mxfp_compose"):
             getattr(L, f"mxq_oracle_{name}").restype = None
         _lib = L
@@ -56,6 +58,11 @@ def lib() -> ctypes.CDLL:
 
 def num_threads() -> int:
     return lib().mxq_oracle_num_threads()
+
+
+def set_num_threads(n: int) -> None:
+    """OpenMP threads used by the oracle (launchers such as torchrun export OMP_NUM_THREADS=1)."""
+    lib().mxq_oracle_set_num_threads(int(n))
 
 
 def _fmt(meta):

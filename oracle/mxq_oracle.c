@@ -242,6 +242,15 @@ void mxq_oracle_mxfp_compose(const uint8_t* scales, const uint8_t* elements, flo
     }
 }
 
+void mxq_oracle_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int mxq_oracle_num_threads(void)
 {
 #ifdef _OPENMP
