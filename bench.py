@@ -58,7 +58,7 @@ def measured_peaks() -> tuple[float, str]:
 class ClockSampler:
     """Samples SM clock / throttle reasons of one GPU with NVML while a region runs."""
 
-    def __init__(self, index: int, period_s: float = 0.02):
+    def __init__(self, index: int, period_s: float = 0.004):
         self.index, self.period = index, period_s
         self.samples: list[tuple[float, int, int]] = []
         self.sm_max = None

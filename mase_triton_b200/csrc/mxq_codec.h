@@ -175,7 +175,8 @@ MXQ_HD int encode_mag_fp(uint32_t qb, const F& f) {
     const int fr = mad_add((int)f32_bits(add_rn(m, bits_f32(cbits))), -(int)(cbits + (1u << fb)));   // 0 .. 2^fb
     int code = mad_add((int)(((qb >> sh) & (0xFFu << fb)) | (uint32_t)fr), -((127 - bias) << fb));
     code = code < 0 ? 0 : code;                                            // biased exponent < 0
-    if ((qb & 0x7FFFFFFFu) < ((uint32_t)(128 - bias) << 23))               // biased exponent <= 0
+    // biased exponent <= 0, i.e. |q| < 2^(1-bias): one float compare with |.| (q is never NaN here)
+    if (__builtin_fabsf(bits_f32(qb)) < bits_f32((uint32_t)(128 - bias) << 23))
         code = (int)((subnormal_table<fb>() >> (code * rt_k(1))) & 0xFu);
     (void)f;
     return code;

@@ -118,3 +118,24 @@ def test_one_pass_quantize_pack_equals_two_step(lib, meta, dtype, shape):
     assert one.hw_format == two.hw_format
     assert torch.equal(one.codes, two.codes)
     assert torch.equal(one.sf, two.sf)
+
+
+@pytest.mark.parametrize("x_meta,w_meta", [(MXFP8_E4M3_fn, MXFP8_E4M3_fn), (MXFP8_E5M2_fn, OCP_MXFP6_E2M3), (OCP_MXFP4_E2M1, OCP_MXFP6_E3M2)],
+                         ids=["e4m3-e4m3", "e5m2-e2m3", "e2m1-e3m2"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_fused_matmul_matches_separate(lib, x_meta, w_meta, dtype):
+    """mxfp_matmul(backend="fused") on batched operands (reference shapes of test/test_mxfp_functional.py:183-265)."""
+    torch.manual_seed(9)
+    a = (torch.randn((2, 3, 128, 512), device=DEV) * 5).to(dtype)
+    b = (torch.randn((2, 3, 512, 256), device=DEV) * 3).to(dtype)
+    y_sep = MX.mxfp_matmul(a, b, x_meta, w_meta, "XqWq", "separate")
+    y_fus = MX.mxfp_matmul(a, b, x_meta, w_meta, "XqWq", "fused")
+    G.check_status(DEV)
+    assert y_fus.shape == y_sep.shape == (2, 3, 128, 256) and y_fus.dtype == dtype
+    a_dq = MX.quantize_dequantize(a, -1, x_meta, torch.float32)
+    b_dq = MX.quantize_dequantize(b, -2, w_meta, torch.float32)
+    assert within_tolerance(y_fus, torch.matmul(a_dq, b_dq))
+    # a 2-D right operand is shared by every batch entry
+    y2 = MX.mxfp_matmul(a, b[0, 0], x_meta, w_meta, "XqWq", "fused")
+    G.check_status(DEV)
+    assert within_tolerance(y2, torch.matmul(a_dq, b_dq[0, 0]))
