@@ -409,7 +409,25 @@ def small_cases():
         layer = MXFPLinearPTQ.from_linear(fc, MXFP8_E4M3_fn, MXFP8_E4M3_fn, None, "XqWqB", "fused" if which == "linear" else "separate")
         return (lambda: layer(x)), flops
 
+    def strided_case(gen, meta, s_in, which, route):
+        """blocks along dim 0 of an [8192, 8192] tensor: the strided kernels against the permuted-copy route"""
+        from mase_triton_b200.mxfp.helpers import flatten_for_quantize, permute_for_dequantize
+        x = gen(shape=(8192, 8192)).to(dev)
+        n = x.numel()
+        if which == "extract":
+            if route == "strided":
+                return (lambda: mxk.extract_mxfp_components_strided(x, 0, meta)), n * (s_in + 1 + 1 / 32)
+            return (lambda: mxk.extract_mxfp_components(flatten_for_quantize(x, 0), meta)), n * (s_in + 1 + 1 / 32)
+        if route == "strided":
+            return (lambda: mxk.quantize_dequantize_strided(x, 0, meta, x.dtype)), n * 2 * s_in
+        return (lambda: permute_for_dequantize(mxk.quantize_dequantize(flatten_for_quantize(x, 0), meta, x.dtype),
+                                               tuple(x.shape), 0).contiguous()), n * 2 * s_in
+
     cases = {"minifloat_qdq_f32": minifloat_qdq_f32}
+    for which in ("extract", "qdq"):
+        for route in ("strided", "permuted"):
+            cases[f"mxfp8_{which}_dim0_{route}_f32"] = (lambda w=which, r=route: strided_case(synthetic.cfg1_mxfp8_fp32, MXFP8_E4M3_fn, 4, w, r))
+            cases[f"mxfp4_{which}_dim0_{route}_bf16"] = (lambda w=which, r=route: strided_case(synthetic.cfg3_mxfp4_bf16, OCP_MXFP4_E2M1, 2, w, r))
     for which in ("gemm", "linear", "separate"):
         cases[f"mx_{which}_small"] = (lambda w=which: gemm_case(2048, 4096, 4096, w))
         cases[f"mx_{which}_cfg4"] = (lambda w=which: gemm_case(8192, 14336, 4096, w))

@@ -100,6 +100,28 @@ int mxq_mxfp_qdq(const void* x, int x_dtype, void* out, int out_dtype, int64_t n
                  void* stream);
 
 /*
+ * ---- MXFP with blocks along a dimension that is not the contiguous one ----
+ * The tensor is [outer, D, inner] (row-major, contiguous) and the blocks run along D.  The three
+ * functions give the bytes the reference produces by first moving D last with a permute + copy
+ * (flatten_for_quantize / permute_for_dequantize, src/mase_triton/mxfp/helpers.py:4-47, called from
+ * src/mase_triton/mxfp/functional/cast.py:36-38,97-99) and then running the flat functions above:
+ *   elements[(o * inner + i) * D + j], scales[(o * inner + i) * (D / block_size) + j / block_size]
+ * while x / out keep the original layout, so no permuted copy is made.
+ * They return MXQ_ESIZE for what they do not cover (block_size != 32, D % 32 != 0, a format or
+ * rounding mode outside the round-to-nearest presets, out_dtype != x_dtype for the fused form,
+ * unaligned buffers); the caller then takes the permute + flat route.
+ */
+int mxq_mxfp_extract_strided(const void* x, int x_dtype, uint8_t* scales, uint8_t* elements, int64_t outer,
+                             int64_t D, int64_t inner, int block_size, int exp_bits, int frac_bits,
+                             int is_finite, int round_mode, void* stream);
+int mxq_mxfp_compose_strided(const uint8_t* scales, const uint8_t* elements, void* out, int out_dtype,
+                             int64_t outer, int64_t D, int64_t inner, int block_size, int exp_bits,
+                             int frac_bits, int is_finite, void* stream);
+int mxq_mxfp_qdq_strided(const void* x, int x_dtype, void* out, int out_dtype, int64_t outer, int64_t D,
+                         int64_t inner, int block_size, int exp_bits, int frac_bits, int is_finite,
+                         int round_mode, void* stream);
+
+/*
  * ---- MX GEMM (tcgen05 block-scaled tensor-core path) ----
  * Together these replace the "dequantise, then cuBLAS" sequence of mxfp_linear_XqWq / mxfp_matmul
  * (src/mase_triton/mxfp/functional/linear.py:36-64, matmul.py:10-35); the reference's own "fused"

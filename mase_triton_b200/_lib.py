@@ -28,6 +28,9 @@ SIGNATURES = {
     "mxq_mxfp_extract": [_p, _i, _p, _p, _i64, _i, _i, _i, _i, _i, _p],
     "mxq_mxfp_compose": [_p, _p, _p, _i, _i64, _i, _i, _i, _i, _p],
     "mxq_mxfp_qdq": [_p, _i, _p, _i, _i64, _i, _i, _i, _i, _i, _p],
+    "mxq_mxfp_extract_strided": [_p, _i, _p, _p, _i64, _i64, _i64, _i, _i, _i, _i, _i, _p],
+    "mxq_mxfp_compose_strided": [_p, _p, _p, _i, _i64, _i64, _i64, _i, _i, _i, _i, _p],
+    "mxq_mxfp_qdq_strided": [_p, _i, _p, _i, _i64, _i64, _i64, _i, _i, _i, _i, _i, _p],
     "mxq_mx_pack_operand": [_p, _p, _i64, _i64, _i, _i, _i, _p, _p, _p, _p],
     "mxq_mx_quantize_pack": [_p, _i, _i64, _i64, _i, _i, _p, _p, _p, _p],
     "mxq_mx_gemm": [_p, _p, _i, _p, _p, _i, _p, _i, _p, _i64, _i64, _i64, _p, _p],

@@ -10,6 +10,13 @@ from ..helpers import flatten_for_quantize, permute_for_dequantize
 from ..meta import MXFPMeta, MXFPTensorMeta
 
 
+def _blocks_are_strided(shape, block_dim: int) -> bool:
+    """True when some dimension after ``block_dim`` has more than one entry, i.e. the reference would
+    need a permuted copy to make the blocks contiguous."""
+    d = block_dim % len(shape)
+    return any(s != 1 for s in tuple(shape)[d + 1:])
+
+
 def extract_mxfp_components(tensor: Tensor, block_dim: int, mxfp_meta: MXFPMeta) -> tuple[Tensor, Tensor, MXFPTensorMeta]:
     """Quantise ``tensor`` with 1-D blocks running along ``block_dim``.
 
@@ -19,7 +26,12 @@ def extract_mxfp_components(tensor: Tensor, block_dim: int, mxfp_meta: MXFPMeta)
     """
     ndim = tensor.ndim
     assert -ndim <= block_dim < ndim
-    scales, elements = kernels.extract_mxfp_components(flatten_for_quantize(tensor, block_dim), mxfp_meta=mxfp_meta)
+    pair = None
+    if _blocks_are_strided(tensor.shape, block_dim) and tensor.is_cuda:
+        pair = kernels.extract_mxfp_components_strided(tensor, block_dim % ndim, mxfp_meta)
+    if pair is None:
+        pair = kernels.extract_mxfp_components(flatten_for_quantize(tensor, block_dim), mxfp_meta=mxfp_meta)
+    scales, elements = pair
     tensor_meta = MXFPTensorMeta(device=tensor.device, dtype=tensor.dtype, shape=tensor.shape,
                                  block_dim=block_dim, meta=mxfp_meta)
     return scales, elements, tensor_meta
@@ -34,6 +46,12 @@ def compose_mxfp_tensor(scales: Tensor, elements: Tensor, tensor_meta: MXFPTenso
     """Dequantise to the original shape; ``output_dtype`` defaults to the recorded source dtype."""
     if output_dtype is None:
         output_dtype = getattr(torch, tensor_meta.dtype)
+    shape = tuple(tensor_meta.shape)
+    if _blocks_are_strided(shape, tensor_meta.block_dim) and elements.is_cuda:
+        out = kernels.compose_mxfp_tensor_strided(scales, elements, shape, tensor_meta.block_dim % len(shape),
+                                                  tensor_meta.meta, output_dtype)
+        if out is not None:
+            return out
     flat = kernels.compose_mxfp_tensor(scales=scales, elements=elements, mxfp_meta=tensor_meta.meta, output_dtype=output_dtype)
     return permute_for_dequantize(flat, ori_shape=tensor_meta.shape, block_dim=tensor_meta.block_dim)
 
@@ -42,6 +60,11 @@ def quantize_dequantize(tensor: Tensor, block_dim: int, mxfp_meta: MXFPMeta, out
     """``compose(extract(tensor))`` in one fused kernel (no codes written to memory)."""
     ndim = tensor.ndim
     assert -ndim <= block_dim < ndim
+    if _blocks_are_strided(tensor.shape, block_dim) and tensor.is_cuda:
+        out = kernels.quantize_dequantize_strided(tensor, block_dim % ndim, mxfp_meta,
+                                                  tensor.dtype if output_dtype is None else output_dtype)
+        if out is not None:
+            return out
     flat = kernels.quantize_dequantize(flatten_for_quantize(tensor, block_dim), mxfp_meta,
                                        tensor.dtype if output_dtype is None else output_dtype)
     return permute_for_dequantize(flat, ori_shape=tuple(tensor.shape), block_dim=block_dim)

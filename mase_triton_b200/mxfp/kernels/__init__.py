@@ -1,1 +1,2 @@
-from .cast import compose_mxfp_tensor, extract_mxfp_components, quantize_dequantize  # noqa: F401
+from .cast import (compose_mxfp_tensor, compose_mxfp_tensor_strided, extract_mxfp_components,  # noqa: F401
+                   extract_mxfp_components_strided, quantize_dequantize, quantize_dequantize_strided)

@@ -257,6 +257,61 @@ def test_public_api_2d_block_dims(lib, meta, block_dim, dtype):
     assert err < (0.3 if meta is OCP_MXFP4_E2M1 else 0.1)
 
 
+# ------------------------------------------------------------------ blocks along a strided dimension
+def _strided_case(shape, dim, dtype, seed):
+    """Adversarial values (specials, zeros, subnormals, wide binades) laid out so that they form blocks
+    along ``dim``; the values come from the same generator as the flat tests."""
+    n = int(np.prod(shape))
+    moved = list(shape[:dim]) + list(shape[dim + 1:]) + [shape[dim]]
+    flat = adversarial_mx_blocks(n // 32, 32, seed=seed).to(dtype)
+    return flat.reshape(moved).movedim(-1, dim).contiguous()
+
+
+@pytest.mark.parametrize("meta", MX_PRESETS, ids=lambda m: m.tag)
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape,dim", [((128, 64), 0), ((32, 200), 0), ((160, 33), 0), ((3, 96, 130), 1), ((2, 64, 5, 7), 1),
+                                        ((256, 1024), 0)], ids=str)
+def test_strided_blocks_match_oracle(lib, meta, dtype, shape, dim):
+    """block_dim that is not the contiguous one: the strided kernels give the bytes of the reference's
+    permute-then-flatten route (mxfp/helpers.py:4-47; the reference tests it at
+    test/test_mxfp_functional.py:127-180)."""
+    x = _strided_case(shape, dim, dtype, seed=5 + len(shape))
+    flat = x.movedim(dim, -1).flatten()
+    s_o, e_o = oracle.extract_mxfp_components(flat, meta)
+    pair = mx_kernels.extract_mxfp_components_strided(x.to(DEV), dim, meta)
+    assert pair is not None, "the strided kernel must cover this case"
+    assert_bits_equal(pair[0], s_o, "scales"); assert_bits_equal(pair[1], e_o, "elements")
+    s, e, tm = MX.extract_mxfp_components(x.to(DEV), dim - len(shape), meta)
+    assert_bits_equal(s, s_o, "scales (public)"); assert_bits_equal(e, e_o, "elements (public)")
+    moved_shape = x.movedim(dim, -1).shape
+    for out_dtype in DTYPES:
+        y_o = oracle.compose_mxfp_tensor(s_o, e_o, meta, out_dtype).reshape(moved_shape).movedim(-1, dim).contiguous()
+        y = mx_kernels.compose_mxfp_tensor_strided(s, e, shape, dim, meta, out_dtype)
+        assert y is not None and y.is_contiguous() and tuple(y.shape) == tuple(shape)
+        assert_bits_equal(y, y_o, f"composed {out_dtype}")
+        assert_bits_equal(MX.compose_mxfp_tensor(s, e, tm, out_dtype).contiguous(), y_o, f"composed {out_dtype} (public)")
+    y_o = oracle.compose_mxfp_tensor(s_o, e_o, meta, dtype).reshape(moved_shape).movedim(-1, dim).contiguous()
+    q = mx_kernels.quantize_dequantize_strided(x.to(DEV), dim, meta, dtype)
+    assert q is not None
+    assert_bits_equal(q, y_o, "fused")
+    assert_bits_equal(MX.quantize_dequantize(x.to(DEV), dim, meta).contiguous(), y_o, "fused (public)")
+
+
+def test_strided_blocks_fall_back_when_not_covered(lib):
+    """Blocks that span columns (D % 32 != 0), other block sizes and rounding modes take the
+    permute + flat route and still match the oracle."""
+    for shape, dim, meta in [((48, 4), 0, mxm(4, 3)), ((64, 6), 0, mxm(4, 3, B=8)), ((64, 6), 0, mxm(2, 1, rm="rz")),
+                             ((64, 6), 0, mxm(5, 2, fin=False))]:
+        x = torch.randn(shape, generator=torch.Generator().manual_seed(1)) * 7
+        flat = x.movedim(dim, -1).flatten()
+        s_o, e_o = oracle.extract_mxfp_components(flat, meta)
+        s, e, tm = MX.extract_mxfp_components(x.to(DEV), dim, meta)
+        assert_bits_equal(s, s_o, "scales"); assert_bits_equal(e, e_o, "elements")
+        y_o = oracle.compose_mxfp_tensor(s_o, e_o, meta, torch.float32).reshape(x.movedim(dim, -1).shape).movedim(-1, dim)
+        assert_bits_equal(MX.compose_mxfp_tensor(s, e, tm).contiguous(), y_o.contiguous(), "composed")
+        assert_bits_equal(MX.quantize_dequantize(x.to(DEV), dim, meta).contiguous(), y_o.contiguous(), "fused")
+
+
 # ------------------------------------------------------------------ full-size configurations, pinned to the reference by digest
 def test_config1_full_size(lib, digests):
     x = synthetic.cfg1_mxfp8_fp32()
