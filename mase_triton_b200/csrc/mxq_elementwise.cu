@@ -139,6 +139,84 @@ __device__ __forceinline__ uint32_t sf_chunk_offset(uint32_t blk, const PackGeom
     return (((r >> 8) * g.KT + (kb >> 2)) * 2u + (lr >> 7)) * 512u + (rr & 31u) * 16u + (rr >> 5) * 4u + (kb & 3u);
 }
 
+// ------------------------------------------------------------------------------------------------
+// MXFP4 (E2M1) elements of bf16 inputs, two elements per 32-bit word on the packed bf16 units.
+// With only eight magnitudes the code is a staircase in the quotient q = |x| * 2^-se (exact in
+// bf16 for a power-of-two factor; below 2^-126 every comparison is false either way):
+//   code = [q>.625] + [q>=1] + [q>1.25] - [q>=1.75] + 2[q>=2] + [q>2.5] + [q>=3.5] + [q>5] - [q>=7]
+// (the two negative steps are the reference's lost mantissa carry at odd exponents,
+// minifloat/fake.py:70, and the first step its single subnormal binade, :56-60).  The sums are kept
+// in bf16 (128 + code, or the decoded value itself for the fused form), so the per-element work is
+// packed compare + add on the fp pipe instead of ~13 integer instructions.
+// An element is kept (else it is +0) when it is not a flushed input and its fp32 quotient does not
+// round to zero: |x| > max(2^(se-150), largest subnormal), one packed comparison against a
+// per-block constant; the sign bit rides along with the kept ones.
+// ------------------------------------------------------------------------------------------------
+struct E2M1Block {
+    uint32_t inv2;    // 2^-se in both halves
+    uint32_t sf2;     // 2^se in both halves (fused form)
+    uint32_t ts2;     // sign threshold in both halves
+};
+
+__device__ __forceinline__ E2M1Block e2m1_block(uint32_t h) {
+    E2M1Block b;
+    const uint32_t sb = (h >> 8) & 0xFFu;
+    b.inv2 = ((h >> 16) & 0x7F80u) * 0x10001u;
+    b.sf2 = (sb == 0u ? 0x0040u : (sb << 7)) * 0x10001u;
+    b.ts2 = (uint32_t)max(((int)sb - 150) * 128, 0x7F) * 0x10001u;
+    return b;
+}
+
+__device__ __forceinline__ __nv_bfloat162 bf2(uint32_t w) { return *reinterpret_cast<__nv_bfloat162*>(&w); }
+__device__ __forceinline__ uint32_t bf2_bits(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
+
+// VALUES = false: 128 + magnitude code per half; true: decoded magnitude per half
+template <bool VALUES>
+__device__ __forceinline__ __nv_bfloat162 e2m1_staircase(__nv_bfloat162 q) {
+    const uint32_t unit = VALUES ? 0x3F003F00u : 0x3F803F80u;      // 0.5 or 1.0: one code step below 2.0
+    const __nv_bfloat162 u = bf2(unit), u2 = bf2(unit + 0x00800080u), u4 = bf2(unit + 0x01000100u);
+    __nv_bfloat162 acc = bf2(VALUES ? 0u : 0x43004300u);
+    acc = __hfma2(__hgt2(q, bf2(0x3F203F20u)), u, acc);            // > 0.625
+    acc = __hfma2(__hge2(q, bf2(0x3F803F80u)), u, acc);            // >= 1
+    acc = __hfma2(__hgt2(q, bf2(0x3FA03FA0u)), u, acc);            // > 1.25
+    acc = __hfma2(__hge2(q, bf2(0x3FE03FE0u)), __hneg2(u), acc);   // >= 1.75 (lost carry)
+    acc = __hfma2(__hge2(q, bf2(0x40004000u)), u2, acc);           // >= 2: code +2, value +1
+    acc = __hfma2(__hgt2(q, bf2(0x40204020u)), VALUES ? u2 : u, acc);   // > 2.5: code +1, value +1
+    acc = __hfma2(__hge2(q, bf2(0x40604060u)), VALUES ? u2 : u, acc);   // >= 3.5
+    acc = __hfma2(__hgt2(q, bf2(0x40A040A0u)), VALUES ? u4 : u, acc);   // > 5: code +1, value +2
+    acc = __hfma2(__hge2(q, bf2(0x40E040E0u)), __hneg2(VALUES ? u4 : u), acc);   // >= 7 (lost carry)
+    return acc;
+}
+
+// one 16-byte access of a lane (8 bf16 inputs) of a finite block -> 8 code bytes or 8 bf16 results
+template <bool VALUES>
+__device__ __forceinline__ void e2m1_bf16_quantise(const Pack<16>& p, const E2M1Block& b, uint32_t* out) {
+    uint32_t r[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t w = p.w[i];
+        const uint32_t aw = w & 0x7FFF7FFFu;
+        const __nv_bfloat162 q = __hmul2(bf2(aw), bf2(b.inv2));
+        // halves that are flushed inputs or whose fp32 quotient rounds to zero give +0 (code 0)
+        const uint32_t keep = __hgt2_mask(bf2(aw), bf2(b.ts2));
+        const __nv_bfloat162 acc = e2m1_staircase<VALUES>(q);
+        if constexpr (VALUES) {
+            const uint32_t y = bf2_bits(__hmul2(acc, bf2(b.sf2)));
+            r[i] = ((y & 0x7FFF7FFFu) | (w & 0x80008000u)) & keep;
+        } else {
+            // 128 + code has bit 3 of each half clear: drop the sign bit of w there, then mask
+            r[i] = ((bf2_bits(acc) & ~0x00080008u) | ((w >> 12) & 0x00080008u)) & keep & 0x000F000Fu;
+        }
+    }
+    if constexpr (VALUES) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) out[i] = r[i];
+    } else {
+        out[0] = __byte_perm(r[0], r[1], 0x6420);
+        out[1] = __byte_perm(r[2], r[3], 0x6420);
+    }
+}
+
 template <class KIn, class F, int U, int MODE, bool FULL>
 __device__ __forceinline__ void mxfp_b32_quant_tile(const char* __restrict__ src, uint8_t* __restrict__ scales,
                                                     char* __restrict__ dst, int64_t first, int64_t left, const F& f,
@@ -177,6 +255,21 @@ __device__ __forceinline__ void mxfp_b32_quant_tile(const char* __restrict__ src
         const uint32_t h = __shfl_sync(0xFFFFFFFFu, hdr, (lane & ~(G - 1)) + j);
         if (!FULL && j * kThreads >= left) continue;
         char* d = dst + (size_t)j * kThreads * OB;
+        if constexpr (std::is_same<KIn, KBF16>::value && F{}.eb() == 2 && F{}.fb() == 1 && MODE != MODE_HWPACK) {
+            if (!(h & 1u)) {
+                const E2M1Block b = e2m1_block(h);
+                if constexpr (WRITE_CODES) {
+                    Pack<V> o;
+                    e2m1_bf16_quantise<false>(p[j], b, o.w);
+                    store_pack<V>(d, o);
+                } else {
+                    Pack<16> o;
+                    e2m1_bf16_quantise<true>(p[j], b, o.w);
+                    store_pack<16>(d, o);
+                }
+                continue;
+            }
+        }
         if (!(h & 1u)) {
             const float inv = __uint_as_float(h & 0x7F800000u);
             uint32_t qb[V], mag[V];

@@ -42,6 +42,54 @@ __device__ __forceinline__ uint32_t load_cols(const char* p) {
     else return (uint32_t)__ldcs(reinterpret_cast<const unsigned short*>(p));
 }
 
+// fp32 bits of max |x| down each column of a thread (any NaN wins); packed 16-bit maxima when a
+// thread holds two columns per word
+template <int CPT, class K>
+__device__ __forceinline__ void column_absmax(const uint32_t (&raw)[32], uint32_t (&amax)[CPT]) {
+    if constexpr (CPT == 2 && std::is_same<K, KBF16>::value) {
+        __nv_bfloat162 m = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&raw[0]));
+#pragma unroll
+        for (int k = 1; k < 32; ++k) m = __hmax2_nan(m, __habs2(*reinterpret_cast<const __nv_bfloat162*>(&raw[k])));
+        const uint32_t mw = *reinterpret_cast<uint32_t*>(&m);
+        amax[0] = mw << 16;
+        amax[1] = mw & 0xFFFF0000u;
+    } else if constexpr (CPT == 2) {
+        __half2 m = __habs2(*reinterpret_cast<const __half2*>(&raw[0]));
+#pragma unroll
+        for (int k = 1; k < 32; ++k) m = __hmax2_nan(m, __habs2(*reinterpret_cast<const __half2*>(&raw[k])));
+        const float2 mf = __half22float2(m);
+        amax[0] = __float_as_uint(mf.x);
+        amax[1] = __float_as_uint(mf.y);
+    } else {
+        float m = 0.f;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) m = max_abs_nan(m, __uint_as_float(column_bits<CPT, K>(raw[k], 0)));
+        amax[0] = __float_as_uint(m);
+    }
+}
+
+// the CPT results of one row of a thread -> memory; PLAIN promises that none is NaN
+template <class K, int CPT, bool PLAIN>
+__device__ __forceinline__ void store_row(char* d, const uint32_t (&y)[CPT]) {
+    if constexpr (K::size == 4) {
+        __stcs(reinterpret_cast<unsigned int*>(d), y[0]);
+    } else if constexpr (CPT == 2) {
+        uint32_t w;
+        if constexpr (PLAIN && std::is_same<K, KBF16>::value) {
+            const __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(y[0]), __uint_as_float(y[1]));
+            w = *reinterpret_cast<const uint32_t*>(&hh);
+        } else if constexpr (PLAIN) {
+            const __half2 hh = __floats2half2_rn(__uint_as_float(y[0]), __uint_as_float(y[1]));
+            w = *reinterpret_cast<const uint32_t*>(&hh);
+        } else {
+            w = K::from_bits(y[0]) | (K::from_bits(y[1]) << 16);
+        }
+        __stcs(reinterpret_cast<unsigned int*>(d), w);
+    } else {
+        __stcs(reinterpret_cast<unsigned short*>(d), (unsigned short)K::from_bits(y[0]));
+    }
+}
+
 // decomposes the CTA index into (column tile, block tile, outer index) and returns false for
 // threads that fall outside the tensor
 template <int CPT>
@@ -58,7 +106,7 @@ __device__ __forceinline__ bool strided_position(const StridedGeom& g, int64_t& 
 }
 
 template <class KIn, class F, int CPT, int MODE>
-__global__ void __launch_bounds__(kThreads) mxfp_strided_quant_kernel(const void* __restrict__ x, uint8_t* __restrict__ scales,
+__global__ void __launch_bounds__(kThreads, MODE == MODE_QDQ ? 2 : 1) mxfp_strided_quant_kernel(const void* __restrict__ x, uint8_t* __restrict__ scales,
                                                                       uint8_t* __restrict__ elements, void* __restrict__ out,
                                                                       StridedGeom g, F f) {
     int64_t o, jb, i0;
@@ -70,82 +118,80 @@ __global__ void __launch_bounds__(kThreads) mxfp_strided_quant_kernel(const void
 #pragma unroll
     for (int k = 0; k < 32; ++k) raw[k] = load_cols<KIn, CPT>(src + k * row_bytes);
 
-    uint32_t y[CPT][32];       // MODE_QDQ: results of both columns, written together
-    bool plain_all = true;
+    uint32_t h[CPT];
+    {
+        uint32_t amax[CPT];
+        column_absmax<CPT, KIn>(raw, amax);
 #pragma unroll
-    for (int col = 0; col < CPT; ++col) {
-        float m = 0.f;
+        for (int col = 0; col < CPT; ++col) h[col] = block_header(amax[col], f);
+    }
+    bool special = false;
 #pragma unroll
-        for (int k = 0; k < 32; ++k) m = max_abs_nan(m, __uint_as_float(column_bits<CPT, KIn>(raw[k], col)));
-        const uint32_t h = block_header(__float_as_uint(m), f);
-        const uint32_t sb = (h >> 8) & 0xFFu;
-        const int64_t colidx = o * g.inner + i0 + col;
-        if constexpr (MODE == MODE_CODES) scales[colidx * (g.D / 32) + jb] = (uint8_t)sb;
-        uint32_t words[8];
-        if (!(h & 1u)) {
-            const float inv = __uint_as_float(h & 0x7F800000u);
-            const float sf = scale_from_byte(sb);
-            const float unbias = __uint_as_float((uint32_t)(254 - fmt_bias(f)) << 23);
+    for (int col = 0; col < CPT; ++col) special = special || (h[col] & 1u);
+
+    if constexpr (MODE == MODE_CODES) {
 #pragma unroll
-            for (int k4 = 0; k4 < 32; k4 += 4) {
-                uint32_t qb[4], mag[4];
+        for (int col = 0; col < CPT; ++col) {
+            const int64_t colidx = o * g.inner + i0 + col;
+            scales[colidx * (g.D / 32) + jb] = (uint8_t)(h[col] >> 8);
+            uint32_t words[8];
+            if (!(h[col] & 1u)) {
+                const float inv = __uint_as_float(h[col] & 0x7F800000u);
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    qb[k] = mx_quotient_bits(column_bits<CPT, KIn>(raw[k4 + k], col), inv);
-                    mag[k] = (uint32_t)encode_mag_fp(qb[k], f);
-                }
-                if constexpr (MODE == MODE_CODES) {
-                    words[k4 >> 2] = pack4_codes(mag, qb, f);
-                } else {
+                for (int k4 = 0; k4 < 32; k4 += 4) {
+                    uint32_t qb[4], mag[4];
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        const float v = __fmul_rn(__uint_as_float((uint32_t)((int)mag[k] * rt_k(0)) << (23 - f.fb())), unbias);
-                        y[col][k4 + k] = __float_as_uint(__fmul_rn(v, sf)) | (qb[k] & 0x80000000u);
+                        qb[k] = mx_quotient_bits(column_bits<CPT, KIn>(raw[k4 + k], col), inv);
+                        mag[k] = (uint32_t)encode_mag_fp(qb[k], f);
                     }
+                    words[k4 >> 2] = pack4_codes(mag, qb, f);
                 }
-            }
-        } else {
-            plain_all = false;
-            const float sf = scale_from_byte(sb);
+            } else {
 #pragma unroll
-            for (int k = 0; k < 32; ++k) {
-                const uint32_t code = mx_encode(column_bits<CPT, KIn>(raw[k], col), 128, f);
-                if constexpr (MODE == MODE_CODES) {
+                for (int k = 0; k < 32; ++k) {
+                    const uint32_t code = mx_encode(column_bits<CPT, KIn>(raw[k], col), 128, f);
                     if ((k & 3) == 0) words[k >> 2] = code; else words[k >> 2] |= code << (8 * (k & 3));
-                } else {
-                    y[col][k] = mx_decode(code, sf, f);
                 }
             }
-        }
-        if constexpr (MODE == MODE_CODES) {
             uint4* d = reinterpret_cast<uint4*>(elements + colidx * g.D + jb * 32);
             __stcs(d, make_uint4(words[0], words[1], words[2], words[3]));
             __stcs(d + 1, make_uint4(words[4], words[5], words[6], words[7]));
         }
-    }
-    if constexpr (MODE == MODE_QDQ) {
+    } else {
+        // results leave row by row, both columns of a thread in one store
         char* dst = reinterpret_cast<char*>(out) + first;
+        float inv[CPT], sf[CPT];
+        int se[CPT];
 #pragma unroll
-        for (int k = 0; k < 32; ++k) {
-            char* d = dst + k * row_bytes;
-            if constexpr (KIn::size == 4) {
-                __stcs(reinterpret_cast<unsigned int*>(d), y[0][k]);
-            } else if constexpr (CPT == 2) {
-                uint32_t w;
-                if (plain_all) {
-                    if constexpr (std::is_same<KIn, KBF16>::value) {
-                        const __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(y[0][k]), __uint_as_float(y[1][k]));
-                        w = *reinterpret_cast<const uint32_t*>(&hh);
-                    } else {
-                        const __half2 hh = __floats2half2_rn(__uint_as_float(y[0][k]), __uint_as_float(y[1][k]));
-                        w = *reinterpret_cast<const uint32_t*>(&hh);
-                    }
-                } else {
-                    w = KIn::from_bits(y[0][k]) | (KIn::from_bits(y[1][k]) << 16);
+        for (int col = 0; col < CPT; ++col) {
+            inv[col] = __uint_as_float(h[col] & 0x7F800000u);
+            sf[col] = scale_from_byte((h[col] >> 8) & 0xFFu);
+            se[col] = (h[col] & 1u) ? 128 : 127 - (int)((h[col] >> 23) & 0xFFu);
+        }
+        const float unbias = __uint_as_float((uint32_t)(254 - fmt_bias(f)) << 23);
+        if (!special) {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {
+                uint32_t y[CPT];
+#pragma unroll
+                for (int col = 0; col < CPT; ++col) {
+                    const uint32_t qb = mx_quotient_bits(column_bits<CPT, KIn>(raw[k], col), inv[col]);
+                    const uint32_t mag = (uint32_t)encode_mag_fp(qb, f);
+                    const float v = __fmul_rn(__uint_as_float((uint32_t)((int)mag * rt_k(0)) << (23 - f.fb())), unbias);
+                    y[col] = __float_as_uint(__fmul_rn(v, sf[col])) | (qb & 0x80000000u);
                 }
-                __stcs(reinterpret_cast<unsigned int*>(d), w);
-            } else {
-                __stcs(reinterpret_cast<unsigned short*>(d), (unsigned short)KIn::from_bits(y[0][k]));
+                store_row<KIn, CPT, true>(dst + k * row_bytes, y);
+            }
+        } else {
+            // a column of this thread holds Inf/NaN: element-by-element generic arithmetic for the pair
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {
+                uint32_t y[CPT];
+#pragma unroll
+                for (int col = 0; col < CPT; ++col)
+                    y[col] = mx_decode(mx_encode(column_bits<CPT, KIn>(raw[k], col), se[col], f), sf[col], f);
+                store_row<KIn, CPT, false>(dst + k * row_bytes, y);
             }
         }
     }
@@ -173,35 +219,27 @@ __global__ void __launch_bounds__(kThreads) mxfp_strided_compose_kernel(const ui
     bool plain = true;
 #pragma unroll
     for (int col = 0; col < CPT; ++col) plain = plain && (sb[col] != 255u);
+    float sf[CPT];
 #pragma unroll
-    for (int k = 0; k < 32; ++k) {
-        uint32_t y[CPT];
+    for (int col = 0; col < CPT; ++col) sf[col] = scale_from_byte(sb[col]);
+    if (plain) {
 #pragma unroll
-        for (int col = 0; col < CPT; ++col) {
-            const uint32_t code = (words[col][k >> 2] >> (8 * (k & 3))) & 0xFFu;
-            const float sf = scale_from_byte(sb[col]);
-            if (plain) y[col] = __float_as_uint(__fmul_rn(__uint_as_float(decode_f32_fast(code, f)), sf));
-            else y[col] = mx_decode(code, sf, f);
-        }
-        char* d = dst + k * row_bytes;
-        if constexpr (KOut::size == 4) {
-            __stcs(reinterpret_cast<unsigned int*>(d), y[0]);
-        } else if constexpr (CPT == 2) {
-            uint32_t w;
-            if (plain) {
-                if constexpr (std::is_same<KOut, KBF16>::value) {
-                    const __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(y[0]), __uint_as_float(y[1]));
-                    w = *reinterpret_cast<const uint32_t*>(&hh);
-                } else {
-                    const __half2 hh = __floats2half2_rn(__uint_as_float(y[0]), __uint_as_float(y[1]));
-                    w = *reinterpret_cast<const uint32_t*>(&hh);
-                }
-            } else {
-                w = KOut::from_bits(y[0]) | (KOut::from_bits(y[1]) << 16);
+        for (int k = 0; k < 32; ++k) {
+            uint32_t y[CPT];
+#pragma unroll
+            for (int col = 0; col < CPT; ++col) {
+                const uint32_t code = (words[col][k >> 2] >> (8 * (k & 3))) & 0xFFu;
+                y[col] = __float_as_uint(__fmul_rn(__uint_as_float(decode_f32_fast(code, f)), sf[col]));
             }
-            __stcs(reinterpret_cast<unsigned int*>(d), w);
-        } else {
-            __stcs(reinterpret_cast<unsigned short*>(d), (unsigned short)KOut::from_bits(y[0]));
+            store_row<KOut, CPT, true>(dst + k * row_bytes, y);
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+            uint32_t y[CPT];
+#pragma unroll
+            for (int col = 0; col < CPT; ++col) y[col] = mx_decode((words[col][k >> 2] >> (8 * (k & 3))) & 0xFFu, sf[col], f);
+            store_row<KOut, CPT, false>(dst + k * row_bytes, y);
         }
     }
 }
