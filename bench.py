@@ -363,6 +363,35 @@ def extras_multi_gpu(dev, dist, rank: int, world: int, local: int, steps: int, p
     out["cfg4_column_parallel"] = {"gemm_only_TFLOPs_total": round(fl / t_gemm / 1e9, 1), "gemm_plus_allgather_TFLOPs_total": round(fl / t_all / 1e9, 1),
                                    "ms": {"gemm": round(t_gemm, 4), "gemm_plus_allgather": round(t_all, 4)},
                                    "out_features_per_gpu": n1 - n0, "collective": "nccl all_gather of bf16 [M, N/g] shards"}
+    # the same with the gather done by the GEMM epilogue (peer stores over NVLink) plus a one-element all-reduce as fence
+    try:
+        import torch.distributed._symmetric_memory as symm_mem
+        bufs, ptrs, handles = [], [], []
+        for _ in range(2):
+            t = symm_mem.empty((M, N), dtype=torch.bfloat16, device=dev)
+            h = symm_mem.rendezvous(t, dist.group.WORLD)
+            bufs.append(t); handles.append(h); ptrs.append([int(p) for p in h.buffer_ptrs])
+        fence = torch.zeros(1, device=dev)
+        turn = [0]
+
+        def fused():
+            G.mx_gemm_gather(a, bq, ptrs[turn[0]], N, n0, torch.bfloat16)
+            dist.all_reduce(fence)
+            turn[0] ^= 1
+
+        t_fused = timed(fused)
+        t_stores = timed(lambda: G.mx_gemm_gather(a, bq, ptrs[0], N, n0, torch.bfloat16))
+        G.check_status(dev)
+        # bytes each GPU sends to its peers per call / time of the kernel that sends them
+        egress = M * (n1 - n0) * 2 * (world - 1)
+        out["cfg4_column_parallel"].update({
+            "gemm_fused_gather_TFLOPs_total": round(fl / t_fused / 1e9, 1),
+            "fused_kernel_only_TFLOPs_total": round(fl / t_stores / 1e9, 1),
+            "fused_kernel_nvlink_egress_GBps_per_gpu": round(egress / t_stores / 1e6, 1),
+            "fused_gather": "GEMM epilogue stores each tile into every rank's [M, N] output (symmetric memory), then a 1-element all-reduce"})
+        out["cfg4_column_parallel"]["ms"].update({"gemm_fused_gather": round(t_fused, 4), "fused_kernel_only": round(t_stores, 4)})
+    except Exception as exc:   # noqa: BLE001 - reported, the NCCL numbers above stand
+        out["cfg4_column_parallel"]["fused_gather_error"] = f"{type(exc).__name__}: {exc}"[:300]
     return out
 
 

@@ -59,6 +59,23 @@ template <int MH> struct Cfg {
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;   // + slack to align the ring
 };
 
+// Destinations of the gather-fused epilogue: the same [M, N] result tile goes, at column offset
+// col0 of a row-major matrix with leading dimension ld, to every pointer in ptr[0..n) -- this GPU's
+// own output and the peers' outputs mapped into this process (plain stores over NVLink).
+constexpr int MAX_DEST = 8;
+struct OutSpec {
+    void* ptr[MAX_DEST];
+    int n;
+    int64_t ld, col0;
+};
+// per epilogue warp: 32 rows x 64 output columns staged in shared memory so that the global stores of
+// a warp cover whole 128-byte (16-bit output) or 256-byte (fp32) row segments
+template <int OUT_DT> struct Stage {
+    static constexpr int ESZ = OUT_DT == MXQ_F32 ? 4 : 2;
+    static constexpr int ROW_BYTES = 64 * ESZ;
+    static constexpr int WARP_BYTES = 32 * ROW_BYTES;
+};
+
 // status codes written to the caller's status word when a bounded wait runs out
 enum : int { ST_OK = 0, ST_PRODUCER_TIMEOUT = 1, ST_MMA_TIMEOUT = 2, ST_EPILOGUE_TIMEOUT = 3 };
 
@@ -195,11 +212,69 @@ __device__ __forceinline__ void store_chunk(void* __restrict__ out, const void* 
     }
 }
 
-template <int OUT_DT, int MH>   // OUT_DT: MXQ_F32 / MXQ_BF16 / MXQ_F16; MH: 128-row accumulators per CTA tile
+// Gather-fused form of store_chunk: the 32 accumulator columns of this lane's row get the bias,
+// are converted and parked in the warp's staging buffer (16-byte units, XOR-swizzled by row so that
+// both the row-per-lane writes and the row-segment reads are free of bank conflicts).
+template <int OUT_DT>
+__device__ __forceinline__ void stage_chunk(uint8_t* stg, const void* __restrict__ bias, const uint32_t (&r)[32], int lane,
+                                            int half, int col0, int N) {
+    using S = Stage<OUT_DT>;
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+    if (bias != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            if (col0 + i < N) {
+                if constexpr (OUT_DT == MXQ_F32) v[i] += reinterpret_cast<const float*>(bias)[col0 + i];
+                else if constexpr (OUT_DT == MXQ_BF16) v[i] += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[col0 + i]);
+                else v[i] += __half2float(reinterpret_cast<const __half*>(bias)[col0 + i]);
+            }
+        }
+    }
+    uint8_t* row = stg + lane * S::ROW_BYTES;
+    if constexpr (OUT_DT == MXQ_F32) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            *reinterpret_cast<float4*>(row + (((half * 8 + u) ^ (lane & 7)) << 4)) = make_float4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
+    } else {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+            if constexpr (OUT_DT == MXQ_BF16) { const __nv_bfloat162 h = __floats2bfloat162_rn(v[i], v[i + 1]); pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h); }
+            else { const __half2 h = __floats2half2_rn(v[i], v[i + 1]); pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h); }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            *reinterpret_cast<uint4*>(row + (((half * 4 + u) ^ (lane & 7)) << 4)) = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
+    }
+}
+
+// staged 32 rows x (32 * halves) columns -> every destination; a warp instruction writes whole row segments
+template <int OUT_DT>
+__device__ __forceinline__ void flush_stage(const uint8_t* stg, const OutSpec& outs, int lane, int halves, int row0, int col0,
+                                            int M, int N) {
+    using S = Stage<OUT_DT>;
+    constexpr int EPU = 16 / S::ESZ;                      // elements per 16-byte unit
+    const int upr = halves * (32 / EPU);                  // units per staged row: 4/8 (16-bit) or 8/16 (fp32)
+    for (int i = 0; i < upr; ++i) {
+        const int flat = i * 32 + lane;
+        const int row = flat / upr, u = flat - row * upr;
+        const int grow = row0 + row, gcol = col0 + u * EPU;
+        if (grow >= M || gcol >= N) continue;             // N is a multiple of EPU: units are never ragged
+        const uint4 val = *reinterpret_cast<const uint4*>(stg + row * S::ROW_BYTES + ((u ^ (row & 7)) << 4));
+        const size_t off = ((size_t)grow * outs.ld + outs.col0 + gcol) * S::ESZ;
+        for (int d = 0; d < outs.n; ++d) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(outs.ptr[d]) + off) = val;
+    }
+}
+
+// OUT_DT: MXQ_F32 / MXQ_BF16 / MXQ_F16; MH: 128-row accumulators per CTA tile; MULTI: gather-fused epilogue
+template <int OUT_DT, int MH, bool MULTI>
 __global__ void __launch_bounds__(THREADS, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, void* __restrict__ out,
-               const void* __restrict__ bias, int M, int N, int K, uint32_t idesc_base, int* status) {
+               const void* __restrict__ bias, int M, int N, int K, uint32_t idesc_base, int* status,
+               const __grid_constant__ OutSpec outs) {
     using C = Cfg<MH>;
     constexpr int STAGES = C::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -325,7 +400,18 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         __syncwarp();
                         if (lane == 0) mbar_arrive(tmem_empty_bar(h));
                     }
-                    store_chunk<OUT_DT>(out, bias, r, row, nt * BN + c * 32, M, N);
+                    if constexpr (!MULTI) {
+                        store_chunk<OUT_DT>(out, bias, r, row, nt * BN + c * 32, M, N);
+                    } else {
+                        // two 32-column chunks share one staging round (the seventh chunk goes alone)
+                        uint8_t* stg = ring_ptr + STAGES * C::STAGE_BYTES + BAR_BYTES + q * Stage<OUT_DT>::WARP_BYTES;
+                        stage_chunk<OUT_DT>(stg, bias, r, lane, c & 1, nt * BN + c * 32, N);
+                        if ((c & 1) || c == BN / 32 - 1) {
+                            __syncwarp();
+                            flush_stage<OUT_DT>(stg, outs, lane, (c & 1) + 1, mt * C::BM + h * 128 + q * 32, nt * BN + (c & ~1) * 32, M, N);
+                            __syncwarp();
+                        }
+                    }
                 }
             }
         }
@@ -466,27 +552,35 @@ static int sm_count() {
     return n;
 }
 
-template <int OUT_DT, int MH>
+// outs == nullptr: plain epilogue into `out`; otherwise the gather-fused epilogue into outs->ptr[]
+template <int OUT_DT, int MH, bool MULTI>
 static int launch_gemm(const uint8_t* a_codes, const uint8_t* b_codes, const uint8_t* sfa, const uint8_t* sfb, void* out,
-                       const void* bias, int M, int N, int K, uint32_t idesc, int* status, cudaStream_t st) {
+                       const void* bias, int M, int N, int K, uint32_t idesc, int* status, cudaStream_t st, const OutSpec* outs) {
     using C = Cfg<MH>;
+    constexpr int SMEM = C::SMEM_BYTES + (MULTI ? 4 * Stage<OUT_DT>::WARP_BYTES : 0);
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] { attr_err = cudaFuncSetAttribute(mx_gemm_kernel<OUT_DT, MH>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES); });
+    std::call_once(once, [] { attr_err = cudaFuncSetAttribute(mx_gemm_kernel<OUT_DT, MH, MULTI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
     if (attr_err != cudaSuccess) { set_last_cuda_error(attr_err); return MXQ_ELAUNCH; }
     CUtensorMap ma, mb;
     if (!make_operand_map(&ma, a_codes, M, K, C::BM) || !make_operand_map(&mb, b_codes, N, K, BN)) return MXQ_ELAUNCH;
     const int tiles = ((M + C::BM - 1) / C::BM) * ((N + BN - 1) / BN);
     const int grid = tiles < sm_count() ? tiles : sm_count();          // persistent: one CTA per SM
-    mx_gemm_kernel<OUT_DT, MH><<<grid, THREADS, C::SMEM_BYTES, st>>>(ma, mb, sfa, sfb, out, bias, M, N, K, idesc, status);
+    mx_gemm_kernel<OUT_DT, MH, MULTI><<<grid, THREADS, SMEM, st>>>(ma, mb, sfa, sfb, out, bias, M, N, K, idesc, status,
+                                                                    MULTI ? *outs : OutSpec{});
     return check_launch();
 }
 
 template <int OUT_DT>
 static int launch_gemm_dt(const uint8_t* a_codes, const uint8_t* b_codes, const uint8_t* sfa, const uint8_t* sfb, void* out,
-                          const void* bias, int M, int N, int K, uint32_t idesc, int* status, cudaStream_t st) {
-    if (M <= 128) return launch_gemm<OUT_DT, 1>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, idesc, status, st);
-    return launch_gemm<OUT_DT, 2>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, idesc, status, st);
+                          const void* bias, int M, int N, int K, uint32_t idesc, int* status, cudaStream_t st,
+                          const OutSpec* outs = nullptr) {
+    if (outs != nullptr) {
+        if (M <= 128) return launch_gemm<OUT_DT, 1, true>(a_codes, b_codes, sfa, sfb, nullptr, bias, M, N, K, idesc, status, st, outs);
+        return launch_gemm<OUT_DT, 2, true>(a_codes, b_codes, sfa, sfb, nullptr, bias, M, N, K, idesc, status, st, outs);
+    }
+    if (M <= 128) return launch_gemm<OUT_DT, 1, false>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, idesc, status, st, nullptr);
+    return launch_gemm<OUT_DT, 2, false>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, idesc, status, st, nullptr);
 }
 
 }  // namespace gemm
@@ -530,6 +624,36 @@ extern "C" int mxq_mx_gemm(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw
     if (out_dtype == MXQ_BF16) return gemm::launch_gemm_dt<MXQ_BF16>(a_codes, b_codes, a_sf, b_sf, out, bias, (int)M, (int)N, (int)K, idesc, status, st);
     if (out_dtype == MXQ_F16) return gemm::launch_gemm_dt<MXQ_F16>(a_codes, b_codes, a_sf, b_sf, out, bias, (int)M, (int)N, (int)K, idesc, status, st);
     return MXQ_EINVAL;
+}
+
+extern "C" int mxq_mx_gemm_gather(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw_format, const uint8_t* b_codes,
+                                  const uint8_t* b_sf, int b_hw_format, void* const* outs, int n_outs, int64_t ld_out,
+                                  int64_t col_offset, int out_dtype, const void* bias, int64_t M, int64_t N, int64_t K,
+                                  int* status, void* stream) {
+    if (M <= 0 || N <= 0 || K <= 0 || K % 32 != 0 || M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return MXQ_EINVAL;
+    if (!a_codes || !a_sf || !b_codes || !b_sf || !outs || n_outs < 1 || n_outs > gemm::MAX_DEST) return MXQ_EINVAL;
+    if ((a_hw_format | b_hw_format) & ~1) return MXQ_EINVAL;
+    if (col_offset < 0 || ld_out < col_offset + N) return MXQ_EINVAL;
+    if (out_dtype != MXQ_F32 && out_dtype != MXQ_BF16 && out_dtype != MXQ_F16) return MXQ_EINVAL;
+    // whole 16-byte units only: the shard width, its offset and the leading dimension in units of 16 bytes
+    const int64_t epu = out_dtype == MXQ_F32 ? 4 : 8;
+    if (N % epu != 0 || ld_out % epu != 0 || col_offset % epu != 0) return MXQ_ESIZE;
+    uintptr_t align = reinterpret_cast<uintptr_t>(a_codes) | reinterpret_cast<uintptr_t>(b_codes) | reinterpret_cast<uintptr_t>(a_sf) |
+                      reinterpret_cast<uintptr_t>(b_sf);
+    gemm::OutSpec spec{};
+    for (int d = 0; d < n_outs; ++d) {
+        if (!outs[d]) return MXQ_EINVAL;
+        spec.ptr[d] = outs[d];
+        align |= reinterpret_cast<uintptr_t>(outs[d]);
+    }
+    if (align % 16 != 0) return MXQ_EINVAL;
+    spec.n = n_outs; spec.ld = ld_out; spec.col0 = col_offset;
+    const uint32_t idesc = ((uint32_t)a_hw_format << 7) | ((uint32_t)b_hw_format << 10) | ((uint32_t)(gemm::BN >> 3) << 17) |
+                           (1u << 23) | ((uint32_t)(128 >> 4) << 24);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (out_dtype == MXQ_F32) return gemm::launch_gemm_dt<MXQ_F32>(a_codes, b_codes, a_sf, b_sf, nullptr, bias, (int)M, (int)N, (int)K, idesc, status, st, &spec);
+    if (out_dtype == MXQ_BF16) return gemm::launch_gemm_dt<MXQ_BF16>(a_codes, b_codes, a_sf, b_sf, nullptr, bias, (int)M, (int)N, (int)K, idesc, status, st, &spec);
+    return gemm::launch_gemm_dt<MXQ_F16>(a_codes, b_codes, a_sf, b_sf, nullptr, bias, (int)M, (int)N, (int)K, idesc, status, st, &spec);
 }
 
 // ------------------------------------------------------------------------------------------------

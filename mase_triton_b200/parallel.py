@@ -7,6 +7,10 @@
   contiguous slice of ``w_elements.view(N, K)`` and ``w_scales.view(N, K/32)``), every rank
   quantises the (replicated) activation itself, and the ``[M, N/g]`` partial outputs are gathered
   with one all-gather (NCCL over NVLink on GPUs, gloo in the CPU tests).
+* :class:`GatherFusedMXFPLinear` removes that collective for layers whose activation and weight are
+  both quantised: the epilogue of the tensor-core GEMM stores every output tile straight into the
+  full ``[M, N]`` output of every rank (peer memory mapped through PyTorch symmetric memory, plain
+  stores over NVLink), so the gather overlaps the GEMM tile by tile.
 
 The reference has no distributed code; this module is new functionality named by the benchmark
 configurations (row-sharded quantisation, column-parallel linears).
@@ -106,3 +110,61 @@ def column_parallel_mxfp_linear(layer, group=None) -> ColumnParallelLinear:
     local = MXFPLinearPTQ.from_quantized(s.contiguous(), e.contiguous(), meta, bias, None, None, None, layer.x_mxfp_meta,
                                          layer.layer_type, layer.backend)
     return ColumnParallelLinear(local, layer.out_features, group)
+
+
+class GatherFusedMXFPLinear:
+    """Column-parallel ``XqWq`` MXFP linear with the all-gather fused into the GEMM epilogue.
+
+    Every rank holds the packed weight rows ``[n0, n1)`` and two ``[max_rows, N]`` output buffers in
+    symmetric memory (mapped into every process of ``group``).  A call quantises the replicated
+    activation, runs ``mxq_mx_gemm_gather`` with the addresses of ALL ranks' current buffers as
+    destinations, and then joins one tiny all-reduce that serves as the fence "every rank's stores have
+    landed".  The two buffers alternate, so a fast rank never overwrites an output a slow rank is
+    still reading: the returned tensor (a view of this rank's buffer) is valid until the call after
+    the next one.
+    """
+
+    def __init__(self, layer, max_rows: int, dtype: torch.dtype = torch.bfloat16, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from .mxfp import gemm as _gemm
+
+        self.group = group if group is not None else dist.group.WORLD
+        world, rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        assert layer.w_scales is not None and layer.x_mxfp_meta is not None, "needs a quantised weight and activation"
+        assert _gemm.supported(layer.x_mxfp_meta) and _gemm.supported(layer.w_tensor_meta.meta)
+        N, K = layer.w_tensor_meta.shape
+        unit = 4 if dtype == torch.float32 else 8
+        assert N % unit == 0, "out_features must be a whole number of 16-byte units"
+        B = layer.w_tensor_meta.meta.block_size
+        self.n0, self.n1 = shard_bounds(N, rank, world, multiple=unit)
+        bpr = K // B
+        scales = layer.w_scales.data.reshape(N * bpr, 1)[self.n0 * bpr:self.n1 * bpr]
+        elements = layer.w_elements.data.reshape(N * bpr, B)[self.n0 * bpr:self.n1 * bpr]
+        self.weight = _gemm.pack_operand(scales, elements, self.n1 - self.n0, K, layer.w_tensor_meta.meta, _gemm.OPERAND_B)
+        self.bias = None if layer.bias is None else layer.bias.data[self.n0:self.n1].to(dtype).contiguous()
+        self.x_meta, self.N, self.K, self.dtype, self.max_rows = layer.x_mxfp_meta, N, K, dtype, max_rows
+        dev = layer.w_elements.device
+        self.bufs, self.ptrs, self._handles = [], [], []
+        for _ in range(2):
+            t = symm_mem.empty((max_rows, N), dtype=dtype, device=dev)
+            h = symm_mem.rendezvous(t, self.group)
+            self.bufs.append(t)
+            self._handles.append(h)
+            self.ptrs.append([int(p) for p in h.buffer_ptrs])
+        self._fence = torch.zeros(1, device=dev)
+        self._turn = 0
+        self._gemm = _gemm
+
+    def __call__(self, x: Tensor) -> Tensor:
+        g = self._gemm
+        x2 = x.reshape(-1, self.K)
+        M = x2.shape[0]
+        assert M <= self.max_rows, "more rows than the output buffers were sized for"
+        a = g.quantize_pack_fused(x2, self.x_meta) if self.x_meta.element_exp_bits >= 4 else g.quantize_pack(x2, self.x_meta)
+        if self.n1 > self.n0:
+            g.mx_gemm_gather(a, self.weight, self.ptrs[self._turn], self.N, self.n0, self.dtype, self.bias)
+        dist.all_reduce(self._fence, group=self.group)        # every rank's tiles are in every buffer after this
+        out = self.bufs[self._turn][:M].view(*x.shape[:-1], self.N)
+        self._turn ^= 1
+        return out

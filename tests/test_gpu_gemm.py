@@ -139,3 +139,24 @@ def test_fused_matmul_matches_separate(lib, x_meta, w_meta, dtype):
     y2 = MX.mxfp_matmul(a, b[0, 0], x_meta, w_meta, "XqWq", "fused")
     G.check_status(DEV)
     assert within_tolerance(y2, torch.matmul(a_dq, b_dq[0, 0]))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(256, 224, 128), (300, 448 + 64, 256), (100, 72, 96), (1024, 1792, 512)])
+def test_gather_epilogue_writes_every_destination(lib, dtype, M, N, K):
+    """The gather-fused epilogue gives, in each destination and at the column offset, the bytes of the
+    plain GEMM; columns outside the shard stay untouched."""
+    torch.manual_seed(M + N)
+    x = torch.randn((M, K), device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn((N, K), device=DEV) * 0.05).to(torch.bfloat16)
+    bias = torch.randn((N,), device=DEV).to(dtype)
+    a, b = G.quantize_pack(x, MXFP8_E4M3_fn), G.quantize_pack(w, OCP_MXFP6_E3M2, G.OPERAND_B)
+    want = G.mx_gemm(a, b, dtype, bias=bias)
+    ld, off = N + 64, 40
+    outs = [torch.full((M + 3, ld), 7.0, device=DEV, dtype=dtype) for _ in range(3)]
+    G.mx_gemm_gather(a, b, [o.data_ptr() for o in outs], ld, off, dtype, bias=bias)
+    G.check_status(DEV)
+    torch.cuda.synchronize()
+    for o in outs:
+        assert torch.equal(o[:M, off:off + N].view(torch.uint8), want.view(torch.uint8))
+        assert bool((o[:M, :off] == 7).all()) and bool((o[:M, off + N:] == 7).all()) and bool((o[M:] == 7).all())
