@@ -375,12 +375,12 @@ def extras_multi_gpu(dev, dist, rank: int, world: int, local: int, steps: int, p
         turn = [0]
 
         def fused():
-            G.mx_gemm_gather(a, bq, ptrs[turn[0]], N, n0, torch.bfloat16)
+            G.mx_gemm_gather(a, bq, ptrs[turn[0]], rank, N, n0, torch.bfloat16)
             dist.all_reduce(fence)
             turn[0] ^= 1
 
         t_fused = timed(fused)
-        t_stores = timed(lambda: G.mx_gemm_gather(a, bq, ptrs[0], N, n0, torch.bfloat16))
+        t_stores = timed(lambda: G.mx_gemm_gather(a, bq, ptrs[0], rank, N, n0, torch.bfloat16))
         G.check_status(dev)
         # bytes each GPU sends to its peers per call / time of the kernel that sends them
         egress = M * (n1 - n0) * 2 * (world - 1)
@@ -388,7 +388,7 @@ def extras_multi_gpu(dev, dist, rank: int, world: int, local: int, steps: int, p
             "gemm_fused_gather_TFLOPs_total": round(fl / t_fused / 1e9, 1),
             "fused_kernel_only_TFLOPs_total": round(fl / t_stores / 1e9, 1),
             "fused_kernel_nvlink_egress_GBps_per_gpu": round(egress / t_stores / 1e6, 1),
-            "fused_gather": "GEMM epilogue stores each tile into every rank's [M, N] output (symmetric memory), then a 1-element all-reduce"})
+            "fused_gather": "the GEMM kernel copies each finished tile into every rank's [M, N] output (symmetric memory, peer stores), then a 1-element all-reduce"})
         out["cfg4_column_parallel"]["ms"].update({"gemm_fused_gather": round(t_fused, 4), "fused_kernel_only": round(t_stores, 4)})
     except Exception as exc:   # noqa: BLE001 - reported, the NCCL numbers above stand
         out["cfg4_column_parallel"]["fused_gather_error"] = f"{type(exc).__name__}: {exc}"[:300]

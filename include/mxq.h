@@ -171,20 +171,22 @@ int mxq_mx_gemm(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw_format, co
                 int64_t M, int64_t N, int64_t K, int* status, void* stream);
 
 /*
- * mxq_mx_gemm whose epilogue also performs the all-gather of a column-parallel linear (no counterpart
- * in the reference, which has no distributed code).  The [M, N] result of this rank's weight shard
- * is written at columns [col_offset, col_offset + N) of EVERY row-major [>= M, ld_out] matrix in
- * outs[0 .. n_outs) (host array of device pointers, at most 8): this GPU's own output and the peers'
- * outputs mapped into this process (CUDA IPC / virtual-memory mappings).  The stores are plain
- * global stores of whole 16-byte units that cover 128-byte row segments; nothing in the kernel waits
- * on another GPU.  Ordering against the readers on the other ranks is the caller's business (a
+ * mxq_mx_gemm that also performs the all-gather of a column-parallel linear (no counterpart in the
+ * reference, which has no distributed code).  The [M, N] result of this rank's weight shard goes
+ * to columns [col_offset, col_offset + N) of EVERY row-major [>= M, ld_out] matrix in
+ * outs[0 .. n_outs) (host array of device pointers, at most 8): outs[self_index] is this GPU's own
+ * output, the others are the peers' outputs mapped into this process (CUDA IPC / virtual-memory
+ * mappings).  The epilogue warps write the local output; four more warps of the same CTAs read each
+ * finished tile back (from L2) and store it to the peers with plain 16-byte stores that cover whole
+ * row segments, while the tensor cores work on the next tile.  Nothing in the kernel waits on
+ * another GPU.  Ordering against the readers on the other ranks is the caller's business (a
  * collective or event after this call on the same stream).
  * N, ld_out and col_offset must be multiples of 8 elements (4 for MXQ_F32), else MXQ_ESIZE.
  */
 int mxq_mx_gemm_gather(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw_format, const uint8_t* b_codes,
-                       const uint8_t* b_sf, int b_hw_format, void* const* outs, int n_outs, int64_t ld_out,
-                       int64_t col_offset, int out_dtype, const void* bias, int64_t M, int64_t N, int64_t K,
-                       int* status, void* stream);
+                       const uint8_t* b_sf, int b_hw_format, void* const* outs, int n_outs, int self_index,
+                       int64_t ld_out, int64_t col_offset, int out_dtype, const void* bias, int64_t M,
+                       int64_t N, int64_t K, int* status, void* stream);
 
 /*
  * mxfp_linear with quantised activation and weight in one call (layer types XqWqB / XqWqBq,

@@ -59,25 +59,20 @@ template <int MH> struct Cfg {
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;   // + slack to align the ring
 };
 
-// Destinations of the gather-fused epilogue: the same [M, N] result tile goes, at column offset
-// col0 of a row-major matrix with leading dimension ld, to every pointer in ptr[0..n) -- this GPU's
-// own output and the peers' outputs mapped into this process (plain stores over NVLink).
+// Destinations of the gather-fused kernel: the [M, N] result goes, at column offset col0 of a
+// row-major matrix with leading dimension ld, to every pointer in ptr[0..n): ptr[self] is this GPU's
+// own output, the others are the peers' outputs mapped into this process.
 constexpr int MAX_DEST = 8;
 struct OutSpec {
     void* ptr[MAX_DEST];
-    int n;
+    int n, self;
     int64_t ld, col0;
 };
-// per epilogue warp: 32 rows x 64 output columns staged in shared memory so that the global stores of
-// a warp cover whole 128-byte (16-bit output) or 256-byte (fp32) row segments
-template <int OUT_DT> struct Stage {
-    static constexpr int ESZ = OUT_DT == MXQ_F32 ? 4 : 2;
-    static constexpr int ROW_BYTES = 64 * ESZ;
-    static constexpr int WARP_BYTES = 32 * ROW_BYTES;
-};
+constexpr int FWD_WARPS = 4;                     // copy-out warps of the gather-fused kernel
+constexpr int STORED_BAR_OFF = 128, ACK_BAR_OFF = 136;   // inside the BAR_BYTES region, past the pipeline barriers
 
 // status codes written to the caller's status word when a bounded wait runs out
-enum : int { ST_OK = 0, ST_PRODUCER_TIMEOUT = 1, ST_MMA_TIMEOUT = 2, ST_EPILOGUE_TIMEOUT = 3 };
+enum : int { ST_OK = 0, ST_PRODUCER_TIMEOUT = 1, ST_MMA_TIMEOUT = 2, ST_EPILOGUE_TIMEOUT = 3, ST_FORWARD_TIMEOUT = 4 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -167,9 +162,10 @@ __device__ __forceinline__ void tile_coords(int t, int MT, int NT, int& mt, int&
     nt = r / gm;
 }
 
+// `out` is a row-major matrix with leading dimension ld; the tile's columns start at column `shift` of it
 template <int OUT_DT>
 __device__ __forceinline__ void store_chunk(void* __restrict__ out, const void* __restrict__ bias, const uint32_t (&r)[32],
-                                            int row, int col0, int M, int N) {
+                                            int row, int col0, int M, int N, int64_t ld, int64_t shift) {
     if (row >= M || col0 >= N) return;
     float v[32];
 #pragma unroll
@@ -186,8 +182,8 @@ __device__ __forceinline__ void store_chunk(void* __restrict__ out, const void* 
         }
     }
     if constexpr (OUT_DT == MXQ_F32) {
-        float* o = reinterpret_cast<float*>(out) + (size_t)row * N + col0;
-        if (whole && (N % 4 == 0)) {
+        float* o = reinterpret_cast<float*>(out) + (size_t)row * ld + shift + col0;
+        if (whole && ((ld | shift) % 4 == 0)) {
 #pragma unroll
             for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
         } else {
@@ -201,8 +197,8 @@ __device__ __forceinline__ void store_chunk(void* __restrict__ out, const void* 
             if constexpr (OUT_DT == MXQ_BF16) { const __nv_bfloat162 h = __floats2bfloat162_rn(v[i], v[i + 1]); pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h); }
             else { const __half2 h = __floats2half2_rn(v[i], v[i + 1]); pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h); }
         }
-        uint16_t* o = reinterpret_cast<uint16_t*>(out) + (size_t)row * N + col0;
-        if (whole && (N % 8 == 0)) {
+        uint16_t* o = reinterpret_cast<uint16_t*>(out) + (size_t)row * ld + shift + col0;
+        if (whole && ((ld | shift) % 8 == 0)) {
 #pragma unroll
             for (int i = 0; i < 16; i += 4) *reinterpret_cast<uint4*>(o + 2 * i) = make_uint4(pk[i], pk[i + 1], pk[i + 2], pk[i + 3]);
         } else {
@@ -212,65 +208,42 @@ __device__ __forceinline__ void store_chunk(void* __restrict__ out, const void* 
     }
 }
 
-// Gather-fused form of store_chunk: the 32 accumulator columns of this lane's row get the bias,
-// are converted and parked in the warp's staging buffer (16-byte units, XOR-swizzled by row so that
-// both the row-per-lane writes and the row-segment reads are free of bank conflicts).
+// Copy-out of the gather-fused kernel: one tile of this GPU's output (just written by the epilogue
+// warps, still in L2) is read back and stored into every peer's output, 16 bytes per lane, whole
+// row segments per warp instruction.
 template <int OUT_DT>
-__device__ __forceinline__ void stage_chunk(uint8_t* stg, const void* __restrict__ bias, const uint32_t (&r)[32], int lane,
-                                            int half, int col0, int N) {
-    using S = Stage<OUT_DT>;
-    float v[32];
+__device__ __forceinline__ void forward_tile(const OutSpec& outs, int fw, int lane, int row0, int rows, int col0, int cols) {
+    constexpr int ESZ = OUT_DT == MXQ_F32 ? 4 : 2;
+    constexpr int EPU = 16 / ESZ;                          // elements per 16-byte unit
+    const int upr = cols / EPU;                            // units per row segment (cols is a multiple of EPU)
+    const int total = rows * upr;
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(outs.ptr[outs.self]);
+    constexpr int UNROLL = 4;
+    for (int base = fw * 32 + lane; base < total; base += FWD_WARPS * 32 * UNROLL) {
+        uint4 v[UNROLL];
+        size_t off[UNROLL];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-    if (bias != nullptr) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            if (col0 + i < N) {
-                if constexpr (OUT_DT == MXQ_F32) v[i] += reinterpret_cast<const float*>(bias)[col0 + i];
-                else if constexpr (OUT_DT == MXQ_BF16) v[i] += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[col0 + i]);
-                else v[i] += __half2float(reinterpret_cast<const __half*>(bias)[col0 + i]);
+        for (int j = 0; j < UNROLL; ++j) {
+            const int flat = base + j * FWD_WARPS * 32;
+            if (flat < total) {
+                const int row = flat / upr, u = flat - row * upr;
+                off[j] = ((size_t)(row0 + row) * outs.ld + outs.col0 + col0 + u * EPU) * ESZ;
+                v[j] = __ldcg(reinterpret_cast<const uint4*>(src + off[j]));
             }
         }
-    }
-    uint8_t* row = stg + lane * S::ROW_BYTES;
-    if constexpr (OUT_DT == MXQ_F32) {
 #pragma unroll
-        for (int u = 0; u < 8; ++u)
-            *reinterpret_cast<float4*>(row + (((half * 8 + u) ^ (lane & 7)) << 4)) = make_float4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
-    } else {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-            if constexpr (OUT_DT == MXQ_BF16) { const __nv_bfloat162 h = __floats2bfloat162_rn(v[i], v[i + 1]); pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h); }
-            else { const __half2 h = __floats2half2_rn(v[i], v[i + 1]); pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h); }
+        for (int j = 0; j < UNROLL; ++j) {
+            if (base + j * FWD_WARPS * 32 < total) {
+                for (int d = 0; d < outs.n; ++d)
+                    if (d != outs.self) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(outs.ptr[d]) + off[j]) = v[j];
+            }
         }
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-            *reinterpret_cast<uint4*>(row + (((half * 4 + u) ^ (lane & 7)) << 4)) = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
-    }
-}
-
-// staged 32 rows x (32 * halves) columns -> every destination; a warp instruction writes whole row segments
-template <int OUT_DT>
-__device__ __forceinline__ void flush_stage(const uint8_t* stg, const OutSpec& outs, int lane, int halves, int row0, int col0,
-                                            int M, int N) {
-    using S = Stage<OUT_DT>;
-    constexpr int EPU = 16 / S::ESZ;                      // elements per 16-byte unit
-    const int upr = halves * (32 / EPU);                  // units per staged row: 4/8 (16-bit) or 8/16 (fp32)
-    for (int i = 0; i < upr; ++i) {
-        const int flat = i * 32 + lane;
-        const int row = flat / upr, u = flat - row * upr;
-        const int grow = row0 + row, gcol = col0 + u * EPU;
-        if (grow >= M || gcol >= N) continue;             // N is a multiple of EPU: units are never ragged
-        const uint4 val = *reinterpret_cast<const uint4*>(stg + row * S::ROW_BYTES + ((u ^ (row & 7)) << 4));
-        const size_t off = ((size_t)grow * outs.ld + outs.col0 + gcol) * S::ESZ;
-        for (int d = 0; d < outs.n; ++d) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(outs.ptr[d]) + off) = val;
     }
 }
 
 // OUT_DT: MXQ_F32 / MXQ_BF16 / MXQ_F16; MH: 128-row accumulators per CTA tile; MULTI: gather-fused epilogue
 template <int OUT_DT, int MH, bool MULTI>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS + (MULTI ? FWD_WARPS * 32 : 0), 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, void* __restrict__ out,
                const void* __restrict__ bias, int M, int N, int K, uint32_t idesc_base, int* status,
@@ -287,6 +260,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
     const uint32_t accum_bar = bars + 8u * (2 * STAGES);
     auto tmem_empty_bar = [&](int h) { return bars + 8u * (2 * STAGES + 1 + h); };   // one per accumulator
+    const uint32_t stored_bar = bars + STORED_BAR_OFF, ack_bar = bars + ACK_BAR_OFF;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KT = (K + BK - 1) / BK;
@@ -298,6 +272,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         mbar_init(accum_bar, 1);
         mbar_init(tmem_empty_bar(0), 4);                             // one arrival per epilogue warp
         mbar_init(tmem_empty_bar(1), 4);
+        if constexpr (MULTI) {
+            mbar_init(stored_bar, 4);                                // epilogue warps: "this tile is in local memory"
+            mbar_init(ack_bar, FWD_WARPS);                           // copy-out warps: "seen it"
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -375,7 +353,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (lane == 0) mma_commit(accum_bar);         // accumulators of this tile complete (or unwinding)
             __syncwarp();
         }
-    } else {
+    } else if (warp < 6) {
         // ---------------- epilogue: TMEM -> registers -> global ----------------
         const int q = warp & 3;                            // TMEM lane quadrant this warp may access
         bool ok = true;
@@ -400,19 +378,32 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         __syncwarp();
                         if (lane == 0) mbar_arrive(tmem_empty_bar(h));
                     }
-                    if constexpr (!MULTI) {
-                        store_chunk<OUT_DT>(out, bias, r, row, nt * BN + c * 32, M, N);
-                    } else {
-                        // two 32-column chunks share one staging round (the seventh chunk goes alone)
-                        uint8_t* stg = ring_ptr + STAGES * C::STAGE_BYTES + BAR_BYTES + q * Stage<OUT_DT>::WARP_BYTES;
-                        stage_chunk<OUT_DT>(stg, bias, r, lane, c & 1, nt * BN + c * 32, N);
-                        if ((c & 1) || c == BN / 32 - 1) {
-                            __syncwarp();
-                            flush_stage<OUT_DT>(stg, outs, lane, (c & 1) + 1, mt * C::BM + h * 128 + q * 32, nt * BN + (c & ~1) * 32, M, N);
-                            __syncwarp();
-                        }
-                    }
+                    if constexpr (!MULTI) store_chunk<OUT_DT>(out, bias, r, row, nt * BN + c * 32, M, N, N, 0);
+                    else store_chunk<OUT_DT>(outs.ptr[outs.self], bias, r, row, nt * BN + c * 32, M, N, outs.ld, outs.col0);
                 }
+            }
+            if constexpr (MULTI) {
+                // tell the copy-out warps that this warp's rows of the tile are in local memory; they must
+                // have picked up the previous tile first (the barrier holds one tile of slack)
+                if (tcount > 0) ok = mbar_wait(ack_bar, (tcount - 1) & 1, status, ST_EPILOGUE_TIMEOUT);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(stored_bar);
+            }
+        }
+    } else {
+        // ---------------- gather-fused kernel only: copy-out warps, local output -> peers ----------------
+        if constexpr (MULTI) {
+            const int fw = warp - 6;
+            bool ok = true;
+            uint32_t tcount = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+                int mt, nt;
+                tile_coords(tile, MT, NT, mt, nt);
+                ok = mbar_wait(stored_bar, tcount & 1, status, ST_FORWARD_TIMEOUT);
+                if (!ok) break;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(ack_bar);
+                forward_tile<OUT_DT>(outs, fw, lane, mt * C::BM, min(C::BM, M - mt * C::BM), nt * BN, min(BN, N - nt * BN));
             }
         }
     }
@@ -557,7 +548,7 @@ template <int OUT_DT, int MH, bool MULTI>
 static int launch_gemm(const uint8_t* a_codes, const uint8_t* b_codes, const uint8_t* sfa, const uint8_t* sfb, void* out,
                        const void* bias, int M, int N, int K, uint32_t idesc, int* status, cudaStream_t st, const OutSpec* outs) {
     using C = Cfg<MH>;
-    constexpr int SMEM = C::SMEM_BYTES + (MULTI ? 4 * Stage<OUT_DT>::WARP_BYTES : 0);
+    constexpr int SMEM = C::SMEM_BYTES;
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] { attr_err = cudaFuncSetAttribute(mx_gemm_kernel<OUT_DT, MH, MULTI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
@@ -566,7 +557,7 @@ static int launch_gemm(const uint8_t* a_codes, const uint8_t* b_codes, const uin
     if (!make_operand_map(&ma, a_codes, M, K, C::BM) || !make_operand_map(&mb, b_codes, N, K, BN)) return MXQ_ELAUNCH;
     const int tiles = ((M + C::BM - 1) / C::BM) * ((N + BN - 1) / BN);
     const int grid = tiles < sm_count() ? tiles : sm_count();          // persistent: one CTA per SM
-    mx_gemm_kernel<OUT_DT, MH, MULTI><<<grid, THREADS, SMEM, st>>>(ma, mb, sfa, sfb, out, bias, M, N, K, idesc, status,
+    mx_gemm_kernel<OUT_DT, MH, MULTI><<<grid, THREADS + (MULTI ? FWD_WARPS * 32 : 0), SMEM, st>>>(ma, mb, sfa, sfb, out, bias, M, N, K, idesc, status,
                                                                     MULTI ? *outs : OutSpec{});
     return check_launch();
 }
@@ -627,11 +618,11 @@ extern "C" int mxq_mx_gemm(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw
 }
 
 extern "C" int mxq_mx_gemm_gather(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw_format, const uint8_t* b_codes,
-                                  const uint8_t* b_sf, int b_hw_format, void* const* outs, int n_outs, int64_t ld_out,
-                                  int64_t col_offset, int out_dtype, const void* bias, int64_t M, int64_t N, int64_t K,
+                                  const uint8_t* b_sf, int b_hw_format, void* const* outs, int n_outs, int self_index,
+                                  int64_t ld_out, int64_t col_offset, int out_dtype, const void* bias, int64_t M, int64_t N, int64_t K,
                                   int* status, void* stream) {
     if (M <= 0 || N <= 0 || K <= 0 || K % 32 != 0 || M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return MXQ_EINVAL;
-    if (!a_codes || !a_sf || !b_codes || !b_sf || !outs || n_outs < 1 || n_outs > gemm::MAX_DEST) return MXQ_EINVAL;
+    if (!a_codes || !a_sf || !b_codes || !b_sf || !outs || n_outs < 1 || n_outs > gemm::MAX_DEST || self_index < 0 || self_index >= n_outs) return MXQ_EINVAL;
     if ((a_hw_format | b_hw_format) & ~1) return MXQ_EINVAL;
     if (col_offset < 0 || ld_out < col_offset + N) return MXQ_EINVAL;
     if (out_dtype != MXQ_F32 && out_dtype != MXQ_BF16 && out_dtype != MXQ_F16) return MXQ_EINVAL;
@@ -647,7 +638,7 @@ extern "C" int mxq_mx_gemm_gather(const uint8_t* a_codes, const uint8_t* a_sf, i
         align |= reinterpret_cast<uintptr_t>(outs[d]);
     }
     if (align % 16 != 0) return MXQ_EINVAL;
-    spec.n = n_outs; spec.ld = ld_out; spec.col0 = col_offset;
+    spec.n = n_outs; spec.self = self_index; spec.ld = ld_out; spec.col0 = col_offset;
     const uint32_t idesc = ((uint32_t)a_hw_format << 7) | ((uint32_t)b_hw_format << 10) | ((uint32_t)(gemm::BN >> 3) << 17) |
                            (1u << 23) | ((uint32_t)(128 >> 4) << 24);
     cudaStream_t st = (cudaStream_t)stream;

@@ -131,13 +131,14 @@ def mx_gemm(a: PackedOperand, b: PackedOperand, out_dtype: torch.dtype, bias: Te
     return out
 
 
-def mx_gemm_gather(a: PackedOperand, b: PackedOperand, out_ptrs: list[int], ld: int, col_offset: int,
+def mx_gemm_gather(a: PackedOperand, b: PackedOperand, out_ptrs: list[int], self_index: int, ld: int, col_offset: int,
                    out_dtype: torch.dtype, bias: Tensor | None = None) -> None:
-    """``a [M,K] @ b[N,K]^T (+ bias)`` written by the GEMM epilogue itself into EVERY buffer of
-    ``out_ptrs`` (device addresses of row-major ``[>=M, ld]`` matrices of ``out_dtype``: this GPU's output
-    and the peers' outputs mapped into this process) at columns ``[col_offset, col_offset + N)``.
-    This is the all-gather of a column-parallel linear done by the producing kernel with plain stores
-    over NVLink; the caller orders it against the consumers on the other ranks."""
+    """``a [M,K] @ b[N,K]^T (+ bias)`` written by the GEMM kernel itself into EVERY buffer of
+    ``out_ptrs`` (device addresses of row-major ``[>=M, ld]`` matrices of ``out_dtype``:
+    ``out_ptrs[self_index]`` is this GPU's output, the others are the peers' outputs mapped into this
+    process) at columns ``[col_offset, col_offset + N)``.  This is the all-gather of a column-parallel
+    linear done by the producing kernel with plain stores over NVLink; the caller orders it against the
+    consumers on the other ranks."""
     assert a.K == b.K and out_dtype in _lib.DTYPE_ID and a.operand == OPERAND_A and b.operand == OPERAND_B
     dev = a.codes.device
     if bias is not None:
@@ -146,7 +147,7 @@ def mx_gemm_gather(a: PackedOperand, b: PackedOperand, out_ptrs: list[int], ld: 
     ptrs = (ctypes.c_void_p * len(out_ptrs))(*out_ptrs)
     with torch.cuda.device(dev):
         rc = _lib.load().mxq_mx_gemm_gather(a.codes.data_ptr(), a.sf.data_ptr(), a.hw_format, b.codes.data_ptr(), b.sf.data_ptr(),
-                                            b.hw_format, ctypes.addressof(ptrs), len(out_ptrs), ld, col_offset,
+                                            b.hw_format, ctypes.addressof(ptrs), len(out_ptrs), self_index, ld, col_offset,
                                             _lib.DTYPE_ID[out_dtype], None if bias is None else bias.data_ptr(),
                                             a.rows, b.rows, a.K, status_word(dev).data_ptr(), _lib.stream_ptr(dev))
     _lib.check(rc, "mxq_mx_gemm_gather")

@@ -8,9 +8,10 @@
   quantises the (replicated) activation itself, and the ``[M, N/g]`` partial outputs are gathered
   with one all-gather (NCCL over NVLink on GPUs, gloo in the CPU tests).
 * :class:`GatherFusedMXFPLinear` removes that collective for layers whose activation and weight are
-  both quantised: the epilogue of the tensor-core GEMM stores every output tile straight into the
+  both quantised: the tensor-core GEMM kernel itself copies every finished output tile into the
   full ``[M, N]`` output of every rank (peer memory mapped through PyTorch symmetric memory, plain
-  stores over NVLink), so the gather overlaps the GEMM tile by tile.
+  stores over NVLink, issued by extra warps of the same CTAs), so the gather overlaps the GEMM tile
+  by tile.
 
 The reference has no distributed code; this module is new functionality named by the benchmark
 configurations (row-sharded quantisation, column-parallel linears).
@@ -153,6 +154,7 @@ class GatherFusedMXFPLinear:
             self._handles.append(h)
             self.ptrs.append([int(p) for p in h.buffer_ptrs])
         self._fence = torch.zeros(1, device=dev)
+        self.rank = rank
         self._turn = 0
         self._gemm = _gemm
 
@@ -163,7 +165,7 @@ class GatherFusedMXFPLinear:
         assert M <= self.max_rows, "more rows than the output buffers were sized for"
         a = g.quantize_pack_fused(x2, self.x_meta) if self.x_meta.element_exp_bits >= 4 else g.quantize_pack(x2, self.x_meta)
         if self.n1 > self.n0:
-            g.mx_gemm_gather(a, self.weight, self.ptrs[self._turn], self.N, self.n0, self.dtype, self.bias)
+            g.mx_gemm_gather(a, self.weight, self.ptrs[self._turn], self.rank, self.N, self.n0, self.dtype, self.bias)
         dist.all_reduce(self._fence, group=self.group)        # every rank's tiles are in every buffer after this
         out = self.bufs[self._turn][:M].view(*x.shape[:-1], self.N)
         self._turn ^= 1

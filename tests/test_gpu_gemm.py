@@ -144,7 +144,7 @@ def test_fused_matmul_matches_separate(lib, x_meta, w_meta, dtype):
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 @pytest.mark.parametrize("M,N,K", [(256, 224, 128), (300, 448 + 64, 256), (100, 72, 96), (1024, 1792, 512)])
 def test_gather_epilogue_writes_every_destination(lib, dtype, M, N, K):
-    """The gather-fused epilogue gives, in each destination and at the column offset, the bytes of the
+    """The gather-fused kernel gives, in each destination and at the column offset, the bytes of the
     plain GEMM; columns outside the shard stay untouched."""
     torch.manual_seed(M + N)
     x = torch.randn((M, K), device=DEV, dtype=torch.bfloat16)
@@ -154,7 +154,7 @@ def test_gather_epilogue_writes_every_destination(lib, dtype, M, N, K):
     want = G.mx_gemm(a, b, dtype, bias=bias)
     ld, off = N + 64, 40
     outs = [torch.full((M + 3, ld), 7.0, device=DEV, dtype=dtype) for _ in range(3)]
-    G.mx_gemm_gather(a, b, [o.data_ptr() for o in outs], ld, off, dtype, bias=bias)
+    G.mx_gemm_gather(a, b, [o.data_ptr() for o in outs], 1, ld, off, dtype, bias=bias)
     G.check_status(DEV)
     torch.cuda.synchronize()
     for o in outs:
