@@ -50,15 +50,17 @@ struct FmtRT {
 // memory: the compiler cannot fold k, so it emits an integer multiply-add, which issues on the
 // fp32/FMA pipe instead of the (saturated) integer ALU pipe.
 #if defined(__CUDACC__)
-static __constant__ int mxq_rt_k[5] = {1, 4, 256, 65536, 1 << 24};
+static __constant__ int mxq_rt_k[8] = {1, 4, 256, 65536, 1 << 24, 1 << 20, 1 << 21, 1 << 22};
 #endif
 MXQ_HD int rt_k(int i) {
 #if defined(__CUDA_ARCH__)
     return mxq_rt_k[i];
 #else
-    return i == 0 ? 1 : i == 1 ? 4 : i == 2 ? 256 : i == 3 ? 65536 : (1 << 24);
+    return i == 0 ? 1 : i == 1 ? 4 : i == 2 ? 256 : i == 3 ? 65536 : i == 4 ? (1 << 24) : (1 << (15 + i));
 #endif
 }
+// 2^(23 - fb) for fb = 1..3 as a run-time factor (entries 7, 6, 5)
+MXQ_HD int rt_pow2_shift(int fb) { return rt_k(8 - fb); }
 MXQ_HD int mad_add(int a, int b) { return a * rt_k(0) + b; }           // a + b
 
 template <class F> MXQ_HD int fmt_bias(const F& f) { return (1 << (f.eb() - 1)) - 1; }
@@ -259,22 +261,43 @@ MXQ_HD uint32_t decode_f32_fast(uint32_t code, const F& f) {
     return y | sign;
 }
 
+// The value is built directly in the fp32 bit domain, without forming the code:
+//   * normal range (biased exponent >= 1): the rounded mantissa field fr << (23-fb) is OR-ed under
+//     the input's own exponent field -- fr = 2^fb lands on exponent bit 23, which is the reference's
+//     OR-merge (carry kept for even exponent fields, lost for odd ones); saturation is an integer min;
+//   * below 2^(1-bias): the single subnormal binade comes from the 9-entry table, anything below
+//     2^-bias is zero.
 template <class F>
 MXQ_HD uint32_t qdq_f32_fast(uint32_t u, const F& f) {
-    const int eb = f.eb(), fb = f.fb();
+    constexpr int fb = F{}.fb(), eb = F{}.eb();
+    static_assert(fb >= 1 && fb <= 3 && eb <= 5, "table-driven subnormal path covers the built-in presets");
+    constexpr int sh = 23 - fb;
+    constexpr int bias = (1 << (eb - 1)) - 1;
+    constexpr uint32_t cbits = (uint32_t)(127 + 23 - fb) << 23;           // 2^(23-fb)
     uint32_t a = u & 0x7FFFFFFFu;
-    uint32_t sign = f32_bits(add_rn(bits_f32(u), 0.0f)) & 0x80000000u;
+    uint32_t s = f32_bits(add_rn(bits_f32(u), 0.0f));                     // sign bit: set for x < 0 only
     if (a >= 0x7F800000u) {                       // Inf / NaN: rare; same rule as encode_f32_fast
         const bool is_nan = a > 0x7F800000u;
         a = (126u << 23) | (is_nan ? ((a & 0x7FFFFFu) | 0x400000u) : 0u);
-        sign = is_nan ? 0u : (u & 0x80000000u);
+        s = is_nan ? 0u : u;
     }
-    int code = encode_mag_fp(a & 0xFFFFFF00u, f);
-    const int cmax = (fmt_emax(f) << fb) | ((1 << fb) - 1);
-    code = code > cmax ? cmax : code;
-    const float v = mul_rn(bits_f32((uint32_t)(code * rt_k(0)) << (23 - fb)), bits_f32((uint32_t)(254 - fmt_bias(f)) << 23));
-    (void)eb;
-    return f32_bits(v) | sign;
+    // mantissa cut to 15 bits, tagged with exponent 0, rounded half-to-even to fb bits by the add:
+    // the sum's bits are cbits + 2^fb + fr, fr in [0, 2^fb]
+    const uint32_t sum = f32_bits(add_rn(bits_f32((a & 0x007FFF00u) | 0x3F800000u), bits_f32(cbits)));
+    // (sum << sh) = 2^23 + (fr << sh) modulo 2^32; written as a multiply-add for the FMA pipe
+    const uint32_t z = sum * (uint32_t)rt_pow2_shift(fb) - 0x800000u;
+    uint32_t y = (a & 0x7F800000u) | z;
+    constexpr int emax = F{}.fin() ? (1 << eb) - 1 : (1 << eb) - 2;
+    constexpr uint32_t ymax = ((uint32_t)(emax - bias + 127) << 23) | (((1u << fb) - 1u) << sh);
+    y = y > ymax ? ymax : y;
+    if (bits_f32(a) < bits_f32((uint32_t)(128 - bias) << 23)) {            // |x| < 2^(1-bias)
+        const uint32_t idx4 = sum * (uint32_t)rt_k(1) - (cbits + (1u << fb)) * 4u;          // 4 * fr (modulo 2^32)
+        uint32_t c0 = (uint32_t)(subnormal_table<fb>() >> idx4) & 0xFu;
+        c0 = bits_f32(a) < bits_f32((uint32_t)(127 - bias) << 23) ? 0u : c0;         // below the binade: zero
+        y = f32_bits(mul_rn(bits_f32(c0 * (uint32_t)rt_pow2_shift(fb)), bits_f32((uint32_t)(254 - bias) << 23)));
+    }
+    (void)f;
+    return y | (s & 0x80000000u);
 }
 
 // ---------------------------------------------------------------------------------------------
