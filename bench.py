@@ -463,6 +463,7 @@ def small_cases():
     for which in ("extract", "compose", "qdq"):
         cases[f"mxfp8_{which}_f32"] = (lambda w=which: mx_case(synthetic.cfg1_mxfp8_fp32, (8192, 8192), MXFP8_E4M3_fn, 4, w))
         cases[f"mxfp4_{which}_bf16"] = (lambda w=which: mx_case(synthetic.cfg3_mxfp4_bf16, (8192, 8192), OCP_MXFP4_E2M1, 2, w))
+        cases[f"mxfp8_{which}_bf16"] = (lambda w=which: mx_case(synthetic.cfg3_mxfp4_bf16, (8192, 8192), MXFP8_E4M3_fn, 2, w))
     return cases
 
 

@@ -261,19 +261,41 @@ MXQ_HD uint32_t decode_f32_fast(uint32_t code, const F& f) {
     return y | sign;
 }
 
-// The value is built directly in the fp32 bit domain, without forming the code:
+// Quantised magnitude of a finite value, built directly in the fp32 bit domain without forming
+// the code (RN presets):
 //   * normal range (biased exponent >= 1): the rounded mantissa field fr << (23-fb) is OR-ed under
 //     the input's own exponent field -- fr = 2^fb lands on exponent bit 23, which is the reference's
-//     OR-merge (carry kept for even exponent fields, lost for odd ones); saturation is an integer min;
+//     OR-merge (carry kept for even exponent fields, lost for odd ones);
 //   * below 2^(1-bias): the single subnormal binade comes from the 9-entry table, anything below
 //     2^-bias is zero.
+// qb: fp32 bits of the value (sign ignored, mantissa cut to 15 bits here). No saturation.
+template <class F>
+MXQ_HD uint32_t qdq_mag_bits(uint32_t qb, const F& f) {
+    constexpr int fb = F{}.fb(), eb = F{}.eb();
+    static_assert(fb >= 1 && fb <= 3 && eb <= 5, "table-driven subnormal path covers the built-in presets");
+    constexpr int bias = (1 << (eb - 1)) - 1;
+    constexpr uint32_t cbits = (uint32_t)(127 + 23 - fb) << 23;           // 2^(23-fb)
+    // mantissa cut to 15 bits, tagged with exponent 0, rounded half-to-even to fb bits by the add:
+    // the sum's bits are cbits + 2^fb + fr, fr in [0, 2^fb]
+    const uint32_t sum = f32_bits(add_rn(bits_f32((qb & 0x007FFF00u) | 0x3F800000u), bits_f32(cbits)));
+    // (sum << (23-fb)) = 2^23 + (fr << (23-fb)) modulo 2^32; written as a multiply-add for the FMA pipe
+    const uint32_t z = sum * (uint32_t)rt_pow2_shift(fb) - 0x800000u;
+    uint32_t y = (qb & 0x7F800000u) | z;
+    const float mag = __builtin_fabsf(bits_f32(qb));
+    if (mag < bits_f32((uint32_t)(128 - bias) << 23)) {                    // |q| < 2^(1-bias)
+        const uint32_t idx4 = sum * (uint32_t)rt_k(1) - (cbits + (1u << fb)) * 4u;          // 4 * fr (modulo 2^32)
+        uint32_t c0 = (uint32_t)(subnormal_table<fb>() >> idx4) & 0xFu;
+        c0 = mag < bits_f32((uint32_t)(127 - bias) << 23) ? 0u : c0;       // below the binade: zero
+        y = f32_bits(mul_rn(bits_f32(c0 * (uint32_t)rt_pow2_shift(fb)), bits_f32((uint32_t)(254 - bias) << 23)));
+    }
+    (void)f;
+    return y;
+}
+
 template <class F>
 MXQ_HD uint32_t qdq_f32_fast(uint32_t u, const F& f) {
     constexpr int fb = F{}.fb(), eb = F{}.eb();
-    static_assert(fb >= 1 && fb <= 3 && eb <= 5, "table-driven subnormal path covers the built-in presets");
-    constexpr int sh = 23 - fb;
     constexpr int bias = (1 << (eb - 1)) - 1;
-    constexpr uint32_t cbits = (uint32_t)(127 + 23 - fb) << 23;           // 2^(23-fb)
     uint32_t a = u & 0x7FFFFFFFu;
     uint32_t s = f32_bits(add_rn(bits_f32(u), 0.0f));                     // sign bit: set for x < 0 only
     if (a >= 0x7F800000u) {                       // Inf / NaN: rare; same rule as encode_f32_fast
@@ -281,22 +303,10 @@ MXQ_HD uint32_t qdq_f32_fast(uint32_t u, const F& f) {
         a = (126u << 23) | (is_nan ? ((a & 0x7FFFFFu) | 0x400000u) : 0u);
         s = is_nan ? 0u : u;
     }
-    // mantissa cut to 15 bits, tagged with exponent 0, rounded half-to-even to fb bits by the add:
-    // the sum's bits are cbits + 2^fb + fr, fr in [0, 2^fb]
-    const uint32_t sum = f32_bits(add_rn(bits_f32((a & 0x007FFF00u) | 0x3F800000u), bits_f32(cbits)));
-    // (sum << sh) = 2^23 + (fr << sh) modulo 2^32; written as a multiply-add for the FMA pipe
-    const uint32_t z = sum * (uint32_t)rt_pow2_shift(fb) - 0x800000u;
-    uint32_t y = (a & 0x7F800000u) | z;
+    uint32_t y = qdq_mag_bits(a, f);
     constexpr int emax = F{}.fin() ? (1 << eb) - 1 : (1 << eb) - 2;
-    constexpr uint32_t ymax = ((uint32_t)(emax - bias + 127) << 23) | (((1u << fb) - 1u) << sh);
-    y = y > ymax ? ymax : y;
-    if (bits_f32(a) < bits_f32((uint32_t)(128 - bias) << 23)) {            // |x| < 2^(1-bias)
-        const uint32_t idx4 = sum * (uint32_t)rt_k(1) - (cbits + (1u << fb)) * 4u;          // 4 * fr (modulo 2^32)
-        uint32_t c0 = (uint32_t)(subnormal_table<fb>() >> idx4) & 0xFu;
-        c0 = bits_f32(a) < bits_f32((uint32_t)(127 - bias) << 23) ? 0u : c0;         // below the binade: zero
-        y = f32_bits(mul_rn(bits_f32(c0 * (uint32_t)rt_pow2_shift(fb)), bits_f32((uint32_t)(254 - bias) << 23)));
-    }
-    (void)f;
+    constexpr uint32_t ymax = ((uint32_t)(emax - bias + 127) << 23) | (((1u << fb) - 1u) << (23 - fb));
+    y = y > ymax ? ymax : y;                      // saturate (emax is odd: a carry at emax was already dropped)
     return y | (s & 0x80000000u);
 }
 
@@ -387,6 +397,14 @@ MXQ_HD uint32_t mx_encode_fast(uint32_t u, float inv_scale, const F& f) {
     const uint32_t qb = mx_quotient_bits(u, inv_scale);
     const uint32_t code = (uint32_t)encode_mag_fp(qb, f);
     return code | ((qb >> (31 - f.eb() - f.fb())) & (1u << (f.eb() + f.fb())));
+}
+
+// Fast fused MXFP quantize-dequantize of one element of a finite block (RN presets): the quantised
+// quotient, built in the fp32 bit domain, times 2^se; the sign is that of the non-zero quotient.
+template <class F>
+MXQ_HD uint32_t mx_qdq_fast(uint32_t u, float inv_scale, float scale, const F& f) {
+    const uint32_t qb = mx_quotient_bits(u, inv_scale);
+    return f32_bits(mul_rn(bits_f32(qdq_mag_bits(qb, f)), scale)) | (qb & 0x80000000u);
 }
 
 // MXFP compose of one element (mxfp/fake.py:71-78): decode(code) * 2^(scale-127) in fp32.

@@ -270,6 +270,17 @@ __device__ __forceinline__ void mxfp_b32_quant_tile(const char* __restrict__ src
                 continue;
             }
         }
+        if constexpr (MODE == MODE_QDQ) {
+            if (!(h & 1u)) {
+                const float inv = __uint_as_float(h & 0x7F800000u);
+                const float sf = scale_from_byte((h >> 8) & 0xFFu);       // never 255 for a finite block
+                uint32_t y[V];
+#pragma unroll
+                for (int i = 0; i < V; ++i) y[i] = mx_qdq_fast(pack_bits<KIn>(p[j], i), inv, sf, f);
+                store_results<KIn, V>(d, y, true);
+                continue;
+            }
+        }
         if (!(h & 1u)) {
             const float inv = __uint_as_float(h & 0x7F800000u);
             uint32_t qb[V], mag[V];
@@ -304,17 +315,6 @@ __device__ __forceinline__ void mxfp_b32_quant_tile(const char* __restrict__ src
 #pragma unroll
                 for (int i = 0; i < V; i += 4) o.w[i >> 2] = pack4_codes(&mag[i], &qb[i], f);
                 store_pack<V>(d, o);
-            } else {
-                const uint32_t sb = (h >> 8) & 0xFFu;       // never 255 for a finite block
-                const float sf = scale_from_byte(sb);
-                const float unbias = __uint_as_float((uint32_t)(254 - fmt_bias(f)) << 23);
-                uint32_t y[V];
-#pragma unroll
-                for (int i = 0; i < V; ++i) {
-                    const float v = __fmul_rn(__uint_as_float((uint32_t)((int)mag[i] * rt_k(0)) << (23 - f.fb())), unbias);
-                    y[i] = __float_as_uint(__fmul_rn(v, sf)) | (qb[i] & 0x80000000u);
-                }
-                store_results<KIn, V>(d, y, true);
             }
         } else {
             uint32_t code[V];

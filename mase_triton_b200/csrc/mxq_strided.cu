@@ -176,6 +176,8 @@ __global__ void __launch_bounds__(kThreads, MODE == MODE_QDQ ? 2 : 1) mxfp_strid
                 uint32_t y[CPT];
 #pragma unroll
                 for (int col = 0; col < CPT; ++col) {
+                    // code then decode (cheaper here than the bit-domain form, whose sub-range test would
+                    // be a branch in each of the 32 x CPT unrolled element slots)
                     const uint32_t qb = mx_quotient_bits(column_bits<CPT, KIn>(raw[k], col), inv[col]);
                     const uint32_t mag = (uint32_t)encode_mag_fp(qb, f);
                     const float v = __fmul_rn(__uint_as_float((uint32_t)((int)mag * rt_k(0)) << (23 - f.fb())), unbias);

@@ -88,3 +88,26 @@ extern "C" int hc_mxfp_compose(const uint8_t* scales, const uint8_t* el, uint32_
 }
 
 extern "C" int hc_log2_roundup_count(int e) { return log2_roundup_count(e); }
+
+// fused quantize-dequantize of 32-blocks with the kernels' fast arithmetic (finite blocks) and the
+// generic encode + decode for blocks holding Inf/NaN
+template <class F>
+static void mx_qdq_blocks(const uint32_t* bits, uint32_t* out, int64_t nb, int B, const F& f) {
+    for (int64_t b = 0; b < nb; ++b) {
+        uint32_t amax = 0;
+        for (int j = 0; j < B; ++j) { const uint32_t a = bits[b * B + j] & 0x7FFFFFFFu; amax = a > amax ? a : amax; }
+        uint32_t sbyte;
+        const int se = shared_exponent(amax, f, &sbyte);
+        const bool special = amax >= 0x7F800000u;
+        const float inv = bits_f32((amax >> 23) == 0u ? 0x3F800000u : (uint32_t)(127 - se) << 23);
+        const float sf = bits_f32(sbyte == 0u ? 0x00400000u : (sbyte << 23));
+        for (int j = 0; j < B; ++j) {
+            const uint32_t u = bits[b * B + j];
+            out[b * B + j] = special ? mx_decode(mx_encode(u, se, f), sf, f) : mx_qdq_fast(u, inv, sf, f);
+        }
+    }
+}
+
+extern "C" int hc_mxfp_qdq(const uint32_t* bits, uint32_t* out, int64_t n, int B, int eb, int fb, int fin, int rm) {
+    return with_preset(eb, fb, fin, rm, [&](auto f) { mx_qdq_blocks(bits, out, n / B, B, f); }) ? 1 : 0;
+}

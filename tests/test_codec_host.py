@@ -32,6 +32,7 @@ def hc():
     L.hc_minifloat_qdq.argtypes = [p, p, i64, i, i, i, i, i]
     L.hc_mxfp_extract.argtypes = [p, p, p, i64, i, i, i, i, i, i]
     L.hc_mxfp_compose.argtypes = [p, p, p, i64, i, i, i, i, i]
+    L.hc_mxfp_qdq.argtypes = [p, p, i64, i, i, i, i, i]
     L.hc_log2_roundup_count.argtypes = [i]
     return L
 
@@ -118,6 +119,24 @@ def test_mxfp_extract_random_normal_data(hc, name):
     s_o, e_o = oracle.extract_mxfp_components(x, mx_meta(eb, fb))
     assert_bits_equal(sc.reshape(-1, 1), s_o, "scales")
     assert_bits_equal(el.reshape(-1, 32), e_o, "elements")
+
+
+@pytest.mark.parametrize("name", list(PRESETS))
+def test_mxfp_fused_qdq(hc, name):
+    """The fused quantize-dequantize arithmetic (value built in the fp32 bit domain) against
+    compose(extract(x)) of the oracle, fp32 results, for inputs of every kernel dtype."""
+    eb, fb = PRESETS[name]
+    meta = mx_meta(eb, fb)
+    g = torch.Generator().manual_seed(8)
+    cases = [adversarial_mx_blocks(4096, 32), adversarial_mx_blocks(4096, 32, seed=3),
+             torch.randn(4096, 32, generator=g) * torch.exp(2.0 * torch.randn(4096, 1, generator=g))]
+    for base in cases:
+        for dt in (torch.float32, torch.bfloat16, torch.float16):
+            x = base.to(dt).float().flatten().contiguous()
+            out = torch.empty(x.numel(), dtype=torch.int32)
+            assert hc.hc_mxfp_qdq(x.data_ptr(), out.data_ptr(), x.numel(), 32, eb, fb, 1, 0) == 1
+            s_o, e_o = oracle.extract_mxfp_components(x, meta)
+            assert_bits_equal(out.view(torch.float32), oracle.compose_mxfp_tensor(s_o, e_o, meta, torch.float32), f"{name} {dt}")
 
 
 @pytest.mark.parametrize("name", list(PRESETS))
