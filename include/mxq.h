@@ -142,6 +142,9 @@ int64_t mxq_mx_sf_bytes(int64_t rows, int64_t K, int operand);
  *   hw_sf              : E8M0 scales in 512-byte chunks per (128 rows, 128 K), mxq_mx_sf_bytes() long,
  *                        tiled for `operand` (MXQ_OPERAND_A or MXQ_OPERAND_B)
  *   *hw_format (host)  : 0 = E4M3, 1 = E5M2
+ * `scales` may be NULL: every block then has scale 2^0, which is how per-tensor minifloat codes
+ * (low byte of the uint16 codes of mxq_minifloat_extract, formats of at most 8 bits) are fed to the
+ * same GEMM for minifloat_linear (src/mase_triton/minifloat/functional/linear.py:108-171).
  * FP6/FP4 element values are exactly representable in E4M3. A block holding a value the hardware
  * format cannot encode (reference E4M3 480, reference E5M2 top binade) is stored with its scale
  * raised by one and its elements halved.

@@ -461,7 +461,7 @@ __global__ void __launch_bounds__(256) mx_pack_kernel(const uint8_t* __restrict_
     uint4* dst = reinterpret_cast<uint4*>(hw_codes + blk * 32);
     dst[0] = o[0];
     dst[1] = o[1];
-    const uint32_t s = scales[blk];
+    const uint32_t s = scales != nullptr ? scales[blk] : 127u;           // no scales: every block is 2^0
     *sf_dst = (uint8_t)((any_bad && s < 255u) ? s + 1u : s);
 }
 
@@ -589,7 +589,7 @@ extern "C" int64_t mxq_mx_sf_bytes(int64_t rows, int64_t K, int operand) {
 
 extern "C" int mxq_mx_pack_operand(const uint8_t* scales, const uint8_t* elements, int64_t rows, int64_t K, int eb, int fb,
                                    int operand, uint8_t* hw_codes, uint8_t* hw_sf, int* hw_format, void* stream) {
-    if (rows <= 0 || K <= 0 || K % 32 != 0 || (operand & ~1) || !scales || !elements || !hw_codes || !hw_sf || !hw_format) return MXQ_EINVAL;
+    if (rows <= 0 || K <= 0 || K % 32 != 0 || (operand & ~1) || !elements || !hw_codes || !hw_sf || !hw_format) return MXQ_EINVAL;
     if ((reinterpret_cast<uintptr_t>(elements) | reinterpret_cast<uintptr_t>(hw_codes)) % 16 != 0) return MXQ_EINVAL;
     gemm::PackTables t;
     if (!gemm::build_pack_tables(eb, fb, &t, hw_format)) return MXQ_EINVAL;

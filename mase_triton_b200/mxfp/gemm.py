@@ -57,22 +57,32 @@ def check_status(device: torch.device) -> None:
 OPERAND_A, OPERAND_B = 0, 1
 
 
-def pack_operand(scales: Tensor, elements: Tensor, rows: int, K: int, meta: MXFPMeta, operand: int) -> PackedOperand:
-    """Reference ``(scales, elements)`` of a ``[rows, K]`` tensor blocked along K -> ``PackedOperand``
-    laid out for the left (``OPERAND_A``) or right (``OPERAND_B``) side of the GEMM."""
+def pack_codes(scales: Tensor | None, elements: Tensor, rows: int, K: int, exp_bits: int, frac_bits: int, operand: int) -> PackedOperand:
+    """Element codes (one per byte, sign at bit ``exp_bits + frac_bits``) of a ``[rows, K]`` tensor and the
+    E8M0 scales of its 32-element blocks along K (``None``: every scale is 2^0, i.e. per-tensor minifloat
+    codes) -> ``PackedOperand`` for the left (``OPERAND_A``) or right (``OPERAND_B``) side of the GEMM."""
     _lib.require_cuda(elements, "pack_operand")
-    assert supported(meta) and K % 32 == 0 and elements.numel() == rows * K and scales.numel() == rows * K // 32
-    scales, elements = scales.contiguous(), elements.contiguous()
+    assert elements.dtype == torch.uint8 and K % 32 == 0 and elements.numel() == rows * K
+    assert scales is None or (scales.dtype == torch.uint8 and scales.numel() == rows * K // 32)
+    elements = elements.contiguous()
+    scales = None if scales is None else scales.contiguous()
     L = _lib.load()
     dev = elements.device
     codes = torch.empty((rows, K), dtype=torch.uint8, device=dev)
     sf = torch.empty((L.mxq_mx_sf_bytes(rows, K, operand),), dtype=torch.uint8, device=dev)
     fmt = ctypes.c_int(0)
     with torch.cuda.device(dev):
-        rc = L.mxq_mx_pack_operand(scales.data_ptr(), elements.data_ptr(), rows, K, meta.element_exp_bits, meta.element_frac_bits,
+        rc = L.mxq_mx_pack_operand(None if scales is None else scales.data_ptr(), elements.data_ptr(), rows, K, exp_bits, frac_bits,
                                    operand, codes.data_ptr(), sf.data_ptr(), ctypes.addressof(fmt), _lib.stream_ptr(dev))
     _lib.check(rc, "mxq_mx_pack_operand")
     return PackedOperand(codes, sf, fmt.value, rows, K, operand)
+
+
+def pack_operand(scales: Tensor, elements: Tensor, rows: int, K: int, meta: MXFPMeta, operand: int) -> PackedOperand:
+    """Reference ``(scales, elements)`` of a ``[rows, K]`` tensor blocked along K -> ``PackedOperand``
+    laid out for the left (``OPERAND_A``) or right (``OPERAND_B``) side of the GEMM."""
+    assert supported(meta)
+    return pack_codes(scales, elements, rows, K, meta.element_exp_bits, meta.element_frac_bits, operand)
 
 
 def quantize_pack(x: Tensor, meta: MXFPMeta, operand: int = OPERAND_A) -> PackedOperand:

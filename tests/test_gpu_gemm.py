@@ -160,3 +160,25 @@ def test_gather_epilogue_writes_every_destination(lib, dtype, M, N, K):
     for o in outs:
         assert torch.equal(o[:M, off:off + N].view(torch.uint8), want.view(torch.uint8))
         assert bool((o[:M, :off] == 7).all()) and bool((o[:M, off + N:] == 7).all()) and bool((o[M:] == 7).all())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_minifloat_linear_fused_saturating_activation(lib, dtype):
+    """Per-tensor minifloat codes through the block-scaled GEMM with unit scales: saturated values
+    (reference E4M3 480, which the hardware format cannot hold) and signed zeros included."""
+    from mase_triton_b200.minifloat import functional as MF
+    from mase_triton_b200.minifloat.meta import FP6_E2M3_fn, FP8_E4M3_fn, FP8_E5M2_fn
+    torch.manual_seed(21)
+    for x_meta, w_meta in [(FP8_E4M3_fn, FP8_E4M3_fn), (FP8_E5M2_fn, FP6_E2M3_fn)]:
+        x = (torch.randn((3, 50, 256), device=DEV) * 300).to(dtype)          # many values beyond the largest code
+        x[0, 0, :8] = torch.tensor([0.0, -0.0, 1e-9, -1e-9, 480.0, -480.0, 1e6, -1e6], device=DEV).to(dtype)
+        w = (torch.randn((96, 256), device=DEV) * 0.2).to(dtype)
+        w_el, w_tm = MF.extract_minifloat_component(w, w_meta)
+        bias = torch.randn((96,), device=DEV).to(dtype)
+        y_sep = MF.minifloat_linear(x, x_meta, None, w_el, w_tm, bias, None, None, "XqWqB", "separate")
+        y_fus = MF.minifloat_linear(x, x_meta, None, w_el, w_tm, bias, None, None, "XqWqB", "fused")
+        G.check_status(DEV)
+        assert y_fus.shape == y_sep.shape == (3, 50, 96) and y_fus.dtype == dtype
+        x_dq = MF.quantize_dequantize(x, x_meta).float()
+        w_dq = MF.compose_minifloat_component(w_el, w_tm).float()
+        assert within_tolerance(y_fus, torch.nn.functional.linear(x_dq, w_dq, bias.float()))
