@@ -452,7 +452,21 @@ def small_cases():
         return (lambda: permute_for_dequantize(mxk.quantize_dequantize(flatten_for_quantize(x, 0), meta, x.dtype),
                                                tuple(x.shape), 0).contiguous()), n * 2 * s_in
 
+    def minifloat_linear_case(M, N, K, backend):
+        """MinifloatLinearPTQ with FP8 activation and weight: tensor-core codes (fused) against dequantise + library GEMM"""
+        from mase_triton_b200.minifloat.layers import MinifloatLinearPTQ
+        from mase_triton_b200.minifloat.meta import FP8_E4M3_fn
+        g = torch.Generator().manual_seed(0)
+        x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(dev)
+        fc = torch.nn.Linear(K, N, bias=False, device=dev, dtype=torch.bfloat16)
+        with torch.no_grad():
+            fc.weight.copy_((0.02 * torch.randn(N, K, generator=g)).to(torch.bfloat16))
+        layer = MinifloatLinearPTQ.from_linear(fc, FP8_E4M3_fn, FP8_E4M3_fn, None, "XqWqB", backend)
+        return (lambda: layer(x)), 2.0 * M * N * K
+
     cases = {"minifloat_qdq_f32": minifloat_qdq_f32}
+    for backend in ("fused", "separate"):
+        cases[f"mx_minifloat_linear_{backend}_cfg4"] = (lambda b=backend: minifloat_linear_case(8192, 14336, 4096, b))
     for which in ("extract", "qdq"):
         for route in ("strided", "permuted"):
             cases[f"mxfp8_{which}_dim0_{route}_f32"] = (lambda w=which, r=route: strided_case(synthetic.cfg1_mxfp8_fp32, MXFP8_E4M3_fn, 4, w, r))
@@ -478,7 +492,7 @@ def run_case(name: str, steps: int, warmup: int) -> None:
     ts = time_steps(fn, steps)
     t = statistics.median(ts)
     peak, kind = measured_peaks()
-    if name.startswith("mx_gemm") or name.startswith("mx_linear") or name.startswith("mx_separate"):
+    if name.startswith("mx_gemm") or name.startswith("mx_linear") or name.startswith("mx_separate") or name.startswith("mx_minifloat"):
         print(json.dumps({"case": name, "steps": steps, "median_ms": round(t, 5), "TFLOPs": round(nbytes / t / 1e9, 1),
                           "frac_of_4500_nominal_mx": round(nbytes / t / 1e9 / 4500, 4)}), flush=True)
         return

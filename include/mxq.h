@@ -163,6 +163,16 @@ int mxq_mx_quantize_pack(const void* x, int x_dtype, int64_t M, int64_t K, int e
                          uint8_t* hw_codes, uint8_t* hw_sf, int* hw_format, void* stream);
 
 /*
+ * The same one-pass route for a per-tensor minifloat activation (minifloat_linear with layer type
+ * XqWq*, src/mase_triton/minifloat/functional/linear.py:36-64): x [M,K] is quantised to FP8 E4M3 or
+ * E5M2 (is_finite, round to nearest) and written as hardware codes with unit scale chunks.
+ * MXQ_ESIZE for other formats, rounding modes or unaligned buffers (then: mxq_minifloat_extract,
+ * narrow the codes to bytes, mxq_mx_pack_operand with scales = NULL).
+ */
+int mxq_minifloat_quantize_pack(const void* x, int x_dtype, int64_t M, int64_t K, int exp_bits, int frac_bits,
+                                int round_mode, uint8_t* hw_codes, uint8_t* hw_sf, int* hw_format, void* stream);
+
+/*
  * out[M,N] = A[M,K] * B[N,K]^T (+ bias[N]) on operands packed as MXQ_OPERAND_A / MXQ_OPERAND_B,
  * fp32 accumulation in tensor memory.
  * out_dtype / bias dtype: MXQ_F32, MXQ_BF16 or MXQ_F16 (bias may be NULL). K % 32 == 0.

@@ -576,6 +576,42 @@ extern "C" int mxq_mxfp_compose(const uint8_t* scales, const uint8_t* elements, 
     return rc;
 }
 
+// Per-tensor minifloat (FP8 E4M3 / E5M2, round to nearest, is_finite) quantisation of a [M, K]
+// activation straight into the tensor-core operand layout: hardware FP8 codes and left-operand scale
+// chunks holding 2^0 (2^1 for a 32-element group that contains the reference's saturated E4M3 480 or
+// an E5M2 top-binade value, whose codes are halved).  One lane per 16 input bytes; the 4 or 8 lanes
+// of a 32-element group agree on the re-bias with shuffles.
+template <class KIn, class F>
+__global__ void __launch_bounds__(kThreads) minifloat_hwpack_kernel(const void* __restrict__ x, uint8_t* __restrict__ hw_codes,
+                                                                    uint8_t* __restrict__ hw_sf, int64_t n_vec, F f, PackGeom geom) {
+    constexpr int V = 16 / KIn::size;
+    constexpr int G = 32 / V;
+    const int64_t idx = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    const bool active = idx < n_vec;                 // whole groups are active or not: n_vec is a multiple of G
+    const int lane = threadIdx.x & 31;
+    Pack<16> p = active ? load_pack<16>(reinterpret_cast<const char*>(x) + idx * 16) : Pack<16>{{0u, 0u, 0u, 0u}};
+    constexpr uint32_t hw_max = (F{}.eb() == 4) ? 0x7Eu : 0x7Bu;
+    uint32_t code[V];
+    uint32_t bad = 0;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        code[i] = encode_f32_fast(pack_bits<KIn>(p, i), f);          // sign at bit 7 for the 8-bit formats
+        bad |= ((code[i] & 0x7Fu) > hw_max) ? 1u : 0u;
+    }
+#pragma unroll
+    for (int o = 1; o < G; o <<= 1) bad |= __shfl_xor_sync(0xFFFFFFFFu, bad, o);
+    if (!active) return;
+    Pack<V> out;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        uint32_t mag = code[i] & 0x7Fu;
+        if (bad) mag = (mag >= (2u << f.fb())) ? mag - (1u << f.fb()) : (mag + ((mag >> 1) & 1u)) >> 1;
+        pack_set<1>(out, i, mag | (code[i] & 0x80u));
+    }
+    store_pack<V>(hw_codes + idx * V, out);
+    if ((lane & (G - 1)) == 0) hw_sf[sf_chunk_offset((uint32_t)(idx / G), geom)] = (uint8_t)(bad ? 128u : 127u);
+}
+
 // Quantise a [M, K] activation to MXFP8 (32-element blocks along K) straight into the tensor-core
 // operand layout of mxq_gemm.cu: hardware FP8 codes [M, K] and left-operand scale-factor chunks.
 // One pass over x instead of extract + pack. Declared in mxq_internal.h; returns MXQ_ESIZE when the
@@ -608,6 +644,35 @@ int quantize_pack_left_operand(const void* x, int x_dtype, int64_t M, int64_t K,
         else
             mxfp_b32_quant_kernel<KIn, FmtCT<5, 2, true, RM_RN>, U, MODE_HWPACK><<<(unsigned)grid, kThreads, 0, st>>>(
                 x, hw_sf, hw_codes, nullptr, n_vec, FmtCT<5, 2, true, RM_RN>{}, g);
+        rc = check_launch();
+    });
+    return rc;
+}
+
+// The same for per-tensor minifloat codes (unit block scales); declared in mxq_internal.h.
+int minifloat_quantize_pack_left_operand(const void* x, int x_dtype, int64_t M, int64_t K, int eb, int fb, uint8_t* hw_codes,
+                                         uint8_t* hw_sf, int64_t sf_bytes, int* hw_format, cudaStream_t st) {
+    const bool e4m3 = (eb == 4 && fb == 3), e5m2 = (eb == 5 && fb == 2);
+    if (!(e4m3 || e5m2) || K % 32 != 0 || M * K / 32 >= (1ll << 31)) return MXQ_ESIZE;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(hw_codes)) % 16 != 0) return MXQ_ESIZE;
+    *hw_format = e5m2 ? 1 : 0;
+    if (cudaMemsetAsync(hw_sf, 127, (size_t)sf_bytes, st) != cudaSuccess) return check_launch();
+    PackGeom g;
+    g.kbpr = (uint32_t)(K / 32);
+    g.shift = 0;
+    while ((1u << g.shift) < g.kbpr) ++g.shift;
+    g.magic = (uint32_t)((((uint64_t)1 << (31 + g.shift)) + g.kbpr - 1) / g.kbpr);
+    g.KT = (uint32_t)((K + 127) / 128);
+    int rc = MXQ_OK;
+    with_kind(x_dtype, [&](auto kin) {
+        using KIn = decltype(kin);
+        constexpr int V = 16 / KIn::size;
+        const int64_t n_vec = M * K / V;
+        const int64_t grid = (n_vec + kThreads - 1) / kThreads;
+        if (e4m3)
+            minifloat_hwpack_kernel<KIn, FmtCT<4, 3, true, RM_RN>><<<(unsigned)grid, kThreads, 0, st>>>(x, hw_codes, hw_sf, n_vec, FmtCT<4, 3, true, RM_RN>{}, g);
+        else
+            minifloat_hwpack_kernel<KIn, FmtCT<5, 2, true, RM_RN>><<<(unsigned)grid, kThreads, 0, st>>>(x, hw_codes, hw_sf, n_vec, FmtCT<5, 2, true, RM_RN>{}, g);
         rc = check_launch();
     });
     return rc;

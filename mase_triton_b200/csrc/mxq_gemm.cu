@@ -735,3 +735,11 @@ extern "C" int mxq_mx_quantize_pack(const void* x, int x_dtype, int64_t M, int64
     return quantize_pack_left_operand(x, x_dtype, M, K, exp_bits, frac_bits, hw_codes, hw_sf, mxq_mx_sf_bytes(M, K, MXQ_OPERAND_A),
                                       hw_format, (cudaStream_t)stream);
 }
+
+extern "C" int mxq_minifloat_quantize_pack(const void* x, int x_dtype, int64_t M, int64_t K, int exp_bits, int frac_bits,
+                                           int round_mode, uint8_t* hw_codes, uint8_t* hw_sf, int* hw_format, void* stream) {
+    if (!x || !hw_codes || !hw_sf || !hw_format || M <= 0 || K <= 0 || K % 32 != 0) return MXQ_EINVAL;
+    if (round_mode != MXQ_RN) return MXQ_ESIZE;
+    return minifloat_quantize_pack_left_operand(x, x_dtype, M, K, exp_bits, frac_bits, hw_codes, hw_sf,
+                                                mxq_mx_sf_bytes(M, K, MXQ_OPERAND_A), hw_format, (cudaStream_t)stream);
+}

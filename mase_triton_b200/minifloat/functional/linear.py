@@ -51,8 +51,10 @@ def _fused_linear(x: Tensor, x_meta: MinifloatMeta, w_element: Tensor, w_tensor_
     from ...mxfp import gemm as _gemm
     k = x.shape[-1]
     x2 = x.reshape(-1, k)
-    codes = kernels.extract_minifloat_component(x2, x_meta).to(torch.uint8)      # the sign sits below bit 8
-    a = _gemm.pack_codes(None, codes, x2.shape[0], k, x_meta.exp_bits, x_meta.frac_bits, _gemm.OPERAND_A)
+    a = _gemm.minifloat_quantize_pack(x2, x_meta.exp_bits, x_meta.frac_bits, x_meta.round_mode)    # FP8: one kernel
+    if a is None:
+        codes = kernels.extract_minifloat_component(x2, x_meta).to(torch.uint8)      # the sign sits below bit 8
+        a = _gemm.pack_codes(None, codes, x2.shape[0], k, x_meta.exp_bits, x_meta.frac_bits, _gemm.OPERAND_A)
     out = _gemm.mx_gemm(a, _packed_weight(w_element, w_tensor_meta), x.dtype, bias=bias)
     return out.reshape(*x.shape[:-1], out.shape[-1])
 

@@ -110,6 +110,27 @@ def quantize_pack_fused(x: Tensor, meta: MXFPMeta) -> PackedOperand:
     return PackedOperand(codes, sf, fmt.value, rows, K, OPERAND_A)
 
 
+def minifloat_quantize_pack(x: Tensor, exp_bits: int, frac_bits: int, round_mode: str) -> PackedOperand | None:
+    """Per-tensor minifloat FP8 quantisation of a ``[..., K]`` activation in one kernel, as a left operand
+    with unit scales.  ``None`` when the library does not cover the format (the caller then extracts,
+    narrows and packs)."""
+    _lib.require_cuda(x, "minifloat_quantize_pack")
+    K = x.shape[-1]
+    rows = x.numel() // K
+    x2 = x.reshape(rows, K).contiguous()
+    L = _lib.load()
+    codes = torch.empty((rows, K), dtype=torch.uint8, device=x.device)
+    sf = torch.empty((L.mxq_mx_sf_bytes(rows, K, OPERAND_A),), dtype=torch.uint8, device=x.device)
+    fmt = ctypes.c_int(0)
+    with torch.cuda.device(x.device):
+        rc = L.mxq_minifloat_quantize_pack(x2.data_ptr(), _lib.DTYPE_ID[x2.dtype], rows, K, exp_bits, frac_bits, _lib.ROUND_ID[round_mode],
+                                           codes.data_ptr(), sf.data_ptr(), ctypes.addressof(fmt), _lib.stream_ptr(x.device))
+    if rc == -3:
+        return None
+    _lib.check(rc, "mxq_minifloat_quantize_pack")
+    return PackedOperand(codes, sf, fmt.value, rows, K, OPERAND_A)
+
+
 def packed_weight(w_scales: Tensor, w_elements: Tensor, shape: tuple[int, int], meta: MXFPMeta) -> PackedOperand:
     """Packed form of a quantised weight.  The result is kept on the ``w_elements`` tensor object itself
     (so it dies with it and can never be confused with another tensor that re-uses the same address)

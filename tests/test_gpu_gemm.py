@@ -182,3 +182,24 @@ def test_minifloat_linear_fused_saturating_activation(lib, dtype):
         x_dq = MF.quantize_dequantize(x, x_meta).float()
         w_dq = MF.compose_minifloat_component(w_el, w_tm).float()
         assert within_tolerance(y_fus, torch.nn.functional.linear(x_dq, w_dq, bias.float()))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_minifloat_one_pass_pack_equals_two_step(lib, dtype):
+    """mxq_minifloat_quantize_pack gives the bytes of extract -> narrow -> pack with unit scales,
+    saturated values, Inf/NaN inputs and ragged row counts included."""
+    from helpers import adversarial_fp32
+    from mase_triton_b200.minifloat import kernels as mfk
+    from mase_triton_b200.minifloat.meta import FP8_E4M3_fn, FP8_E5M2_fn
+    for meta in (FP8_E4M3_fn, FP8_E5M2_fn):
+        for rows, K in ((300, 256), (129, 96), (5, 32)):
+            x = adversarial_fp32(max(rows * K, 4096), seed=rows)[: rows * K].reshape(rows, K).clone()
+            x[0, :4] = torch.tensor([480.0, -480.0, 1e9, float("inf")])
+            x = x.to(dtype).to(DEV)
+            one = G.minifloat_quantize_pack(x, meta.exp_bits, meta.frac_bits, meta.round_mode)
+            assert one is not None
+            codes = mfk.extract_minifloat_component(x, meta).to(torch.uint8)
+            two = G.pack_codes(None, codes, rows, K, meta.exp_bits, meta.frac_bits, G.OPERAND_A)
+            assert one.hw_format == two.hw_format
+            assert torch.equal(one.codes, two.codes), f"{meta.tag} {dtype} {rows}x{K}: codes differ"
+            assert torch.equal(one.sf, two.sf), f"{meta.tag} {dtype} {rows}x{K}: scale chunks differ"
