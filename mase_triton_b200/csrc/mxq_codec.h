@@ -166,8 +166,13 @@ MXQ_HD float add_rn(float a, float b) {
 #endif
 }
 
+// The three pieces of the fast magnitude encode; encode_mag_fp below strings them together and the
+// block quantiser calls them separately so that a whole warp can skip the sub-range piece.
+//   encode_mag_normal : code as if the biased exponent were >= 1 (negative for smaller inputs)
+//   is_subrange       : |q| < 2^(1-bias), i.e. biased exponent <= 0 (q is never NaN here)
+//   subrange_code     : the code of such an input from what encode_mag_normal returned
 template <class F>
-MXQ_HD int encode_mag_fp(uint32_t qb, const F& f) {
+MXQ_HD int encode_mag_normal(uint32_t qb, const F& f) {
     constexpr int fb = F{}.fb(), eb = F{}.eb();
     static_assert(fb >= 1 && fb <= 3 && eb <= 5, "table-driven subnormal path covers the built-in presets");
     constexpr int sh = 23 - fb;
@@ -175,12 +180,27 @@ MXQ_HD int encode_mag_fp(uint32_t qb, const F& f) {
     constexpr uint32_t cbits = (uint32_t)(127 + 23 - fb) << 23;           // 2^(23-fb)
     const float m = bits_f32((qb & 0x007FFFFFu) | 0x3F800000u);
     const int fr = mad_add((int)f32_bits(add_rn(m, bits_f32(cbits))), -(int)(cbits + (1u << fb)));   // 0 .. 2^fb
-    int code = mad_add((int)(((qb >> sh) & (0xFFu << fb)) | (uint32_t)fr), -((127 - bias) << fb));
-    code = code < 0 ? 0 : code;                                            // biased exponent < 0
-    // biased exponent <= 0, i.e. |q| < 2^(1-bias): one float compare with |.| (q is never NaN here)
-    if (__builtin_fabsf(bits_f32(qb)) < bits_f32((uint32_t)(128 - bias) << 23))
-        code = (int)((subnormal_table<fb>() >> (code * rt_k(1))) & 0xFu);
     (void)f;
+    return mad_add((int)(((qb >> sh) & (0xFFu << fb)) | (uint32_t)fr), -((127 - bias) << fb));
+}
+template <class F>
+MXQ_HD bool is_subrange(uint32_t qb, const F& f) {
+    constexpr int bias = (1 << (F{}.eb() - 1)) - 1;
+    (void)f;
+    return __builtin_fabsf(bits_f32(qb)) < bits_f32((uint32_t)(128 - bias) << 23);
+}
+template <class F>
+MXQ_HD int subrange_code(int code, const F& f) {
+    constexpr int fb = F{}.fb();
+    code = code < 0 ? 0 : code;                                            // biased exponent < 0
+    (void)f;
+    return (int)((subnormal_table<fb>() >> (code * rt_k(1))) & 0xFu);
+}
+
+template <class F>
+MXQ_HD int encode_mag_fp(uint32_t qb, const F& f) {
+    int code = encode_mag_normal(qb, f);
+    if (is_subrange(qb, f)) code = subrange_code(code, f);
     return code;
 }
 
@@ -269,26 +289,38 @@ MXQ_HD uint32_t decode_f32_fast(uint32_t code, const F& f) {
 //   * below 2^(1-bias): the single subnormal binade comes from the 9-entry table, anything below
 //     2^-bias is zero.
 // qb: fp32 bits of the value (sign ignored, mantissa cut to 15 bits here). No saturation.
+// qdq_mag_normal returns the normal-range result and the rounding sum that qdq_mag_subrange needs.
 template <class F>
-MXQ_HD uint32_t qdq_mag_bits(uint32_t qb, const F& f) {
+MXQ_HD uint32_t qdq_mag_normal(uint32_t qb, uint32_t* sum_out, const F& f) {
     constexpr int fb = F{}.fb(), eb = F{}.eb();
     static_assert(fb >= 1 && fb <= 3 && eb <= 5, "table-driven subnormal path covers the built-in presets");
-    constexpr int bias = (1 << (eb - 1)) - 1;
     constexpr uint32_t cbits = (uint32_t)(127 + 23 - fb) << 23;           // 2^(23-fb)
     // mantissa cut to 15 bits, tagged with exponent 0, rounded half-to-even to fb bits by the add:
     // the sum's bits are cbits + 2^fb + fr, fr in [0, 2^fb]
     const uint32_t sum = f32_bits(add_rn(bits_f32((qb & 0x007FFF00u) | 0x3F800000u), bits_f32(cbits)));
+    *sum_out = sum;
     // (sum << (23-fb)) = 2^23 + (fr << (23-fb)) modulo 2^32; written as a multiply-add for the FMA pipe
     const uint32_t z = sum * (uint32_t)rt_pow2_shift(fb) - 0x800000u;
-    uint32_t y = (qb & 0x7F800000u) | z;
-    const float mag = __builtin_fabsf(bits_f32(qb));
-    if (mag < bits_f32((uint32_t)(128 - bias) << 23)) {                    // |q| < 2^(1-bias)
-        const uint32_t idx4 = sum * (uint32_t)rt_k(1) - (cbits + (1u << fb)) * 4u;          // 4 * fr (modulo 2^32)
-        uint32_t c0 = (uint32_t)(subnormal_table<fb>() >> idx4) & 0xFu;
-        c0 = mag < bits_f32((uint32_t)(127 - bias) << 23) ? 0u : c0;       // below the binade: zero
-        y = f32_bits(mul_rn(bits_f32(c0 * (uint32_t)rt_pow2_shift(fb)), bits_f32((uint32_t)(254 - bias) << 23)));
-    }
     (void)f;
+    return (qb & 0x7F800000u) | z;
+}
+// |q| < 2^(1-bias): the subnormal binade from the table, zero below it
+template <class F>
+MXQ_HD uint32_t qdq_mag_subrange(uint32_t qb, uint32_t sum, const F& f) {
+    constexpr int fb = F{}.fb(), eb = F{}.eb();
+    constexpr int bias = (1 << (eb - 1)) - 1;
+    constexpr uint32_t cbits = (uint32_t)(127 + 23 - fb) << 23;
+    const uint32_t idx4 = sum * (uint32_t)rt_k(1) - (cbits + (1u << fb)) * 4u;              // 4 * fr (modulo 2^32)
+    uint32_t c0 = (uint32_t)(subnormal_table<fb>() >> idx4) & 0xFu;
+    c0 = __builtin_fabsf(bits_f32(qb)) < bits_f32((uint32_t)(127 - bias) << 23) ? 0u : c0;  // below the binade: zero
+    (void)f;
+    return f32_bits(mul_rn(bits_f32(c0 * (uint32_t)rt_pow2_shift(fb)), bits_f32((uint32_t)(254 - bias) << 23)));
+}
+template <class F>
+MXQ_HD uint32_t qdq_mag_bits(uint32_t qb, const F& f) {
+    uint32_t sum;
+    uint32_t y = qdq_mag_normal(qb, &sum, f);
+    if (is_subrange(qb, f)) y = qdq_mag_subrange(qb, sum, f);
     return y;
 }
 

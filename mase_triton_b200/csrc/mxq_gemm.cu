@@ -68,8 +68,11 @@ struct OutSpec {
     int n, self;
     int64_t ld, col0;
 };
-constexpr int FWD_WARPS = 4;                     // copy-out warps of the gather-fused kernel
-constexpr int STORED_BAR_OFF = 128, ACK_BAR_OFF = 136;   // inside the BAR_BYTES region, past the pipeline barriers
+#ifndef MXQ_FWD_WARPS
+#define MXQ_FWD_WARPS 4
+#endif
+constexpr int FWD_WARPS = MXQ_FWD_WARPS;         // copy-out warps of the gather-fused kernel
+constexpr int STORED_BAR_OFF = 128, ACK_BAR_OFF = 144;   // two barriers each (one per accumulator), inside the BAR_BYTES region past the pipeline barriers
 
 // status codes written to the caller's status word when a bounded wait runs out
 enum : int { ST_OK = 0, ST_PRODUCER_TIMEOUT = 1, ST_MMA_TIMEOUT = 2, ST_EPILOGUE_TIMEOUT = 3, ST_FORWARD_TIMEOUT = 4 };
@@ -260,7 +263,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
     const uint32_t accum_bar = bars + 8u * (2 * STAGES);
     auto tmem_empty_bar = [&](int h) { return bars + 8u * (2 * STAGES + 1 + h); };   // one per accumulator
-    const uint32_t stored_bar = bars + STORED_BAR_OFF, ack_bar = bars + ACK_BAR_OFF;
+    auto stored_bar = [&](int h) { return bars + STORED_BAR_OFF + 8u * h; };
+    auto ack_bar = [&](int h) { return bars + ACK_BAR_OFF + 8u * h; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KT = (K + BK - 1) / BK;
@@ -273,8 +277,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         mbar_init(tmem_empty_bar(0), 4);                             // one arrival per epilogue warp
         mbar_init(tmem_empty_bar(1), 4);
         if constexpr (MULTI) {
-            mbar_init(stored_bar, 4);                                // epilogue warps: "this tile is in local memory"
-            mbar_init(ack_bar, FWD_WARPS);                           // copy-out warps: "seen it"
+            for (int h = 0; h < 2; ++h) {
+                mbar_init(stored_bar(h), 4);                         // epilogue warps: "this accumulator's rows are in local memory"
+                mbar_init(ack_bar(h), FWD_WARPS);                    // copy-out warps: "seen it"
+            }
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -381,13 +387,13 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if constexpr (!MULTI) store_chunk<OUT_DT>(out, bias, r, row, nt * BN + c * 32, M, N, N, 0);
                     else store_chunk<OUT_DT>(outs.ptr[outs.self], bias, r, row, nt * BN + c * 32, M, N, outs.ld, outs.col0);
                 }
-            }
-            if constexpr (MULTI) {
-                // tell the copy-out warps that this warp's rows of the tile are in local memory; they must
-                // have picked up the previous tile first (the barrier holds one tile of slack)
-                if (tcount > 0) ok = mbar_wait(ack_bar, (tcount - 1) & 1, status, ST_EPILOGUE_TIMEOUT);
-                __syncwarp();
-                if (lane == 0) mbar_arrive(stored_bar);
+                if constexpr (MULTI) {
+                    // tell the copy-out warps that this warp's rows of accumulator h are in local memory; they
+                    // must have picked up the same accumulator of the previous tile first (one tile of slack)
+                    if (tcount > 0) ok = mbar_wait(ack_bar(h), (tcount - 1) & 1, status, ST_EPILOGUE_TIMEOUT);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(stored_bar(h));
+                }
             }
         }
     } else {
@@ -399,11 +405,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
                 int mt, nt;
                 tile_coords(tile, MT, NT, mt, nt);
-                ok = mbar_wait(stored_bar, tcount & 1, status, ST_FORWARD_TIMEOUT);
-                if (!ok) break;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(ack_bar);
-                forward_tile<OUT_DT>(outs, fw, lane, mt * C::BM, min(C::BM, M - mt * C::BM), nt * BN, min(BN, N - nt * BN));
+                for (int h = 0; h < MH && ok; ++h) {                  // 128 rows at a time, as the epilogue finishes them
+                    ok = mbar_wait(stored_bar(h), tcount & 1, status, ST_FORWARD_TIMEOUT);
+                    if (!ok) break;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(ack_bar(h));
+                    const int row0 = mt * C::BM + h * 128;
+                    if (row0 < M) forward_tile<OUT_DT>(outs, fw, lane, row0, min(128, M - row0), nt * BN, min(BN, N - nt * BN));
+                }
             }
         }
     }
