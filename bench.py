@@ -307,6 +307,34 @@ def extras_single_gpu(dev, steps: int, warmup: int, peak: float) -> dict:
     sweep["sweep_TFLOPs"] = round(tot_flops / tot_ms / 1e9, 1)
     sweep["sweep_ms"] = round(tot_ms, 4)
     out["cfg5_llama3_8b_layer_fused_linear"] = sweep
+
+    # widening rows: blocks along a non-contiguous dimension, and the minifloat linear on the tensor cores
+    from mase_triton_b200.minifloat.layers import MinifloatLinearPTQ
+    from mase_triton_b200.minifloat.meta import FP8_E4M3_fn
+    from mase_triton_b200.mxfp.helpers import flatten_for_quantize, permute_for_dequantize
+    xs2 = synthetic.cfg1_mxfp8_fp32(shape=(8192, 8192)).to(dev)
+    nb = xs2.numel() * 8
+    t_str = graph_time(lambda: mxk.quantize_dequantize_strided(xs2, 0, MXFP8_E4M3_fn, xs2.dtype), reps)
+    t_perm = graph_time(lambda: permute_for_dequantize(mxk.quantize_dequantize(flatten_for_quantize(xs2, 0), MXFP8_E4M3_fn, xs2.dtype),
+                                                       tuple(xs2.shape), 0).contiguous(), max(3, reps // 2))
+    out["mxfp8_fp32_8192x8192_blocks_along_dim0_fused_qdq"] = {
+        "strided_kernel_GBps": round(nb / t_str / 1e6, 1), "strided_kernel_frac_of_peak": round(nb / t_str / 1e6 / peak, 3),
+        "permuted_copy_route_GBps": round(nb / t_perm / 1e6, 1), "ms": {"strided": round(t_str, 4), "permuted": round(t_perm, 4)}}
+    del xs2
+    torch.cuda.empty_cache()
+    xc, wc = synthetic.cfg4_linear_operands()
+    xc, wc = xc.to(dev), wc.to(dev)
+    flops = 2.0 * xc.shape[0] * wc.shape[0] * xc.shape[1]
+    fc = torch.nn.Linear(xc.shape[1], wc.shape[0], bias=False, device=dev, dtype=torch.bfloat16)
+    with torch.no_grad():
+        fc.weight.copy_(wc)
+    mf_f = MinifloatLinearPTQ.from_linear(fc, FP8_E4M3_fn, FP8_E4M3_fn, None, "XqWqB", "fused")
+    mf_s = MinifloatLinearPTQ.from_linear(fc, FP8_E4M3_fn, FP8_E4M3_fn, None, "XqWqB", "separate")
+    t_mf = graph_time(lambda: mf_f(xc), reps)
+    t_ms = graph_time(lambda: mf_s(xc), max(3, reps // 2))
+    G.check_status(dev)
+    out["cfg4_shape_minifloat_linear_e4m3"] = {"fused_TFLOPs": round(flops / t_mf / 1e9, 1), "separate_TFLOPs": round(flops / t_ms / 1e9, 1),
+                                               "ms": {"fused": round(t_mf, 4), "separate": round(t_ms, 4)}}
     return out
 
 
