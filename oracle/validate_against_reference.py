@@ -2,7 +2,7 @@
 
 Run where the reference checkout is available:
 
-    python oracle/validate_against_reference.py [path/to/reference/src]
+    python oracle/validate_against_reference.py path/to/mase-triton/src
 
 It imports ``mase_triton.minifloat.fake`` / ``mase_triton.mxfp.fake`` from the
 reference and compares them with ``oracle`` on random and adversarial inputs.
@@ -12,6 +12,7 @@ product, the tests or the benchmark.
 
 from __future__ import annotations
 
+import os
 import sys
 from pathlib import Path
 from types import SimpleNamespace
@@ -20,7 +21,9 @@ import torch
 
 ROOT = Path(__file__).resolve().parents[1]
 sys.path.insert(0, str(ROOT))
-REF_SRC = sys.argv[1] if len(sys.argv) > 1 else "/root/reference/src"
+if len(sys.argv) < 2 and "MASE_TRITON_SRC" not in os.environ:
+    raise SystemExit("usage: python " + sys.argv[0] + " <path to the src/ folder of a mase-triton checkout> (or set MASE_TRITON_SRC)")
+REF_SRC = sys.argv[1] if len(sys.argv) > 1 else os.environ["MASE_TRITON_SRC"]
 sys.path.insert(0, REF_SRC)
 
 import oracle  # noqa: E402

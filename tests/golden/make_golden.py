@@ -2,7 +2,7 @@
 
 Run where the reference checkout is available:
 
-    python tests/golden/make_golden.py [path/to/reference/src]
+    python tests/golden/make_golden.py path/to/mase-triton/src
 
 Writes
   * golden_small.npz  - inputs and the reference's outputs for small adversarial cases
@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import hashlib
 import json
+import os
 import sys
 from pathlib import Path
 
@@ -27,7 +28,9 @@ HERE = Path(__file__).resolve().parent
 ROOT = HERE.parents[1]
 sys.path.insert(0, str(ROOT))
 sys.path.insert(0, str(ROOT / "tests"))
-REF_SRC = sys.argv[1] if len(sys.argv) > 1 else "/root/reference/src"
+if len(sys.argv) < 2 and "MASE_TRITON_SRC" not in os.environ:
+    raise SystemExit("usage: python " + sys.argv[0] + " <path to the src/ folder of a mase-triton checkout> (or set MASE_TRITON_SRC)")
+REF_SRC = sys.argv[1] if len(sys.argv) > 1 else os.environ["MASE_TRITON_SRC"]
 sys.path.insert(0, REF_SRC)
 
 from helpers import PRESETS, adversarial_fp32, adversarial_mx_blocks  # noqa: E402
