@@ -141,21 +141,23 @@ __device__ __forceinline__ uint32_t sf_chunk_offset(uint32_t blk, const PackGeom
 
 // ------------------------------------------------------------------------------------------------
 // MXFP4 (E2M1) elements of bf16 inputs, two elements per 32-bit word on the packed bf16 units.
-// With only eight magnitudes the code is a staircase in the quotient q = |x| * 2^-se (exact in
-// bf16 for a power-of-two factor; below 2^-126 every comparison is false either way):
-//   code = [q>.625] + [q>=1] + [q>1.25] - [q>=1.75] + 2[q>=2] + [q>2.5] + [q>=3.5] + [q>5] - [q>=7]
-// (the two negative steps are the reference's lost mantissa carry at odd exponents,
-// minifloat/fake.py:70, and the first step its single subnormal binade, :56-60).  The sums are kept
-// in bf16 (128 + code, or the decoded value itself for the fused form), so the per-element work is
-// packed compare + add on the fp pipe instead of ~13 integer instructions.
+// The quotient q = |x| * 2^-se is exact in bf16 for a power-of-two factor (below 2^-126 it only has
+// to stay below 0.625), and q < 8 for a finite block.  Per word:
+//   * q >= 1: the 7-bit mantissa, tagged with exponent 0, plus 63.0 is 64 + (m - 1) rounded half to
+//     even to a multiple of 0.5, so the sum's bits are those of 64.0 plus fr in {0, 1, 2}; fr << 6
+//     OR-ed under q's own exponent field is the quantised quotient in bf16 (fr = 2 lands on the
+//     exponent's low bit: the reference's OR-merge, minifloat/fake.py:70, carry lost for odd fields);
+//     the code is that pattern shifted down, re-biased with one XOR;
+//   * q < 1: the single subnormal binade (:56-60) leaves code 1 (0.5) above 0.625 and zero below.
 // An element is kept (else it is +0) when it is not a flushed input and its fp32 quotient does not
 // round to zero: |x| > max(2^(se-150), largest subnormal), one packed comparison against a
 // per-block constant; the sign bit rides along with the kept ones.
+// This is ~8 integer-pipe instructions per element instead of ~13 for the generic codec.
 // ------------------------------------------------------------------------------------------------
 struct E2M1Block {
     uint32_t inv2;    // 2^-se in both halves
     uint32_t sf2;     // 2^se in both halves (fused form)
-    uint32_t ts2;     // sign threshold in both halves
+    uint32_t ts2;     // keep threshold in both halves
 };
 
 __device__ __forceinline__ E2M1Block e2m1_block(uint32_t h) {
@@ -170,24 +172,6 @@ __device__ __forceinline__ E2M1Block e2m1_block(uint32_t h) {
 __device__ __forceinline__ __nv_bfloat162 bf2(uint32_t w) { return *reinterpret_cast<__nv_bfloat162*>(&w); }
 __device__ __forceinline__ uint32_t bf2_bits(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
 
-// VALUES = false: 128 + magnitude code per half; true: decoded magnitude per half
-template <bool VALUES>
-__device__ __forceinline__ __nv_bfloat162 e2m1_staircase(__nv_bfloat162 q) {
-    const uint32_t unit = VALUES ? 0x3F003F00u : 0x3F803F80u;      // 0.5 or 1.0: one code step below 2.0
-    const __nv_bfloat162 u = bf2(unit), u2 = bf2(unit + 0x00800080u), u4 = bf2(unit + 0x01000100u);
-    __nv_bfloat162 acc = bf2(VALUES ? 0u : 0x43004300u);
-    acc = __hfma2(__hgt2(q, bf2(0x3F203F20u)), u, acc);            // > 0.625
-    acc = __hfma2(__hge2(q, bf2(0x3F803F80u)), u, acc);            // >= 1
-    acc = __hfma2(__hgt2(q, bf2(0x3FA03FA0u)), u, acc);            // > 1.25
-    acc = __hfma2(__hge2(q, bf2(0x3FE03FE0u)), __hneg2(u), acc);   // >= 1.75 (lost carry)
-    acc = __hfma2(__hge2(q, bf2(0x40004000u)), u2, acc);           // >= 2: code +2, value +1
-    acc = __hfma2(__hgt2(q, bf2(0x40204020u)), VALUES ? u2 : u, acc);   // > 2.5: code +1, value +1
-    acc = __hfma2(__hge2(q, bf2(0x40604060u)), VALUES ? u2 : u, acc);   // >= 3.5
-    acc = __hfma2(__hgt2(q, bf2(0x40A040A0u)), VALUES ? u4 : u, acc);   // > 5: code +1, value +2
-    acc = __hfma2(__hge2(q, bf2(0x40E040E0u)), __hneg2(VALUES ? u4 : u), acc);   // >= 7 (lost carry)
-    return acc;
-}
-
 // one 16-byte access of a lane (8 bf16 inputs) of a finite block -> 8 code bytes or 8 bf16 results
 template <bool VALUES>
 __device__ __forceinline__ void e2m1_bf16_quantise(const Pack<16>& p, const E2M1Block& b, uint32_t* out) {
@@ -197,15 +181,22 @@ __device__ __forceinline__ void e2m1_bf16_quantise(const Pack<16>& p, const E2M1
         const uint32_t w = p.w[i];
         const uint32_t aw = w & 0x7FFF7FFFu;
         const __nv_bfloat162 q = __hmul2(bf2(aw), bf2(b.inv2));
-        // halves that are flushed inputs or whose fp32 quotient rounds to zero give +0 (code 0)
+        const uint32_t qb = bf2_bits(q);
         const uint32_t keep = __hgt2_mask(bf2(aw), bf2(b.ts2));
-        const __nv_bfloat162 acc = e2m1_staircase<VALUES>(q);
+        // normal range: rounded mantissa field under q's exponent field
+        const uint32_t sum = bf2_bits(__hadd2(bf2((qb & 0x007F007Fu) | 0x3F803F80u), bf2(0x427C427Cu)));      // + 63.0
+        const uint32_t z = sum * (uint32_t)rt_k(9) - 0x42804280u * 64u;        // (sum - bits(64.0)) << 6 per half, as one multiply-add
+        const uint32_t y = (qb & 0x7F807F80u) | z;
+        const uint32_t lt1 = __hlt2_mask(q, bf2(0x3F803F80u));                  // q < 1
+        const uint32_t gt = __hgt2_mask(q, bf2(0x3F203F20u));                   // q > 0.625
         if constexpr (VALUES) {
-            const uint32_t y = bf2_bits(__hmul2(acc, bf2(b.sf2)));
-            r[i] = ((y & 0x7FFF7FFFu) | (w & 0x80008000u)) & keep;
+            const uint32_t v = (lt1 & gt & 0x3F003F00u) | (~lt1 & y);            // 0.5 / 0 below 1, else the quantised quotient
+            const uint32_t o = bf2_bits(__hmul2(bf2(v), bf2(b.sf2)));
+            r[i] = ((o & 0x7FFF7FFFu) | (w & 0x80008000u)) & keep;
         } else {
-            // 128 + code has bit 3 of each half clear: drop the sign bit of w there, then mask
-            r[i] = ((bf2_bits(acc) & ~0x00080008u) | ((w >> 12) & 0x00080008u)) & keep & 0x000F000Fu;
+            const uint32_t cn = ((y >> 6) ^ 0x00040004u) & 0x00070007u;          // (E << 1 | fr) - 252, modulo 8
+            const uint32_t c = (lt1 & gt & 0x00010001u) | (~lt1 & cn);
+            r[i] = (c | ((w >> 12) & 0x00080008u)) & keep;
         }
     }
     if constexpr (VALUES) {
