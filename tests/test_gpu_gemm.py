@@ -2,6 +2,7 @@
 
 from __future__ import annotations
 
+import numpy as np
 import pytest
 import torch
 
@@ -203,3 +204,26 @@ def test_minifloat_one_pass_pack_equals_two_step(lib, dtype):
             assert one.hw_format == two.hw_format
             assert torch.equal(one.codes, two.codes), f"{meta.tag} {dtype} {rows}x{K}: codes differ"
             assert torch.equal(one.sf, two.sf), f"{meta.tag} {dtype} {rows}x{K}: scale chunks differ"
+
+
+def test_gemm_random_shapes(lib):
+    """Ragged M and N, every K that is a multiple of 32 up to 640, all output dtypes and format pairs,
+    against an fp32 matmul of the dequantised operands."""
+    rng = np.random.default_rng(17)
+    metas = [MXFP8_E4M3_fn, MXFP8_E5M2_fn, OCP_MXFP6_E2M3, OCP_MXFP6_E3M2, OCP_MXFP4_E2M1]
+    for trial in range(24):
+        M = int(rng.integers(1, 700)); N = int(rng.integers(1, 900)); K = 32 * int(rng.integers(1, 21))
+        xm, wm = metas[trial % 5], metas[(trial // 5 + trial) % 5]
+        dtype = (torch.bfloat16, torch.float16, torch.float32)[trial % 3]
+        g = torch.Generator().manual_seed(trial)
+        x = (torch.randn((M, K), generator=g) * float(rng.uniform(0.1, 30))).to(DEV)
+        w = (torch.randn((N, K), generator=g) * float(rng.uniform(0.01, 3))).to(DEV)
+        bias = torch.randn((N,), generator=g).to(dtype).to(DEV) if trial % 2 else None
+        a, b = G.quantize_pack(x, xm), G.quantize_pack(w, wm, G.OPERAND_B)
+        y = G.mx_gemm(a, b, dtype, bias=bias)
+        G.check_status(DEV)
+        x_dq = MX.quantize_dequantize(x, -1, xm, torch.float32)
+        w_dq = MX.quantize_dequantize(w, -1, wm, torch.float32)
+        y32 = x_dq @ w_dq.t() + (bias.float() if bias is not None else 0)
+        assert y.shape == (M, N) and y.dtype == dtype
+        assert within_tolerance(y, y32), f"trial {trial}: M={M} N={N} K={K} {xm.tag} x {wm.tag} {dtype}"

@@ -297,6 +297,26 @@ def test_strided_blocks_match_oracle(lib, meta, dtype, shape, dim):
     assert_bits_equal(MX.quantize_dequantize(x.to(DEV), dim, meta).contiguous(), y_o, "fused (public)")
 
 
+def test_strided_blocks_random_shapes(lib):
+    """Random (outer, D, inner) splits, all dtypes and presets: the strided kernels against the
+    permute-then-flatten order of the oracle."""
+    rng = np.random.default_rng(23)
+    for trial in range(30):
+        outer, D, inner = int(rng.integers(1, 5)), 32 * int(rng.integers(1, 9)), int(rng.integers(2, 150))
+        meta = MX_PRESETS[trial % 5]
+        dtype = DTYPES[trial % 3]
+        shape = (outer, D, inner)
+        x = _strided_case(shape, 1, dtype, seed=100 + trial)
+        flat = x.movedim(1, -1).flatten()
+        s_o, e_o = oracle.extract_mxfp_components(flat, meta)
+        pair = mx_kernels.extract_mxfp_components_strided(x.to(DEV), 1, meta)
+        assert pair is not None
+        assert_bits_equal(pair[0], s_o, f"scales {shape}"); assert_bits_equal(pair[1], e_o, f"elements {shape}")
+        y_o = oracle.compose_mxfp_tensor(s_o, e_o, meta, dtype).reshape(outer, inner, D).movedim(-1, 1).contiguous()
+        assert_bits_equal(mx_kernels.compose_mxfp_tensor_strided(pair[0], pair[1], shape, 1, meta, dtype), y_o, f"composed {shape}")
+        assert_bits_equal(mx_kernels.quantize_dequantize_strided(x.to(DEV), 1, meta, dtype), y_o, f"fused {shape}")
+
+
 def test_strided_blocks_fall_back_when_not_covered(lib):
     """Blocks that span columns (D % 32 != 0), other block sizes and rounding modes take the
     permute + flat route and still match the oracle."""
