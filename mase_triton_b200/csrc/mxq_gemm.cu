@@ -71,6 +71,9 @@ struct OutSpec {
 #ifndef MXQ_FWD_WARPS
 #define MXQ_FWD_WARPS 4
 #endif
+#ifndef MXQ_FWD_UNROLL
+#define MXQ_FWD_UNROLL 4
+#endif
 constexpr int FWD_WARPS = MXQ_FWD_WARPS;         // copy-out warps of the gather-fused kernel
 constexpr int STORED_BAR_OFF = 128, ACK_BAR_OFF = 144;   // two barriers each (one per accumulator), inside the BAR_BYTES region past the pipeline barriers
 
@@ -221,7 +224,7 @@ __device__ __forceinline__ void forward_tile(const OutSpec& outs, int fw, int la
     const int upr = cols / EPU;                            // units per row segment (cols is a multiple of EPU)
     const int total = rows * upr;
     const uint8_t* src = reinterpret_cast<const uint8_t*>(outs.ptr[outs.self]);
-    constexpr int UNROLL = 4;
+    constexpr int UNROLL = MXQ_FWD_UNROLL;
     for (int base = fw * 32 + lane; base < total; base += FWD_WARPS * 32 * UNROLL) {
         uint4 v[UNROLL];
         size_t off[UNROLL];
