@@ -146,3 +146,30 @@ def test_minifloat_linear_ptq(lib, x_meta, w_meta, dtype):
             q._apply(lambda t: t.to(torch.float32))
     ym = MF.minifloat_matmul(x, fc.weight.t().contiguous(), x_meta, w_meta, ("Xq" if x_meta else "X") + ("Wq" if w_meta else "W"), "separate")
     assert torch.equal(ym, torch.matmul(x_dq, w_dq.t().contiguous()))
+
+
+@pytest.mark.parametrize("rows,chunk", [(1000, 256), (512, 512), (37, 64), (300, 4096)])
+def test_host_pipeline_matches_device_result(lib, rows, chunk):
+    """The chunked pinned-host -> device -> pinned-host front end gives the bytes of one device-resident
+    call, for row counts that are not a multiple of the chunk and for a single chunk."""
+    from mase_triton_b200.hostpath import HostPipeline
+    from mase_triton_b200.minifloat import kernels as mfk
+    from mase_triton_b200.mxfp import kernels as mxk
+    g = torch.Generator().manual_seed(rows)
+    x = (torch.randn((rows, 2048), generator=g) * torch.exp2(torch.randint(-20, 20, (rows, 1), generator=g).float())).pin_memory()
+    out = torch.empty_like(x).pin_memory()
+    dev = torch.device(DEV)
+    for op, direct in (
+        (lambda a, b: mfk.quantize_dequantize(a, FP8_E4M3_fn, torch.float32, out=b),
+         lambda t: mfk.quantize_dequantize(t, FP8_E4M3_fn, torch.float32)),
+        (lambda a, b: mxk.quantize_dequantize(a.reshape(-1), MXFP8_E4M3_fn, torch.float32, out=b.reshape(-1)),
+         lambda t: mxk.quantize_dequantize(t.reshape(-1), MXFP8_E4M3_fn, torch.float32).reshape(t.shape)),
+    ):
+        pipe = HostPipeline(op, dev, chunk_rows=chunk)
+        for _ in range(2):                       # the second pass re-uses the staging buffers
+            out.zero_()
+            pipe.run(x, out)
+            torch.cuda.synchronize()
+            want = direct(x.to(dev)).cpu()
+            assert torch.equal(out.view(torch.int32), want.view(torch.int32))
+        assert pipe.launches == 2 * ((rows + min(chunk, rows) - 1) // min(chunk, rows))
