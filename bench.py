@@ -55,6 +55,37 @@ def measured_peaks() -> tuple[float, str]:
     return 6650.0, "fallback"
 
 
+def measured_tensor_peak() -> float:
+    """Measured cuBLAS bf16 burst TFLOP/s of this pool's B200 (driver-written), else the fallback 1590."""
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["bf16_tflops"])
+        except Exception:
+            pass
+    return 1590.0
+
+
+def library_mx_gemm_bar(M: int, N: int, K: int, dev, reps: int, flops: float) -> dict:
+    """The library's own block-scaled MXFP8 GEMM (torch._scaled_mm with E8M0 scales on operands of the same
+    shape) timed the same way, as a bar for the hand-written kernel.  Comparison only: no product path calls it.
+    Unit scales and random codes: the time of a GEMM does not depend on the values."""
+    try:
+        e8 = getattr(torch, "float8_e8m0fnu")
+        a = torch.randint(0, 120, (M, K), device=dev, dtype=torch.uint8).view(torch.float8_e4m3fn)
+        b = torch.randint(0, 120, (N, K), device=dev, dtype=torch.uint8).view(torch.float8_e4m3fn)
+        ru = lambda v, m: (v + m - 1) // m * m      # noqa: E731
+        sa = torch.full((ru(M, 128) * ru(K // 32, 4),), 127, device=dev, dtype=torch.uint8).view(e8)
+        sb = torch.full((ru(N, 128) * ru(K // 32, 4),), 127, device=dev, dtype=torch.uint8).view(e8)
+        fn = lambda: torch._scaled_mm(a, b.t(), scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16)     # noqa: E731
+        fn()
+        torch.cuda.synchronize()
+        t = graph_time(fn, reps, rounds=9)
+        return {"TFLOPs": round(flops / t / 1e9, 1), "ms": round(t, 4), "what": "torch._scaled_mm, float8_e4m3fn x float8_e4m3fn, float8_e8m0fnu block-32 scales, bf16 out"}
+    except Exception as exc:      # noqa: BLE001 - a missing library kernel must not hide our own numbers
+        return {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+
+
 class ClockSampler:
     """Samples SM clock / throttle reasons of one GPU with NVML while a region runs."""
 
@@ -118,8 +149,10 @@ def dist_setup(n_gpus: int):
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")     # keep stdout for the one JSON line
+        import datetime
         torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # a rank that fails alone must not leave the others waiting in a collective for long
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(minutes=4))
         return dist, rank, world, local
     return None, 0, 1, 0
 
@@ -267,7 +300,12 @@ def extras_single_gpu(dev, steps: int, warmup: int, peak: float) -> dict:
     flops = 2.0 * M * N * K
     a, b = G.quantize_pack(xc, MXFP8_E4M3_fn), G.quantize_pack(wc, MXFP8_E4M3_fn, G.OPERAND_B)
     o = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
-    t_gemm = graph_time(lambda: G.mx_gemm(a, b, torch.bfloat16, out=o), reps)
+    gemm_clock = ClockSampler(dev.index or 0, period_s=0.002)
+    gemm_clock.start()
+    tg0 = time.perf_counter()
+    t_gemm = graph_time(lambda: G.mx_gemm(a, b, torch.bfloat16, out=o), max(reps, 20), rounds=9)
+    tg1 = time.perf_counter()
+    gemm_clock.stop()
     fc = torch.nn.Linear(K, N, bias=False, device=dev, dtype=torch.bfloat16)
     with torch.no_grad():
         fc.weight.copy_(wc)
@@ -277,36 +315,87 @@ def extras_single_gpu(dev, steps: int, warmup: int, peak: float) -> dict:
     t_sep = graph_time(lambda: sep(xc), max(3, reps // 2))
     G.check_status(dev)
     rel = ((fused(xc).float() - sep(xc).float()).abs().mean() / sep(xc).float().abs().mean()).item()
+    bf16_peak = measured_tensor_peak()
     out["cfg4_mxfp_linear_8192x14336x4096"] = {
         "gemm_kernel_TFLOPs": round(flops / t_gemm / 1e9, 1), "fused_linear_TFLOPs": round(flops / t_fused / 1e9, 1),
         "separate_linear_TFLOPs_reference_style_cublas_bf16": round(flops / t_sep / 1e9, 1),
         "gemm_frac_of_4500_nominal_mx": round(flops / t_gemm / 1e9 / 4500, 3),
         "ms": {"gemm": round(t_gemm, 4), "fused_linear": round(t_fused, 4), "separate_linear": round(t_sep, 4)},
         "mean_rel_diff_fused_vs_separate": round(rel, 8),
+        # roofline of the tensor-core kernel: 2*M*N*K flops per launch over its CUDA-graph-replay time
+        "roofline": {"bound": "tensor", "achieved": round(flops / t_gemm / 1e9, 1), "unit": "TFLOP/s", "peak": 4500.0,
+                     "frac": round(flops / t_gemm / 1e9 / 4500, 4), "peak_source": "nominal dense MXFP8 (no measured MX peak on file)",
+                     "peak_2x_measured_bf16_burst": round(2 * bf16_peak, 1), "frac_of_2x_measured_bf16_burst": round(flops / t_gemm / 1e9 / (2 * bf16_peak), 4),
+                     "kernel": "mx_gemm_kernel<bf16, MH=2>", "launch_ms": round(t_gemm, 5), "flops_per_launch": flops,
+                     "clocks_during_gemm": gemm_clock.summary(tg0, tg1)},
     }
-    del fc, fused, sep, a, b, o, xc, wc
+    out["cfg4_mxfp_linear_8192x14336x4096"]["library_bar_scaled_mm_mxfp8"] = library_mx_gemm_bar(M, N, K, dev, max(reps, 20), flops)
+    # the other layer types on the kind::f16 GEMM (weight codes expanded in the operand loader; dense operands)
+    from mase_triton_b200 import tc_linear
+    wq_f = MXFPLinearPTQ.from_linear(fc, None, MXFP8_E4M3_fn, None, "XWqB", "fused")
+    wq_s = MXFPLinearPTQ.from_linear(fc, None, MXFP8_E4M3_fn, None, "XWqB", "separate")
+    xq_f = MXFPLinearPTQ.from_linear(fc, MXFP8_E4M3_fn, None, None, "XqWB", "fused")
+    xq_s = MXFPLinearPTQ.from_linear(fc, MXFP8_E4M3_fn, None, None, "XqWB", "separate")
+    t = {"XWq_fused": graph_time(lambda: wq_f(xc), reps), "XWq_separate": graph_time(lambda: wq_s(xc), max(3, reps // 2)),
+         "XqW_fused": graph_time(lambda: xq_f(xc), reps), "XqW_separate": graph_time(lambda: xq_s(xc), max(3, reps // 2)),
+         "dense_gemm": graph_time(lambda: tc_linear.dense_linear(xc, wc), reps),
+         "library_dense_gemm": graph_time(lambda: torch.nn.functional.linear(xc, wc), reps)}
+    G.check_status(dev)
+    rel_wq = ((wq_f(xc).float() - wq_s(xc).float()).abs().mean() / wq_s(xc).float().abs().mean()).item()
+    out["cfg4_shape_mixed_layer_types_kind_f16_gemm"] = {
+        "TFLOPs": {k: round(flops / v / 1e9, 1) for k, v in t.items()}, "ms": {k: round(v, 4) for k, v in t.items()},
+        "mean_rel_diff_XWq_fused_vs_separate": round(rel_wq, 8),
+        "frac_of_measured_bf16_burst": {k: round(flops / v / 1e9 / bf16_peak, 3) for k, v in t.items()},
+        "note": "fused = this library's tcgen05 kind::f16 GEMM (256x256 tiles); separate = dequantise kernels + torch.nn.functional.linear"}
+    del fc, fused, sep, wq_f, wq_s, xq_f, xq_s, a, b, o, xc, wc
     torch.cuda.empty_cache()
 
-    # configuration 5: seven projections of one Llama-3-8B-shaped layer, W MXFP6 E3M2, x MXFP8 E4M3, 16x2048 tokens
+    # configuration 5: seven projections of one Llama-3-8B-shaped layer, W MXFP6 E3M2, x MXFP8 E4M3, 16x2048 tokens.
+    # "independent": every projection is one public forward call (activation quantised inside every call);
+    # "shared activation": q/k/v and gate/up quantise their common input once (pack_input + forward_packed).
     sweep, tot_flops, tot_ms = {}, 0.0, 0.0
+    layers, inputs = {}, {}
     for pname, n_out, n_in in synthetic.CFG5_PROJECTIONS:
         w = synthetic.cfg5_weight(pname).to(dev)
-        x5 = synthetic.cfg5_input(n_in).to(dev)
+        if n_in not in inputs:
+            inputs[n_in] = synthetic.cfg5_input(n_in).to(dev)
         fc = torch.nn.Linear(n_in, n_out, bias=False, device=dev, dtype=torch.bfloat16)
         with torch.no_grad():
             fc.weight.copy_(w)
-        layer = MXFPLinearPTQ.from_linear(fc, MXFP8_E4M3_fn, OCP_MXFP6_E3M2, None, "XqWqB", "fused")
+        layers[pname] = MXFPLinearPTQ.from_linear(fc, MXFP8_E4M3_fn, OCP_MXFP6_E3M2, None, "XqWqB", "fused")
+        del fc, w
+    for pname, n_out, n_in in synthetic.CFG5_PROJECTIONS:
+        x5, layer = inputs[n_in], layers[pname]
         t = graph_time(lambda: layer(x5), max(3, reps // 2))
         fl = 2.0 * x5.shape[0] * x5.shape[1] * n_in * n_out
         sweep[pname] = {"ms": round(t, 4), "TFLOPs": round(fl / t / 1e9, 1)}
         tot_flops += fl
         tot_ms += t
-        del fc, layer, w, x5
-        torch.cuda.empty_cache()
     G.check_status(dev)
     sweep["sweep_TFLOPs"] = round(tot_flops / tot_ms / 1e9, 1)
     sweep["sweep_ms"] = round(tot_ms, 4)
+    shared_ms = 0.0
+    groups = {}
+    for gname, members in (("qkv", ("q", "k", "v")), ("o", ("o",)), ("gate_up", ("gate", "up")), ("down", ("down",))):
+        x5 = inputs[layers[members[0]].in_features]
+        lead = tuple(x5.shape[:-1])
+
+        def run_group(ms=members, x5=x5, lead=lead):
+            packed = layers[ms[0]].pack_input(x5)
+            return [layers[m].forward_packed(packed, torch.bfloat16, lead_shape=lead) for m in ms]
+        t = graph_time(run_group, max(3, reps // 2))
+        for m, y in zip(members, run_group()):
+            assert torch.equal(y, layers[m](x5)), f"shared-activation result of {m} differs from forward()"
+        fl = sum(2.0 * x5.shape[0] * x5.shape[1] * layers[m].in_features * layers[m].out_features for m in members)
+        groups[gname] = {"ms": round(t, 4), "TFLOPs": round(fl / t / 1e9, 1)}
+        shared_ms += t
+    G.check_status(dev)
+    sweep["shared_activation"] = {"groups": groups, "sweep_TFLOPs": round(tot_flops / shared_ms / 1e9, 1), "sweep_ms": round(shared_ms, 4),
+                                  "frac_of_4500_nominal_mx": round(tot_flops / shared_ms / 1e9 / 4500, 3)}
+    sweep["frac_of_4500_nominal_mx"] = round(tot_flops / tot_ms / 1e9 / 4500, 3)
     out["cfg5_llama3_8b_layer_fused_linear"] = sweep
+    del layers, inputs
+    torch.cuda.empty_cache()
 
     # widening rows: blocks along a non-contiguous dimension, and the minifloat linear on the tensor cores
     from mase_triton_b200.minifloat.layers import MinifloatLinearPTQ
@@ -339,87 +428,152 @@ def extras_single_gpu(dev, steps: int, warmup: int, peak: float) -> dict:
 
 
 def extras_multi_gpu(dev, dist, rank: int, world: int, local: int, steps: int, peak: float) -> dict:
-    """Sharded runs of configurations 3 (rows) and 4 (output features) on `world` GPUs; every time is the
-    max over ranks of a CUDA-event measurement that starts after a barrier."""
+    """The sharded configurations on `world` GPUs: configuration 3 split by rows (no collective) and the linears
+    of configurations 4 and 5 column-parallel by output feature, the partial outputs gathered either by NCCL or
+    by the GEMM kernel itself (peer stores).  Before anything is timed every rank checks its sharded results
+    against the whole problem computed on its own GPU, bit for bit.  Times are device times, max over ranks,
+    taken after a barrier: CUDA-graph replay where no collective is involved, otherwise one event pair around
+    `n` back-to-back calls so that a short kernel is not a measurement of launch gaps."""
     from mase_triton_b200 import parallel, synthetic
     from mase_triton_b200.mxfp import gemm as G
     from mase_triton_b200.mxfp import kernels as mxk
-    from mase_triton_b200.mxfp.meta import MXFP8_E4M3_fn, OCP_MXFP4_E2M1
+    from mase_triton_b200.mxfp.layers import MXFPLinearPTQ
+    from mase_triton_b200.mxfp.meta import MXFP8_E4M3_fn, OCP_MXFP4_E2M1, OCP_MXFP6_E3M2
     out = {}
-    reps = max(4, min(steps, 20))
 
     def max_over_ranks(ms: float) -> float:
         t = torch.tensor([ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    def timed(fn) -> float:
-        for _ in range(3):
-            fn()
+    def sync_all():
         dist.barrier(device_ids=[local])
         torch.cuda.synchronize()
-        return max_over_ranks(statistics.median(time_steps(fn, reps)))
 
-    # configuration 3: rows split evenly, no collective
+    def timed_graph(fn, reps: int) -> float:
+        sync_all()
+        return max_over_ranks(graph_time(fn, reps))
+
+    def timed_many(fn, n: int) -> float:
+        for _ in range(3):
+            fn()
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return max_over_ranks(e0.elapsed_time(e1) / n)
+
+    def all_ranks_agree(flag: bool, what: str) -> None:
+        t = torch.tensor([0 if flag else 1], device=dev, dtype=torch.int32)
+        dist.all_reduce(t)
+        if int(t.item()) != 0:
+            raise RuntimeError(f"{what}: {int(t.item())} rank(s) disagree with the single-GPU result")
+
+    # ---- configuration 3: rows split evenly, no collective ----
     rows = 16384
     lo, hi = parallel.shard_bounds(rows, rank, world)
-    x = synthetic.cfg3_mxfp4_bf16(rows=slice(lo, hi)).to(dev).flatten()
-    n_total = rows * 8192
-    t_ext = timed(lambda: mxk.extract_mxfp_components(x, OCP_MXFP4_E2M1))
+    x_full = synthetic.cfg3_mxfp4_bf16().to(dev)
+    x = x_full[lo:hi].contiguous().flatten()
+    s_full, e_full = mxk.extract_mxfp_components(x_full.flatten(), OCP_MXFP4_E2M1)
     s, e = mxk.extract_mxfp_components(x, OCP_MXFP4_E2M1)
-    t_cmp = timed(lambda: mxk.compose_mxfp_tensor(s, e, OCP_MXFP4_E2M1, torch.bfloat16))
+    bpr = 8192 // 32
+    ok = torch.equal(s, s_full[lo * bpr:hi * bpr]) and torch.equal(e, e_full[lo * bpr:hi * bpr])
+    y_full = mxk.compose_mxfp_tensor(s_full, e_full, OCP_MXFP4_E2M1, torch.bfloat16)
+    ok = ok and torch.equal(mxk.compose_mxfp_tensor(s, e, OCP_MXFP4_E2M1, torch.bfloat16).view(torch.int16), y_full[lo * 8192:hi * 8192].view(torch.int16))
+    ok = ok and torch.equal(mxk.quantize_dequantize(x, OCP_MXFP4_E2M1, torch.bfloat16).view(torch.int16), y_full[lo * 8192:hi * 8192].view(torch.int16))
+    all_ranks_agree(ok, "configuration 3 row shard")
+    del x_full, s_full, e_full, y_full
+    torch.cuda.empty_cache()
+    n_total = rows * 8192
+    reps = 40
+    t_ext = timed_graph(lambda: mxk.extract_mxfp_components(x, OCP_MXFP4_E2M1), reps)
+    t_cmp = timed_graph(lambda: mxk.compose_mxfp_tensor(s, e, OCP_MXFP4_E2M1, torch.bfloat16), reps)
+    t_qdq = timed_graph(lambda: mxk.quantize_dequantize(x, OCP_MXFP4_E2M1, torch.bfloat16), reps)
     b = n_total * (2 + 1 + 1 / 32)
     out["cfg3_rows_sharded"] = {"extract_GBps_total": round(b / t_ext / 1e6, 1), "compose_GBps_total": round(b / t_cmp / 1e6, 1),
                                 "extract_plus_compose_GBps_total": round(2 * b / (t_ext + t_cmp) / 1e6, 1),
-                                "frac_of_peak_per_gpu": round(2 * b / (t_ext + t_cmp) / 1e6 / peak / world, 3),
-                                "rows_per_gpu": hi - lo, "collective": "none"}
+                                "fused_qdq_GBps_total": round(n_total * 4 / t_qdq / 1e6, 1),
+                                "frac_of_peak_per_gpu": {"extract": round(b / t_ext / 1e6 / peak / world, 3), "compose": round(b / t_cmp / 1e6 / peak / world, 3),
+                                                         "extract_plus_compose": round(2 * b / (t_ext + t_cmp) / 1e6 / peak / world, 3),
+                                                         "fused_qdq": round(n_total * 4 / t_qdq / 1e6 / peak / world, 3)},
+                                "ms": {"extract": round(t_ext, 5), "compose": round(t_cmp, 5), "fused_qdq": round(t_qdq, 5)},
+                                "rows_per_gpu": hi - lo, "collective": "none", "scaling": "strong (16384 rows in total)",
+                                "timing": f"CUDA graph replay of {reps} launches, max over ranks", "verified": "shard results equal the slices of the whole-tensor results on every rank"}
     del x, s, e
     torch.cuda.empty_cache()
 
-    # configuration 4: weight split by output feature, activation replicated, outputs all-gathered over NCCL
-    xc, wc = synthetic.cfg4_linear_operands()
-    n0, n1 = parallel.shard_bounds(wc.shape[0], rank, world)
-    xc, wl = xc.to(dev), wc[n0:n1].contiguous().to(dev)
-    M, K, N = xc.shape[0], xc.shape[1], wc.shape[0]
-    a, bq = G.quantize_pack(xc, MXFP8_E4M3_fn), G.quantize_pack(wl, MXFP8_E4M3_fn, G.OPERAND_B)
-    sizes = [q - p for p, q in (parallel.shard_bounds(N, r, world) for r in range(world))]
-    o = torch.empty((M, n1 - n0), dtype=torch.bfloat16, device=dev)
-    t_gemm = timed(lambda: G.mx_gemm(a, bq, torch.bfloat16, out=o))
-    t_all = timed(lambda: parallel.gather_columns(G.mx_gemm(a, bq, torch.bfloat16, out=o), sizes))
-    G.check_status(dev)
-    fl = 2.0 * M * N * K
-    out["cfg4_column_parallel"] = {"gemm_only_TFLOPs_total": round(fl / t_gemm / 1e9, 1), "gemm_plus_allgather_TFLOPs_total": round(fl / t_all / 1e9, 1),
-                                   "ms": {"gemm": round(t_gemm, 4), "gemm_plus_allgather": round(t_all, 4)},
-                                   "out_features_per_gpu": n1 - n0, "collective": "nccl all_gather of bf16 [M, N/g] shards"}
-    # the same with the gather done by the GEMM epilogue (peer stores over NVLink) plus a one-element all-reduce as fence
-    try:
-        import torch.distributed._symmetric_memory as symm_mem
-        bufs, ptrs, handles = [], [], []
-        for _ in range(2):
-            t = symm_mem.empty((M, N), dtype=torch.bfloat16, device=dev)
-            h = symm_mem.rendezvous(t, dist.group.WORLD)
-            bufs.append(t); handles.append(h); ptrs.append([int(p) for p in h.buffer_ptrs])
-        fence = torch.zeros(1, device=dev)
-        turn = [0]
-
-        def fused():
-            G.mx_gemm_gather(a, bq, ptrs[turn[0]], rank, N, n0, torch.bfloat16)
-            dist.all_reduce(fence)
-            turn[0] ^= 1
-
-        t_fused = timed(fused)
-        t_stores = timed(lambda: G.mx_gemm_gather(a, bq, ptrs[0], rank, N, n0, torch.bfloat16))
+    # ---- column-parallel linears: configuration 4 and the seven projections of configuration 5 ----
+    def column_parallel(name: str, x: torch.Tensor, w: torch.Tensor, x_meta, w_meta, n_calls: int) -> dict:
+        n_out, n_in = w.shape
+        fc = torch.nn.Linear(n_in, n_out, bias=False, device=dev, dtype=torch.bfloat16)
+        with torch.no_grad():
+            fc.weight.copy_(w.to(dev))
+        layer = MXFPLinearPTQ.from_linear(fc, x_meta, w_meta, None, "XqWqB", "fused")
+        del fc
+        xg = x.to(dev)
+        rows_x = xg.numel() // n_in
+        want = layer(xg).reshape(rows_x, n_out)                       # the whole layer on this GPU
+        via_nccl = parallel.column_parallel_mxfp_linear(layer)
+        fused = parallel.GatherFusedMXFPLinear(layer, max_rows=rows_x, dtype=torch.bfloat16)
+        got_nccl = via_nccl(xg).reshape(rows_x, n_out).contiguous()
+        got_fused = fused(xg).reshape(rows_x, n_out)
         G.check_status(dev)
-        # bytes each GPU sends to its peers per call / time of the kernel that sends them
-        egress = M * (n1 - n0) * 2 * (world - 1)
-        out["cfg4_column_parallel"].update({
-            "gemm_fused_gather_TFLOPs_total": round(fl / t_fused / 1e9, 1),
-            "fused_kernel_only_TFLOPs_total": round(fl / t_stores / 1e9, 1),
-            "fused_kernel_nvlink_egress_GBps_per_gpu": round(egress / t_stores / 1e6, 1),
-            "fused_gather": "the GEMM kernel copies each finished tile into every rank's [M, N] output (symmetric memory, peer stores), then a 1-element all-reduce"})
-        out["cfg4_column_parallel"]["ms"].update({"gemm_fused_gather": round(t_fused, 4), "fused_kernel_only": round(t_stores, 4)})
-    except Exception as exc:   # noqa: BLE001 - reported, the NCCL numbers above stand
-        out["cfg4_column_parallel"]["fused_gather_error"] = f"{type(exc).__name__}: {exc}"[:300]
+        torch.cuda.synchronize()
+        ok_n = torch.equal(got_nccl.view(torch.int16), want.view(torch.int16))
+        ok_f = torch.equal(got_fused.view(torch.int16), want.view(torch.int16))
+        all_ranks_agree(ok_n, f"{name}: NCCL-gathered output")
+        all_ranks_agree(ok_f, f"{name}: gather-fused output")
+        del want, got_nccl, got_fused
+        fl = 2.0 * rows_x * n_in * n_out
+        n0, n1 = fused.n0, fused.n1
+        a = G.pack_activation(xg.reshape(rows_x, n_in), x_meta)
+        o = torch.empty((rows_x, max(1, n1 - n0)), dtype=torch.bfloat16, device=dev)
+        t_gemm = timed_many(lambda: G.mx_gemm(a, fused.weight, torch.bfloat16, out=o), n_calls) if n1 > n0 else 0.0
+        t_kernel = timed_many(lambda: G.mx_gemm_gather(a, fused.weight, fused.ptrs[0], rank, n_out, n0, torch.bfloat16), n_calls)
+        t_local = timed_many(lambda: via_nccl(xg, gather=False), n_calls)
+        t_nccl = timed_many(lambda: via_nccl(xg), n_calls)
+        t_fused = timed_many(lambda: fused(xg), n_calls)
+        G.check_status(dev)
+        egress = rows_x * (n1 - n0) * 2 * (world - 1)
+        link_ms = egress / 770e9 * 1e3
+        res = {"out_features_per_gpu": n1 - n0, "tile_columns": fused.weight.tile_rows or 224,
+               "TFLOPs_total": {"gemm_only": round(fl / t_gemm / 1e9, 1) if t_gemm else None, "layer_without_gather": round(fl / t_local / 1e9, 1),
+                                "layer_nccl_allgather": round(fl / t_nccl / 1e9, 1), "layer_gather_fused": round(fl / t_fused / 1e9, 1)},
+               "ms": {"gemm_only": round(t_gemm, 4), "gather_fused_kernel_only": round(t_kernel, 4), "layer_without_gather": round(t_local, 4),
+                      "layer_nccl_allgather": round(t_nccl, 4), "layer_gather_fused": round(t_fused, 4)},
+               "fused_kernel_nvlink_egress_GBps_per_gpu": round(egress / t_kernel / 1e6, 1),
+               "fused_kernel_frac_of_roofline": round(max(t_gemm, link_ms) / t_kernel, 3),
+               "roofline_ms": {"gemm": round(t_gemm, 4), "link_at_770_GBps": round(link_ms, 4)},
+               "verified": "NCCL-gathered and gather-fused outputs equal the single-GPU layer bit for bit on every rank",
+               "timing": f"one event pair around {n_calls} back-to-back calls, max over ranks"}
+        del layer, via_nccl, fused, a, o, xg
+        torch.cuda.empty_cache()
+        return res, fl, {"gemm_only": t_gemm, "layer_without_gather": t_local, "layer_nccl_allgather": t_nccl, "layer_gather_fused": t_fused}
+
+    try:
+        xc, wc = synthetic.cfg4_linear_operands()
+        res, _, _ = column_parallel("cfg4", xc, wc, MXFP8_E4M3_fn, MXFP8_E4M3_fn, 50)
+        res["collective"] = "all-gather of bf16 [M, N/g] shards: NCCL, or peer stores issued by the GEMM kernel + a one-element all-reduce as fence"
+        out["cfg4_column_parallel"] = res
+        del xc, wc
+        sweep, tot_fl, tot = {}, 0.0, {}
+        inputs = {}
+        for pname, n_out, n_in in synthetic.CFG5_PROJECTIONS:
+            if n_in not in inputs:
+                inputs = {n_in: synthetic.cfg5_input(n_in)}            # one input alive at a time (the widest is 0.9 GB)
+            res, fl, ts = column_parallel(f"cfg5 {pname}", inputs[n_in], synthetic.cfg5_weight(pname), MXFP8_E4M3_fn, OCP_MXFP6_E3M2, 20)
+            sweep[pname] = res
+            tot_fl += fl
+            for k, v in ts.items():
+                tot[k] = tot.get(k, 0.0) + v
+        sweep["sweep_TFLOPs_total"] = {k: round(tot_fl / v / 1e9, 1) for k, v in tot.items() if v}
+        sweep["sweep_ms"] = {k: round(v, 4) for k, v in tot.items()}
+        out["cfg5_column_parallel"] = sweep
+    except Exception as exc:   # noqa: BLE001 - reported in the line; the headline stands
+        out["column_parallel_error"] = f"{type(exc).__name__}: {exc}"[:400]
     return out
 
 
@@ -465,9 +619,15 @@ def small_cases():
             outs = [torch.empty((M, N), dtype=torch.bfloat16, device=dev) for _ in range(2)]
             ptrs = [o.data_ptr() for o in outs]
             return (lambda: G.mx_gemm_gather(a, b, ptrs, 0, N, 0, torch.bfloat16)), flops
+        if which == "dense":            # the kind::f16 GEMM on two dense bf16 operands
+            from mase_triton_b200 import tc_linear
+            return (lambda: tc_linear.dense_linear(x, w)), flops
         fc = torch.nn.Linear(K, N, bias=False, device=dev, dtype=torch.bfloat16)
         with torch.no_grad():
             fc.weight.copy_(w)
+        if which == "xwq":              # weight-only quantisation: codes expanded in the GEMM's operand loader
+            layer = MXFPLinearPTQ.from_linear(fc, None, MXFP8_E4M3_fn, None, "XWqB", "fused")
+            return (lambda: layer(x)), flops
         layer = MXFPLinearPTQ.from_linear(fc, MXFP8_E4M3_fn, MXFP8_E4M3_fn, None, "XqWqB", "fused" if which == "linear" else "separate")
         return (lambda: layer(x)), flops
 
@@ -505,7 +665,7 @@ def small_cases():
             cases[f"mxfp8_{which}_dim0_{route}_f32"] = (lambda w=which, r=route: strided_case(synthetic.cfg1_mxfp8_fp32, MXFP8_E4M3_fn, 4, w, r))
             cases[f"mxfp4_{which}_dim0_{route}_bf16"] = (lambda w=which, r=route: strided_case(synthetic.cfg3_mxfp4_bf16, OCP_MXFP4_E2M1, 2, w, r))
     cases["mx_gemm_gather_local_cfg4"] = (lambda: gemm_case(8192, 14336, 4096, "gather_local"))
-    for which in ("gemm", "linear", "separate"):
+    for which in ("gemm", "linear", "separate", "xwq", "dense"):
         cases[f"mx_{which}_small"] = (lambda w=which: gemm_case(2048, 4096, 4096, w))
         cases[f"mx_{which}_cfg4"] = (lambda w=which: gemm_case(8192, 14336, 4096, w))
     for which in ("extract", "compose", "qdq"):
@@ -526,7 +686,7 @@ def run_case(name: str, steps: int, warmup: int) -> None:
     ts = time_steps(fn, steps)
     t = statistics.median(ts)
     peak, kind = measured_peaks()
-    if name.startswith("mx_gemm") or name.startswith("mx_linear") or name.startswith("mx_separate") or name.startswith("mx_minifloat"):
+    if name.startswith(("mx_gemm", "mx_linear", "mx_separate", "mx_minifloat", "mx_xwq", "mx_dense")):
         print(json.dumps({"case": name, "steps": steps, "median_ms": round(t, 5), "TFLOPs": round(nbytes / t / 1e9, 1),
                           "frac_of_4500_nominal_mx": round(nbytes / t / 1e9 / 4500, 4)}), flush=True)
         return
@@ -540,9 +700,9 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-extras", action="store_true", help="skip the configuration 1 / 3 side measurements")
-    ap.add_argument("--multi-extras", action="store_true",
-                    help="with more than one GPU, also run the sharded configuration 3 / 4 measurements (uses NCCL all-gather)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the side measurements (one GPU: configurations 1, 3, 4, 5; several GPUs: the sharded "
+                         "configuration 3 and the column-parallel linears of configurations 4 and 5)")
     ap.add_argument("--case", default=None, help="run one small single-kernel case (for profiling) and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -588,7 +748,6 @@ def main() -> None:
     t0 = time.perf_counter()
     per_step = time_steps(step, args.steps)
     barrier()
-    t1 = time.perf_counter()
     total_ms = sum(per_step)
     if dist is not None:
         t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
@@ -598,27 +757,43 @@ def main() -> None:
     value = world * n * BYTES_PER_ELT / (ms_per_step * 1e-3) / 1e9
     kern_ms = statistics.mean(per_step)
     achieved = n * BYTES_PER_ELT / (kern_ms * 1e-3) / 1e9
+    # K steps of 85 us are over before a clock sampler sees them: keep the same kernel running, in batches of the
+    # same size, until half a second has gone by, so that the clock record covers the kernel the line reports on
+    sustained = list(per_step)
+    while time.perf_counter() - t0 < 0.5:
+        sustained += time_steps(step, max(args.steps, 50))
+    t1 = time.perf_counter()
+    sustained_ms = statistics.median(sustained)
 
     # end to end: pinned host input -> device -> kernel -> pinned host output, every step
     out_host = torch.empty_like(x_host).pin_memory()
     pipe = HostPipeline(lambda a, b: mfk.quantize_dequantize(a, FP8_E5M2_fn, torch.float32, out=b), dev, chunk_rows=512)
+    copy_only = HostPipeline(lambda a, b: None, dev, chunk_rows=512)       # the same chunked copies with no kernel: what the host link allows
     e2e_steps = max(3, min(args.steps, 10))
-    pipe.run(x_host, out_host)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed_pipe(p) -> float:
+        p.run(x_host, out_host)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(e2e_steps):
+            p.run(x_host, out_host)
+        e1.record()
+        barrier()
+        return e0.elapsed_time(e1)
+
+    copy_ms_local = timed_pipe(copy_only)
     launches_before = pipe.launches
-    e0.record()
-    for _ in range(e2e_steps):
-        pipe.run(x_host, out_host)
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1)
+    e2e_ms_local = timed_pipe(pipe)
     e2e_launches = pipe.launches - launches_before
+    e2e_ms, copy_ms, e2e_spread = e2e_ms_local, copy_ms_local, None
     if dist is not None:
-        t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+        t = torch.tensor([e2e_ms_local, copy_ms_local, -e2e_ms_local], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+        e2e_ms, copy_ms = float(t[0].item()), float(t[1].item())
+        e2e_spread = {"fastest_rank_ms_per_step": round(-float(t[2].item()) / e2e_steps, 3), "slowest_rank_ms_per_step": round(e2e_ms / e2e_steps, 3)}
     e2e_value = world * n * BYTES_PER_ELT / (e2e_ms / e2e_steps * 1e-3) / 1e9
+    copy_value = world * n * BYTES_PER_ELT / (copy_ms / e2e_steps * 1e-3) / 1e9
     sampler.stop()
     clocks = sampler.summary(t0, t1)
     # the e2e result must equal the device-resident one
@@ -636,10 +811,18 @@ def main() -> None:
                          "traffic_source": "ncu dram__bytes_read+write on the 4096x8192 case scaled by elements "
                                            "(profiles/minifloat_qdq_f32_small_case_full.md); writes still in L2 at kernel end are not counted",
                          "peak_source": f"{peak_kind} HBM copy bandwidth",
-                         "kernel": "ew_vec_kernel<4,4,4,4,QdqOp<f32,f32,E5M2>>", "launch_ms": round(kern_ms, 5)},
+                         "kernel": "ew_vec_kernel<4,4,4,4,QdqOp<f32,f32,E5M2>>", "launch_ms": round(kern_ms, 5),
+                         "sustained": {"steps": len(sustained), "median_launch_ms": round(sustained_ms, 5),
+                                       "achieved": round(n * BYTES_PER_ELT / (sustained_ms * 1e-3) / 1e9, 1),
+                                       "frac": round(n * BYTES_PER_ELT / (sustained_ms * 1e-3) / 1e9 / peak, 4),
+                                       "what": "the same launch repeated until 0.5 s had passed, so that the clock record covers it"}},
             "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": n * 4, "d2h_bytes_per_step": n * 4,
                     "steps": e2e_steps, "ms_per_step": round(e2e_ms / e2e_steps, 3), "matches_device_result": e2e_ok,
-                    "path": "HostPipeline: pinned host -> 512-row chunks over 3 streams -> pinned host"},
+                    "path": "HostPipeline: pinned host -> 512-row chunks over 3 streams -> pinned host",
+                    # the same chunked host->device and device->host copies with no kernel in between: the ceiling the
+                    # host link (PCIe, shared by the ranks of one box) sets for this number
+                    "copy_ceiling": round(copy_value, 2), "frac": round(e2e_value / copy_value, 4),
+                    "copy_ceiling_ms_per_step": round(copy_ms / e2e_steps, 3), "rank_spread": e2e_spread},
             "gpu_launches": args.steps, "e2e_gpu_launches": e2e_launches,
             "clocks": clocks,
         }
@@ -656,7 +839,7 @@ def main() -> None:
             except Exception as exc:
                 line["extras"] = {"error": str(exc)}
     extras_multi = None
-    if dist is not None and args.multi_extras:
+    if dist is not None and not args.no_extras:
         del x, out
         torch.cuda.empty_cache()
         try:

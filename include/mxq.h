@@ -130,10 +130,20 @@ int mxq_mxfp_qdq_strided(const void* x, int x_dtype, void* out, int out_dtype, i
 
 /* operand roles of the GEMM: the scale-factor array is tiled to the CTA tile of its side */
 #define MXQ_OPERAND_A 0 /* left operand  [M, K]: 256-row scale tiles */
-#define MXQ_OPERAND_B 1 /* right operand [N, K]: 224-row scale tiles */
+#define MXQ_OPERAND_B 1 /* right operand [N, K]: scale tiles of `tile_rows` rows = the CTA tile width */
+
+/*
+ * The right operand is packed for one CTA tile width (`tile_rows`: 0 = the default 224, else a
+ * multiple of 16 in [16, 224]) and the same value is handed to the GEMM as `b_tile_rows`.  224 gives
+ * the highest arithmetic intensity; a narrower tile pays when N is not close to a multiple of 224
+ * (N = 1024: five tiles of 208 instead of five of 224) or when whole 128-byte lines per row segment
+ * matter (192 for the gather-fused kernel).  mxq_mx_best_tile_rows(N) returns the width with the
+ * least padded work.  The left operand ignores `tile_rows` (pass 0).
+ */
+int mxq_mx_best_tile_rows(int64_t N);
 
 /* Bytes of the hardware scale-factor array of an operand with `rows` rows and K columns. */
-int64_t mxq_mx_sf_bytes(int64_t rows, int64_t K, int operand);
+int64_t mxq_mx_sf_bytes(int64_t rows, int64_t K, int operand, int tile_rows);
 
 /*
  * Re-encode an MXFP operand (reference scales [rows*K/32] and elements [rows*K], 32-element blocks
@@ -150,8 +160,8 @@ int64_t mxq_mx_sf_bytes(int64_t rows, int64_t K, int operand);
  * raised by one and its elements halved.
  */
 int mxq_mx_pack_operand(const uint8_t* scales, const uint8_t* elements, int64_t rows, int64_t K,
-                        int exp_bits, int frac_bits, int operand, uint8_t* hw_codes, uint8_t* hw_sf,
-                        int* hw_format, void* stream);
+                        int exp_bits, int frac_bits, int operand, int tile_rows, uint8_t* hw_codes,
+                        uint8_t* hw_sf, int* hw_format, void* stream);
 
 /*
  * One-pass alternative to mxq_mxfp_extract + mxq_mx_pack_operand for the LEFT operand: quantise
@@ -174,14 +184,55 @@ int mxq_minifloat_quantize_pack(const void* x, int x_dtype, int64_t M, int64_t K
 
 /*
  * out[M,N] = A[M,K] * B[N,K]^T (+ bias[N]) on operands packed as MXQ_OPERAND_A / MXQ_OPERAND_B,
- * fp32 accumulation in tensor memory.
+ * fp32 accumulation in tensor memory.  `b_tile_rows` is the value B was packed with.
  * out_dtype / bias dtype: MXQ_F32, MXQ_BF16 or MXQ_F16 (bias may be NULL). K % 32 == 0.
- * `status` (device int32, may be NULL, must be zero on entry) receives a non-zero code if a
- * bounded wait inside the kernel ran out; the output is then undefined.
+ * `status` (an int32 the GPU can write: device memory, or pinned host memory mapped into the device so
+ * that the host can poll it without synchronising; may be NULL; must be zero on entry) receives a
+ * non-zero code if a bounded wait inside the kernel ran out: 1 operand copies, 2 MMA issue,
+ * 3 epilogue, 4 copy-out to peers.  The kernel then unwinds (waits, bounded, for its own copies and
+ * MMAs in flight, frees its tensor memory) and returns; the output is undefined.
  */
 int mxq_mx_gemm(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw_format, const uint8_t* b_codes,
-                const uint8_t* b_sf, int b_hw_format, void* out, int out_dtype, const void* bias,
-                int64_t M, int64_t N, int64_t K, int* status, void* stream);
+                const uint8_t* b_sf, int b_hw_format, int b_tile_rows, void* out, int out_dtype,
+                const void* bias, int64_t M, int64_t N, int64_t K, int* status, void* stream);
+
+/*
+ * ---- Tensor-core GEMMs for the layer types whose operands are not both block-quantised ----
+ * out[M,N] = x[M,K] * W[N,K]^T (+ bias[N]); x, out and bias are bf16 or fp16 (`dtype`: MXQ_BF16 /
+ * MXQ_F16; MXQ_F32 returns MXQ_ESIZE), fp32 accumulation in tensor memory (tcgen05.mma.kind::f16,
+ * 256 x 256 tiles, x by TMA).  `status` as for mxq_mx_gemm (code 5: a dequantiser wait ran out).
+ * They replace "compose the weight to a dense tensor, then torch.nn.functional.linear" in
+ * mxfp_linear_XWq / _XqW / _XW (src/mase_triton/mxfp/functional/linear.py:10-33,67-116),
+ * minifloat_linear_XWq / _XqW / _XW (src/mase_triton/minifloat/functional/linear.py:10-105) and the
+ * matmul forms (mxfp/functional/matmul.py:10-35, minifloat/functional/matmul.py:10-35); an activation
+ * that the layer type quantises is fake-quantised first by mxq_mxfp_qdq / mxq_minifloat_qdq.
+ */
+
+/* W is a dense [N, K] matrix of the same dtype as x (brought in by TMA). K % 8 == 0. */
+int mxq_dense_linear(const void* x, const void* w, int dtype, void* out, const void* bias, int64_t M,
+                     int64_t N, int64_t K, int* status, void* stream);
+
+/*
+ * W stays quantised in memory, in the reference's own layout: w_elements [N*K] code bytes and
+ * w_scales [N*K/32] E8M0 bytes of 32-element blocks along K (what mxq_mxfp_extract writes for a
+ * [N, K] weight; the Parameters of MXFPLinearPTQ, src/mase_triton/mxfp/layers.py:66-80).  Eight
+ * warps of each CTA expand the codes to `dtype` inside the operand loader, with the rounding of
+ * compose_mxfp_tensor(..., output_dtype=dtype) (src/mase_triton/mxfp/fake.py:62-79); the dense weight
+ * is never written to memory.  Element format: is_finite, exp_bits + frac_bits <= 7.  K % 32 == 0.
+ */
+int mxq_mxfp_weight_linear(const void* x, int dtype, const uint8_t* w_scales, const uint8_t* w_elements,
+                           int exp_bits, int frac_bits, void* out, const void* bias, int64_t M,
+                           int64_t N, int64_t K, int* status, void* stream);
+
+/*
+ * The same with a per-tensor minifloat weight: w_codes [N*K] uint16 codes as written by
+ * mxq_minifloat_extract (Parameter `w_element` of MinifloatLinearPTQ), decoded like
+ * compose_minifloat_component(..., output_dtype=dtype) (src/mase_triton/minifloat/fake.py:81-125).
+ * exp_bits <= 8 (else MXQ_ESIZE).  K % 8 == 0.
+ */
+int mxq_minifloat_weight_linear(const void* x, int dtype, const uint16_t* w_codes, int exp_bits,
+                                int frac_bits, int is_finite, void* out, const void* bias, int64_t M,
+                                int64_t N, int64_t K, int* status, void* stream);
 
 /*
  * mxq_mx_gemm that also performs the all-gather of a column-parallel linear (no counterpart in the
@@ -197,7 +248,7 @@ int mxq_mx_gemm(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw_format, co
  * N, ld_out and col_offset must be multiples of 8 elements (4 for MXQ_F32), else MXQ_ESIZE.
  */
 int mxq_mx_gemm_gather(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw_format, const uint8_t* b_codes,
-                       const uint8_t* b_sf, int b_hw_format, void* const* outs, int n_outs, int self_index,
+                       const uint8_t* b_sf, int b_hw_format, int b_tile_rows, void* const* outs, int n_outs, int self_index,
                        int64_t ld_out, int64_t col_offset, int out_dtype, const void* bias, int64_t M,
                        int64_t N, int64_t K, int* status, void* stream);
 
@@ -211,9 +262,9 @@ int mxq_mx_gemm_gather(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw_for
  */
 int64_t mxq_mx_linear_scratch_bytes(int64_t M, int64_t K);
 int mxq_mx_linear(const void* x, int x_dtype, int64_t M, int64_t K, int x_exp_bits, int x_frac_bits,
-                  const uint8_t* w_codes, const uint8_t* w_sf, int w_hw_format, int64_t N, void* out,
-                  int out_dtype, const void* bias, void* scratch, int64_t scratch_bytes, int* status,
-                  void* stream);
+                  const uint8_t* w_codes, const uint8_t* w_sf, int w_hw_format, int w_tile_rows, int64_t N,
+                  void* out, int out_dtype, const void* bias, void* scratch, int64_t scratch_bytes,
+                  int* status, void* stream);
 
 /*
  * mxq_mx_linear for callers that cannot allocate device memory (no counterpart in the reference,
@@ -233,8 +284,8 @@ int mxq_mx_linear(const void* x, int x_dtype, int64_t M, int64_t K, int x_exp_bi
  */
 int64_t mxq_mx_linear_static_capacity(void);
 int mxq_mx_linear_static(const void* x, int x_dtype, int64_t M, int64_t K, int x_exp_bits, int x_frac_bits,
-                         const uint8_t* w_codes, const uint8_t* w_sf, int w_hw_format, int64_t N,
-                         void* out, int out_dtype, const void* bias, int* status, void* stream);
+                         const uint8_t* w_codes, const uint8_t* w_sf, int w_hw_format, int w_tile_rows,
+                         int64_t N, void* out, int out_dtype, const void* bias, int* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -11,10 +11,7 @@ from pathlib import Path
 
 import torch
 
-import os
-
-# MXQ_LIB overrides the in-tree build (for comparing two builds of the library)
-LIB_PATH = Path(os.environ.get("MXQ_LIB") or (Path(__file__).resolve().parent / "csrc" / "libmxq.so"))
+LIB_PATH = Path(__file__).resolve().parent / "csrc" / "libmxq.so"
 
 DTYPE_ID = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 ROUND_ID = {"rn": 0, "ru": 1, "rd": 2, "rz": 3}
@@ -31,16 +28,20 @@ SIGNATURES = {
     "mxq_mxfp_extract_strided": [_p, _i, _p, _p, _i64, _i64, _i64, _i, _i, _i, _i, _i, _p],
     "mxq_mxfp_compose_strided": [_p, _p, _p, _i, _i64, _i64, _i64, _i, _i, _i, _i, _p],
     "mxq_mxfp_qdq_strided": [_p, _i, _p, _i, _i64, _i64, _i64, _i, _i, _i, _i, _i, _p],
-    "mxq_mx_pack_operand": [_p, _p, _i64, _i64, _i, _i, _i, _p, _p, _p, _p],
+    "mxq_mx_pack_operand": [_p, _p, _i64, _i64, _i, _i, _i, _i, _p, _p, _p, _p],
+    "mxq_mx_best_tile_rows": [_i64],
     "mxq_mx_quantize_pack": [_p, _i, _i64, _i64, _i, _i, _p, _p, _p, _p],
     "mxq_minifloat_quantize_pack": [_p, _i, _i64, _i64, _i, _i, _i, _p, _p, _p, _p],
-    "mxq_mx_gemm": [_p, _p, _i, _p, _p, _i, _p, _i, _p, _i64, _i64, _i64, _p, _p],
-    "mxq_mx_gemm_gather": [_p, _p, _i, _p, _p, _i, _p, _i, _i, _i64, _i64, _i, _p, _i64, _i64, _i64, _p, _p],
-    "mxq_mx_linear": [_p, _i, _i64, _i64, _i, _i, _p, _p, _i, _i64, _p, _i, _p, _p, _i64, _p, _p],
-    "mxq_mx_linear_static": [_p, _i, _i64, _i64, _i, _i, _p, _p, _i, _i64, _p, _i, _p, _p, _p],
+    "mxq_mx_gemm": [_p, _p, _i, _p, _p, _i, _i, _p, _i, _p, _i64, _i64, _i64, _p, _p],
+    "mxq_mx_gemm_gather": [_p, _p, _i, _p, _p, _i, _i, _p, _i, _i, _i64, _i64, _i, _p, _i64, _i64, _i64, _p, _p],
+    "mxq_mx_linear": [_p, _i, _i64, _i64, _i, _i, _p, _p, _i, _i, _i64, _p, _i, _p, _p, _i64, _p, _p],
+    "mxq_mx_linear_static": [_p, _i, _i64, _i64, _i, _i, _p, _p, _i, _i, _i64, _p, _i, _p, _p, _p],
+    "mxq_dense_linear": [_p, _p, _i, _p, _p, _i64, _i64, _i64, _p, _p],
+    "mxq_mxfp_weight_linear": [_p, _i, _p, _p, _i, _i, _p, _p, _i64, _i64, _i64, _p, _p],
+    "mxq_minifloat_weight_linear": [_p, _i, _p, _i, _i, _i, _p, _p, _i64, _i64, _i64, _p, _p],
     "mxq_version": [],
 }
-_I64_FUNCS = {"mxq_mx_sf_bytes": [_i64, _i64, _i], "mxq_mx_linear_scratch_bytes": [_i64, _i64],
+_I64_FUNCS = {"mxq_mx_sf_bytes": [_i64, _i64, _i, _i], "mxq_mx_linear_scratch_bytes": [_i64, _i64],
               "mxq_mx_linear_static_capacity": []}
 _STRING_FUNCS = {"mxq_status_string": [_i], "mxq_last_cuda_error": []}
 

@@ -17,7 +17,7 @@ int check_launch() {
 }
 }  // namespace mxq
 
-extern "C" int mxq_version(void) { return 1000; }
+extern "C" int mxq_version(void) { return 1100; }
 
 extern "C" const char* mxq_status_string(int status) {
     switch (status) {

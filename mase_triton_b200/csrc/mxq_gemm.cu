@@ -6,11 +6,13 @@
 //     by TMA (cp.async.bulk.tensor, 128-byte swizzle) into a shared-memory ring;
 //   * the E8M0 block scales of a (tile rows) x 128(K) slab are 512-byte chunks brought in with a
 //     bulk copy and moved shared -> tensor memory with tcgen05.cp;
-//   * one elected thread issues tcgen05.mma.kind::mxf8f6f4.block_scale (M=128, N=224, K=32); the
-//     fp32 accumulators (one or two 128-lane x 224-column blocks) live in tensor memory;
+//   * one elected thread issues tcgen05.mma.kind::mxf8f6f4.block_scale (M=128, N=bn, K=32); the
+//     fp32 accumulators (one or two 128-lane x bn-column blocks) live in tensor memory;
 //   * four epilogue warps read them back with tcgen05.ld, add the bias, convert and store.
-// The CTA tile is 256 x 224 (128 x 224 when M <= 128): two accumulators fill the 512 TMEM columns
-// and raise the flops per byte pulled from L2, which is what bounds this kernel.  CTAs are
+// The CTA tile is 256 x bn (128 x bn when M <= 128) with bn = 224 by default: two accumulators fill
+// the 512 TMEM columns and raise the flops per byte pulled from L2, which is what bounds this kernel.
+// bn is a run-time value (a multiple of 16, at most 224) fixed when the right operand is packed, so a
+// narrow layer can use the width that wastes the least padded work (1024 features: 5 tiles of 208).  CTAs are
 // persistent (one per SM, tiles dealt round-robin in an L2-friendly order): the TMA producer runs
 // ahead into the next tile while the epilogue drains tensor memory.
 // Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer (also owns the TMEM allocation),
@@ -19,43 +21,35 @@
 //
 // Operand layout in HBM (produced by the pack kernel in this file):
 //   codes : [rows, K] bytes, K contiguous
-//   sf    : [ceil(rows/T)][ceil(K/128)][2][512] bytes, T = 256 for the A operand and 224 for B; chunk
+//   sf    : [ceil(rows/T)][ceil(K/128)][2][512] bytes, T = 256 for the A operand and bn for B; chunk
 //           h holds tile-local rows 128h .. 128h+127; inside a chunk the scale of local row r and
 //           K block b (0..3) sits at (r % 32) * 16 + (r / 32) * 4 + b -- the order tcgen05.cp
 //           (32x128b.warpx4) expects.
-#include <cuda.h>
-#include <cuda_bf16.h>
-#include <cuda_fp16.h>
-#include <cuda_runtime.h>
-#include <stdint.h>
-
 #include <cmath>
-#include <mutex>
 
-#include "../../include/mxq.h"
 #include "mxq_codec.h"
-#include "mxq_internal.h"
+#include "mxq_tc.cuh"
 
 namespace mxq {
 namespace gemm {
 
-constexpr int BN = 224, BK = 128;
+using namespace tc;
+
+constexpr int BN_MAX = 224, BK = 128;            // widest right-operand tile (columns of the CTA tile)
 constexpr int A_TILE_ROWS = 256;                 // rows per scale-factor tile of the A operand
-constexpr int B_BYTES = BN * BK;                 // 28 KiB
+constexpr int B_BYTES = BN_MAX * BK;             // 28 KiB reserved per stage, bn * 128 bytes of it used
 constexpr int SF_REGION = 2048;                  // A chunks (<= 1024) + B chunks (1024)
 constexpr int BAR_BYTES = 256;
 constexpr int TMEM_COLS = 512;
 constexpr int SFA_COL = 448, SFB_COL = 456;      // accumulators occupy columns [0, 448)
 constexpr int THREADS = 192;
-constexpr uint32_t SPIN_LIMIT = 1u << 22;
-constexpr int GROUP_M = 8;                       // tiles are dealt in groups of 8 row tiles x all column tiles
 
 template <int MH> struct Cfg {
     static constexpr int BM = 128 * MH;
     static constexpr int A_BYTES = BM * BK;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SF_REGION;       // multiple of 1024
     static constexpr int STAGES = MH == 2 ? 3 : 4;
-    static constexpr int TX_BYTES = A_BYTES + B_BYTES + MH * 512 + 1024;
+    static constexpr int TX_FIXED = A_BYTES + MH * 512 + 1024;       // + bn * BK for the right operand's codes
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;   // + slack to align the ring
 };
 
@@ -68,151 +62,10 @@ struct OutSpec {
     int n, self;
     int64_t ld, col0;
 };
-#ifndef MXQ_FWD_WARPS
-#define MXQ_FWD_WARPS 4
-#endif
-#ifndef MXQ_FWD_UNROLL
-#define MXQ_FWD_UNROLL 4
-#endif
-constexpr int FWD_WARPS = MXQ_FWD_WARPS;         // copy-out warps of the gather-fused kernel
+constexpr int FWD_WARPS = 4;                     // copy-out warps of the gather-fused kernel
+constexpr int FWD_UNROLL = 4;                    // 16-byte units each copy-out lane keeps in flight
 constexpr int STORED_BAR_OFF = 128, ACK_BAR_OFF = 144;   // two barriers each (one per accumulator), inside the BAR_BYTES region past the pipeline barriers
 
-// status codes written to the caller's status word when a bounded wait runs out
-enum : int { ST_OK = 0, ST_PRODUCER_TIMEOUT = 1, ST_MMA_TIMEOUT = 2, ST_EPILOGUE_TIMEOUT = 3, ST_FORWARD_TIMEOUT = 4 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// bounded wait: false (and a code in *status) when the phase never completes
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
-    for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (it > 64) __nanosleep(32);
-    }
-    if (status) atomicCAS(status, 0, code);
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-
-// shared-memory matrix descriptors (tcgen05): start address, leading/stride byte offsets in 16-byte
-// units, version 1, layout type in bits 61..63
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
-    return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
-           ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | ((uint64_t)layout << 61);
-}
-constexpr uint32_t LAYOUT_NONE = 0, LAYOUT_SW128 = 2;
-
-__device__ __forceinline__ void tmem_cp_32x128b(uint32_t taddr, uint64_t desc) {
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
-}
-__device__ __forceinline__ void mma_mxf8f6f4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                             uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
-// tile index -> (row tile, column tile): groups of GROUP_M row tiles sweep all column tiles, so the
-// CTAs running at the same time share a few A tiles and re-use B tiles out of L2
-__device__ __forceinline__ void tile_coords(int t, int MT, int NT, int& mt, int& nt) {
-    const int per_group = GROUP_M * NT;
-    const int g = t / per_group, r = t % per_group;
-    const int gm = min(GROUP_M, MT - g * GROUP_M);
-    mt = g * GROUP_M + r % gm;
-    nt = r / gm;
-}
-
-// `out` is a row-major matrix with leading dimension ld; the tile's columns start at column `shift` of it
-template <int OUT_DT>
-__device__ __forceinline__ void store_chunk(void* __restrict__ out, const void* __restrict__ bias, const uint32_t (&r)[32],
-                                            int row, int col0, int M, int N, int64_t ld, int64_t shift) {
-    if (row >= M || col0 >= N) return;
-    float v[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-    const bool whole = (col0 + 32 <= N);
-    if (bias != nullptr) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            if (whole || col0 + i < N) {
-                if constexpr (OUT_DT == MXQ_F32) v[i] += reinterpret_cast<const float*>(bias)[col0 + i];
-                else if constexpr (OUT_DT == MXQ_BF16) v[i] += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[col0 + i]);
-                else v[i] += __half2float(reinterpret_cast<const __half*>(bias)[col0 + i]);
-            }
-        }
-    }
-    if constexpr (OUT_DT == MXQ_F32) {
-        float* o = reinterpret_cast<float*>(out) + (size_t)row * ld + shift + col0;
-        if (whole && ((ld | shift) % 4 == 0)) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-        } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) if (col0 + i < N) o[i] = v[i];
-        }
-    } else {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-            if constexpr (OUT_DT == MXQ_BF16) { const __nv_bfloat162 h = __floats2bfloat162_rn(v[i], v[i + 1]); pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h); }
-            else { const __half2 h = __floats2half2_rn(v[i], v[i + 1]); pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h); }
-        }
-        uint16_t* o = reinterpret_cast<uint16_t*>(out) + (size_t)row * ld + shift + col0;
-        if (whole && ((ld | shift) % 8 == 0)) {
-#pragma unroll
-            for (int i = 0; i < 16; i += 4) *reinterpret_cast<uint4*>(o + 2 * i) = make_uint4(pk[i], pk[i + 1], pk[i + 2], pk[i + 3]);
-        } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) if (col0 + i < N) o[i] = (uint16_t)(pk[i >> 1] >> (16 * (i & 1)));
-        }
-    }
-}
 
 // Copy-out of the gather-fused kernel: one tile of this GPU's output (just written by the epilogue
 // warps, still in L2) is read back and stored into every peer's output, 16 bytes per lane, whole
@@ -224,7 +77,7 @@ __device__ __forceinline__ void forward_tile(const OutSpec& outs, int fw, int la
     const int upr = cols / EPU;                            // units per row segment (cols is a multiple of EPU)
     const int total = rows * upr;
     const uint8_t* src = reinterpret_cast<const uint8_t*>(outs.ptr[outs.self]);
-    constexpr int UNROLL = MXQ_FWD_UNROLL;
+    constexpr int UNROLL = FWD_UNROLL;
     for (int base = fw * 32 + lane; base < total; base += FWD_WARPS * 32 * UNROLL) {
         uint4 v[UNROLL];
         size_t off[UNROLL];
@@ -247,12 +100,13 @@ __device__ __forceinline__ void forward_tile(const OutSpec& outs, int fw, int la
     }
 }
 
-// OUT_DT: MXQ_F32 / MXQ_BF16 / MXQ_F16; MH: 128-row accumulators per CTA tile; MULTI: gather-fused epilogue
+// OUT_DT: MXQ_F32 / MXQ_BF16 / MXQ_F16; MH: 128-row accumulators per CTA tile; MULTI: gather-fused epilogue;
+// bn: columns of the CTA tile (multiple of 16, <= BN_MAX) = rows per scale-factor tile of the right operand
 template <int OUT_DT, int MH, bool MULTI>
 __global__ void __launch_bounds__(THREADS + (MULTI ? FWD_WARPS * 32 : 0), 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, void* __restrict__ out,
-               const void* __restrict__ bias, int M, int N, int K, uint32_t idesc_base, int* status,
+               const void* __restrict__ bias, int M, int N, int K, int bn, uint32_t idesc_base, int* status,
                const __grid_constant__ OutSpec outs) {
     using C = Cfg<MH>;
     constexpr int STAGES = C::STAGES;
@@ -260,25 +114,28 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t ring = (raw + 1023u) & ~1023u;                    // 1024-aligned operand ring
     uint8_t* ring_ptr = smem_raw + (ring - raw);
-    const uint32_t bars = ring + STAGES * C::STAGE_BYTES;            // full[S], empty[S], accum_full, tmem_empty[2], tmem slot
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ring_ptr + STAGES * C::STAGE_BYTES + 8 * (2 * STAGES + 3));
+    const uint32_t bars = ring + STAGES * C::STAGE_BYTES;            // full[S], empty[S], accum_full, tmem_empty[2], drain, tmem slot
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ring_ptr + STAGES * C::STAGE_BYTES + 8 * (2 * STAGES + 4));
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
     const uint32_t accum_bar = bars + 8u * (2 * STAGES);
     auto tmem_empty_bar = [&](int h) { return bars + 8u * (2 * STAGES + 1 + h); };   // one per accumulator
+    const uint32_t drain_bar = bars + 8u * (2 * STAGES + 3);                         // used only when the MMA warp unwinds
     auto stored_bar = [&](int h) { return bars + STORED_BAR_OFF + 8u * h; };
     auto ack_bar = [&](int h) { return bars + ACK_BAR_OFF + 8u * h; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KT = (K + BK - 1) / BK;
-    const int MT = (M + C::BM - 1) / C::BM, NT = (N + BN - 1) / BN;
+    const int MT = (M + C::BM - 1) / C::BM, NT = (N + bn - 1) / bn;
     const int num_tiles = MT * NT;
+    const uint32_t tx_bytes = (uint32_t)(C::TX_FIXED + bn * BK);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         mbar_init(accum_bar, 1);
         mbar_init(tmem_empty_bar(0), 4);                             // one arrival per epilogue warp
         mbar_init(tmem_empty_bar(1), 4);
+        mbar_init(drain_bar, 1);
         if constexpr (MULTI) {
             for (int h = 0; h < 2; ++h) {
                 mbar_init(stored_bar(h), 4);                         // epilogue warps: "this accumulator's rows are in local memory"
@@ -310,17 +167,24 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int kt = 0; kt < KT && ok; ++kt, ++it) {
                 const int s = it % STAGES;
                 if (it >= STAGES) ok = mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, status, ST_PRODUCER_TIMEOUT);
-                if (ok && lane == 0) {
+                if (!ok) break;
+                if (lane == 0) {
                     const uint32_t st = ring + s * C::STAGE_BYTES;
-                    mbar_expect_tx(full_bar(s), C::TX_BYTES);
+                    mbar_expect_tx(full_bar(s), tx_bytes);
                     tma_load_2d(st, &map_a, kt * BK, mt * C::BM, full_bar(s));
-                    tma_load_2d(st + C::A_BYTES, &map_b, kt * BK, nt * BN, full_bar(s));
+                    tma_load_2d(st + C::A_BYTES, &map_b, kt * BK, nt * bn, full_bar(s));
                     bulk_load(st + C::A_BYTES + B_BYTES, sfa_tile + (size_t)kt * 1024, MH * 512, full_bar(s));
                     bulk_load(st + C::A_BYTES + B_BYTES + 1024, sfb_tile + (size_t)kt * 1024, 1024, full_bar(s));
                 }
                 __syncwarp();
             }
         }
+        // Every copy this warp started must have landed before the CTA gives its shared memory back.  In a
+        // run that went well the MMA warp has consumed them all and these waits return at once; after a
+        // wait that ran out they (bounded, too) cover the copies nobody consumed.
+        const uint32_t issued = it;
+        for (uint32_t j = (issued > (uint32_t)STAGES ? issued - STAGES : 0u); j < issued; ++j)
+            mbar_wait(full_bar(j % STAGES), (j / STAGES) & 1, status, ST_PRODUCER_TIMEOUT);
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         bool ok = true;
@@ -351,7 +215,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             // +32 bytes along K inside the 128-byte swizzle span = +2 in the address field;
                             // scale-factor byte k of each 32-bit TMEM column
                             const uint32_t idesc = idesc_base | (k << 29) | (k << 4);
-                            mma_mxf8f6f4(tmem_base + h * BN, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_base + SFA_COL + 4 * h,
+                            mma_mxf8f6f4(tmem_base + h * BN_MAX, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_base + SFA_COL + 4 * h,
                                          tmem_base + SFB_COL, (kt > 0 || k > 0) ? 1u : 0u);
                         }
                         if (h == MH - 1) mma_commit(empty_bar(s));     // frees the stage once these MMAs have read it
@@ -359,12 +223,25 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     __syncwarp();
                 }
             }
+#ifndef MXQ_TEST_DROP_ACCUM_COMMIT
             if (lane == 0) mma_commit(accum_bar);         // accumulators of this tile complete (or unwinding)
+#endif
             __syncwarp();
+        }
+#ifdef MXQ_TEST_DROP_ACCUM_COMMIT
+        ok = false;                                       // test-only build: nothing above tracked the MMAs' completion
+#endif
+        if (!ok) {
+            // unwinding after a wait that ran out: the MMAs already issued must finish before tensor memory is freed
+            if (lane == 0) mma_commit(drain_bar);
+            __syncwarp();
+            mbar_wait(drain_bar, 0, nullptr, 0);
         }
     } else if (warp < 6) {
         // ---------------- epilogue: TMEM -> registers -> global ----------------
         const int q = warp & 3;                            // TMEM lane quadrant this warp may access
+        const int full_chunks = bn >> 5;                   // 32-column chunks, then possibly one of 16 columns
+        const bool tail16 = (bn & 16) != 0;
         bool ok = true;
         uint32_t tcount = 0;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
@@ -376,19 +253,30 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
             for (int h = 0; h < MH; ++h) {
                 const int row = mt * C::BM + h * 128 + q * 32 + lane;
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + h * BN_MAX;
+                void* dst = MULTI ? outs.ptr[outs.self] : out;
+                const int64_t ld = MULTI ? outs.ld : (int64_t)N, shift = MULTI ? outs.col0 : 0;
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
+                for (int c = 0; c < full_chunks; ++c) {
                     uint32_t r[32];
-                    tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + h * BN + c * 32, r);
+                    tmem_ld_32x32b_x32(taddr + c * 32, r);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (c == BN / 32 - 1) {
+                    if (c == full_chunks - 1 && !tail16) {
                         // last read of this accumulator: hand it back to the MMA warp
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(tmem_empty_bar(h));
                     }
-                    if constexpr (!MULTI) store_chunk<OUT_DT>(out, bias, r, row, nt * BN + c * 32, M, N, N, 0);
-                    else store_chunk<OUT_DT>(outs.ptr[outs.self], bias, r, row, nt * BN + c * 32, M, N, outs.ld, outs.col0);
+                    store_chunk<OUT_DT, 32>(dst, bias, r, row, nt * bn + c * 32, M, N, ld, shift);
+                }
+                if (tail16) {
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x16(taddr + full_chunks * 32, r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tmem_empty_bar(h));
+                    store_chunk<OUT_DT, 16>(dst, bias, r, row, nt * bn + full_chunks * 32, M, N, ld, shift);
                 }
                 if constexpr (MULTI) {
                     // tell the copy-out warps that this warp's rows of accumulator h are in local memory; they
@@ -414,7 +302,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     __syncwarp();
                     if (lane == 0) mbar_arrive(ack_bar(h));
                     const int row0 = mt * C::BM + h * 128;
-                    if (row0 < M) forward_tile<OUT_DT>(outs, fw, lane, row0, min(128, M - row0), nt * BN, min(BN, N - nt * BN));
+                    if (row0 < M) forward_tile<OUT_DT>(outs, fw, lane, row0, min(128, M - row0), nt * bn, min(bn, N - nt * bn));
                 }
             }
         }
@@ -517,22 +405,6 @@ static bool build_pack_tables(int eb, int fb, PackTables* t, int* hw_fmt) {
     return true;
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    });
-    return fn;
-}
-
 static bool make_operand_map(CUtensorMap* map, const void* codes, int64_t rows, int64_t K, int box_rows) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
@@ -544,46 +416,46 @@ static bool make_operand_map(CUtensorMap* map, const void* codes, int64_t rows, 
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-static int sm_count() {
-    static int n = 0;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    });
-    return n;
-}
-
 // outs == nullptr: plain epilogue into `out`; otherwise the gather-fused epilogue into outs->ptr[]
 template <int OUT_DT, int MH, bool MULTI>
 static int launch_gemm(const uint8_t* a_codes, const uint8_t* b_codes, const uint8_t* sfa, const uint8_t* sfb, void* out,
-                       const void* bias, int M, int N, int K, uint32_t idesc, int* status, cudaStream_t st, const OutSpec* outs) {
+                       const void* bias, int M, int N, int K, int bn, uint32_t idesc, int* status, cudaStream_t st, const OutSpec* outs) {
     using C = Cfg<MH>;
     constexpr int SMEM = C::SMEM_BYTES;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] { attr_err = cudaFuncSetAttribute(mx_gemm_kernel<OUT_DT, MH, MULTI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
+    static bool attr_done[MAX_DEVICES] = {false};
+    const cudaError_t attr_err = raise_smem_limit(mx_gemm_kernel<OUT_DT, MH, MULTI>, SMEM, attr_done);
     if (attr_err != cudaSuccess) { set_last_cuda_error(attr_err); return MXQ_ELAUNCH; }
     CUtensorMap ma, mb;
-    if (!make_operand_map(&ma, a_codes, M, K, C::BM) || !make_operand_map(&mb, b_codes, N, K, BN)) return MXQ_ELAUNCH;
-    const int tiles = ((M + C::BM - 1) / C::BM) * ((N + BN - 1) / BN);
+    if (!make_operand_map(&ma, a_codes, M, K, C::BM) || !make_operand_map(&mb, b_codes, N, K, bn)) return MXQ_ELAUNCH;
+    const int tiles = ((M + C::BM - 1) / C::BM) * ((N + bn - 1) / bn);
     const int grid = tiles < sm_count() ? tiles : sm_count();          // persistent: one CTA per SM
-    mx_gemm_kernel<OUT_DT, MH, MULTI><<<grid, THREADS + (MULTI ? FWD_WARPS * 32 : 0), SMEM, st>>>(ma, mb, sfa, sfb, out, bias, M, N, K, idesc, status,
+    mx_gemm_kernel<OUT_DT, MH, MULTI><<<grid, THREADS + (MULTI ? FWD_WARPS * 32 : 0), SMEM, st>>>(ma, mb, sfa, sfb, out, bias, M, N, K, bn, idesc, status,
                                                                     MULTI ? *outs : OutSpec{});
     return check_launch();
 }
 
 template <int OUT_DT>
 static int launch_gemm_dt(const uint8_t* a_codes, const uint8_t* b_codes, const uint8_t* sfa, const uint8_t* sfb, void* out,
-                          const void* bias, int M, int N, int K, uint32_t idesc, int* status, cudaStream_t st,
+                          const void* bias, int M, int N, int K, int bn, uint32_t idesc, int* status, cudaStream_t st,
                           const OutSpec* outs = nullptr) {
     if (outs != nullptr) {
-        if (M <= 128) return launch_gemm<OUT_DT, 1, true>(a_codes, b_codes, sfa, sfb, nullptr, bias, M, N, K, idesc, status, st, outs);
-        return launch_gemm<OUT_DT, 2, true>(a_codes, b_codes, sfa, sfb, nullptr, bias, M, N, K, idesc, status, st, outs);
+        if (M <= 128) return launch_gemm<OUT_DT, 1, true>(a_codes, b_codes, sfa, sfb, nullptr, bias, M, N, K, bn, idesc, status, st, outs);
+        return launch_gemm<OUT_DT, 2, true>(a_codes, b_codes, sfa, sfb, nullptr, bias, M, N, K, bn, idesc, status, st, outs);
     }
-    if (M <= 128) return launch_gemm<OUT_DT, 1, false>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, idesc, status, st, nullptr);
-    return launch_gemm<OUT_DT, 2, false>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, idesc, status, st, nullptr);
+    if (M <= 128) return launch_gemm<OUT_DT, 1, false>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, bn, idesc, status, st, nullptr);
+    return launch_gemm<OUT_DT, 2, false>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, bn, idesc, status, st, nullptr);
+}
+
+// instruction descriptor: A/B formats, K-major operands, N >> 3, E8M0 scales, M >> 4
+static uint32_t mx_idesc(int a_hw_format, int b_hw_format, int bn) {
+    return ((uint32_t)a_hw_format << 7) | ((uint32_t)b_hw_format << 10) | ((uint32_t)(bn >> 3) << 17) | (1u << 23) |
+           ((uint32_t)(128 >> 4) << 24);
+}
+
+// the right operand's tile width: 0 selects the default, otherwise a multiple of 16 in [16, BN_MAX]
+static int resolve_b_tile(int b_tile_rows) {
+    if (b_tile_rows == 0) return BN_MAX;
+    return (b_tile_rows >= 16 && b_tile_rows <= BN_MAX && b_tile_rows % 16 == 0) ? b_tile_rows : -1;
 }
 
 }  // namespace gemm
@@ -591,51 +463,68 @@ static int launch_gemm_dt(const uint8_t* a_codes, const uint8_t* b_codes, const 
 
 using namespace mxq;
 
-static int sf_tile_rows(int operand) { return operand == 0 ? gemm::A_TILE_ROWS : gemm::BN; }
+// rows per scale-factor tile: 256 for the left operand; for the right one the CTA tile width it will be multiplied with
+static int sf_tile_rows(int operand, int tile_rows) { return operand == MXQ_OPERAND_A ? gemm::A_TILE_ROWS : gemm::resolve_b_tile(tile_rows); }
 
-extern "C" int64_t mxq_mx_sf_bytes(int64_t rows, int64_t K, int operand) {
+extern "C" int mxq_mx_best_tile_rows(int64_t N) {
+    // fewest padded columns first, the wider tile on a tie; widths below 160 only cost arithmetic intensity
+    if (N <= 0) return gemm::BN_MAX;
+    int best = gemm::BN_MAX;
+    int64_t best_padded = ((N + best - 1) / best) * best;
+    for (int t = gemm::BN_MAX - 16; t >= 160; t -= 16) {
+        const int64_t padded = ((N + t - 1) / t) * t;
+        if (padded < best_padded) { best = t; best_padded = padded; }
+    }
+    return best;
+}
+
+extern "C" int64_t mxq_mx_sf_bytes(int64_t rows, int64_t K, int operand, int tile_rows) {
     if (rows < 0 || K < 0 || (operand & ~1)) return MXQ_EINVAL;
-    const int64_t t = sf_tile_rows(operand);
+    const int64_t t = sf_tile_rows(operand, tile_rows);
+    if (t <= 0) return MXQ_EINVAL;
     return ((rows + t - 1) / t) * ((K + 127) / 128) * 1024;
 }
 
 extern "C" int mxq_mx_pack_operand(const uint8_t* scales, const uint8_t* elements, int64_t rows, int64_t K, int eb, int fb,
-                                   int operand, uint8_t* hw_codes, uint8_t* hw_sf, int* hw_format, void* stream) {
+                                   int operand, int tile_rows, uint8_t* hw_codes, uint8_t* hw_sf, int* hw_format, void* stream) {
     if (rows <= 0 || K <= 0 || K % 32 != 0 || (operand & ~1) || !elements || !hw_codes || !hw_sf || !hw_format) return MXQ_EINVAL;
     if ((reinterpret_cast<uintptr_t>(elements) | reinterpret_cast<uintptr_t>(hw_codes)) % 16 != 0) return MXQ_EINVAL;
     gemm::PackTables t;
     if (!gemm::build_pack_tables(eb, fb, &t, hw_format)) return MXQ_EINVAL;
-    const int tile = sf_tile_rows(operand);
+    const int tile = sf_tile_rows(operand, tile_rows);
+    if (tile <= 0) return MXQ_EINVAL;
     const int64_t total = ((rows + tile - 1) / tile) * 256 * (((K + 127) / 128) * 4);
     gemm::mx_pack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(scales, elements, hw_codes, hw_sf, rows, K, tile, t);
     return check_launch();
 }
 
 extern "C" int mxq_mx_gemm(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw_format, const uint8_t* b_codes,
-                           const uint8_t* b_sf, int b_hw_format, void* out, int out_dtype, const void* bias, int64_t M,
-                           int64_t N, int64_t K, int* status, void* stream) {
+                           const uint8_t* b_sf, int b_hw_format, int b_tile_rows, void* out, int out_dtype, const void* bias,
+                           int64_t M, int64_t N, int64_t K, int* status, void* stream) {
     if (M <= 0 || N <= 0 || K <= 0 || K % 32 != 0 || M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return MXQ_EINVAL;
     if (!a_codes || !a_sf || !b_codes || !b_sf || !out) return MXQ_EINVAL;
     if ((a_hw_format | b_hw_format) & ~1) return MXQ_EINVAL;
+    const int bn = gemm::resolve_b_tile(b_tile_rows);
+    if (bn <= 0) return MXQ_EINVAL;
     if ((reinterpret_cast<uintptr_t>(a_codes) | reinterpret_cast<uintptr_t>(b_codes) | reinterpret_cast<uintptr_t>(a_sf) |
          reinterpret_cast<uintptr_t>(b_sf) | reinterpret_cast<uintptr_t>(out)) % 16 != 0) return MXQ_EINVAL;
-    // instruction descriptor: A/B formats, K-major operands, N >> 3, E8M0 scales, M >> 4
-    const uint32_t idesc = ((uint32_t)a_hw_format << 7) | ((uint32_t)b_hw_format << 10) | ((uint32_t)(gemm::BN >> 3) << 17) |
-                           (1u << 23) | ((uint32_t)(128 >> 4) << 24);
+    const uint32_t idesc = gemm::mx_idesc(a_hw_format, b_hw_format, bn);
     cudaStream_t st = (cudaStream_t)stream;
-    if (out_dtype == MXQ_F32) return gemm::launch_gemm_dt<MXQ_F32>(a_codes, b_codes, a_sf, b_sf, out, bias, (int)M, (int)N, (int)K, idesc, status, st);
-    if (out_dtype == MXQ_BF16) return gemm::launch_gemm_dt<MXQ_BF16>(a_codes, b_codes, a_sf, b_sf, out, bias, (int)M, (int)N, (int)K, idesc, status, st);
-    if (out_dtype == MXQ_F16) return gemm::launch_gemm_dt<MXQ_F16>(a_codes, b_codes, a_sf, b_sf, out, bias, (int)M, (int)N, (int)K, idesc, status, st);
+    if (out_dtype == MXQ_F32) return gemm::launch_gemm_dt<MXQ_F32>(a_codes, b_codes, a_sf, b_sf, out, bias, (int)M, (int)N, (int)K, bn, idesc, status, st);
+    if (out_dtype == MXQ_BF16) return gemm::launch_gemm_dt<MXQ_BF16>(a_codes, b_codes, a_sf, b_sf, out, bias, (int)M, (int)N, (int)K, bn, idesc, status, st);
+    if (out_dtype == MXQ_F16) return gemm::launch_gemm_dt<MXQ_F16>(a_codes, b_codes, a_sf, b_sf, out, bias, (int)M, (int)N, (int)K, bn, idesc, status, st);
     return MXQ_EINVAL;
 }
 
 extern "C" int mxq_mx_gemm_gather(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw_format, const uint8_t* b_codes,
-                                  const uint8_t* b_sf, int b_hw_format, void* const* outs, int n_outs, int self_index,
+                                  const uint8_t* b_sf, int b_hw_format, int b_tile_rows, void* const* outs, int n_outs, int self_index,
                                   int64_t ld_out, int64_t col_offset, int out_dtype, const void* bias, int64_t M, int64_t N, int64_t K,
                                   int* status, void* stream) {
     if (M <= 0 || N <= 0 || K <= 0 || K % 32 != 0 || M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return MXQ_EINVAL;
     if (!a_codes || !a_sf || !b_codes || !b_sf || !outs || n_outs < 1 || n_outs > gemm::MAX_DEST || self_index < 0 || self_index >= n_outs) return MXQ_EINVAL;
     if ((a_hw_format | b_hw_format) & ~1) return MXQ_EINVAL;
+    const int bn = gemm::resolve_b_tile(b_tile_rows);
+    if (bn <= 0) return MXQ_EINVAL;
     if (col_offset < 0 || ld_out < col_offset + N) return MXQ_EINVAL;
     if (out_dtype != MXQ_F32 && out_dtype != MXQ_BF16 && out_dtype != MXQ_F16) return MXQ_EINVAL;
     // whole 16-byte units only: the shard width, its offset and the leading dimension in units of 16 bytes
@@ -651,19 +540,18 @@ extern "C" int mxq_mx_gemm_gather(const uint8_t* a_codes, const uint8_t* a_sf, i
     }
     if (align % 16 != 0) return MXQ_EINVAL;
     spec.n = n_outs; spec.self = self_index; spec.ld = ld_out; spec.col0 = col_offset;
-    const uint32_t idesc = ((uint32_t)a_hw_format << 7) | ((uint32_t)b_hw_format << 10) | ((uint32_t)(gemm::BN >> 3) << 17) |
-                           (1u << 23) | ((uint32_t)(128 >> 4) << 24);
+    const uint32_t idesc = gemm::mx_idesc(a_hw_format, b_hw_format, bn);
     cudaStream_t st = (cudaStream_t)stream;
-    if (out_dtype == MXQ_F32) return gemm::launch_gemm_dt<MXQ_F32>(a_codes, b_codes, a_sf, b_sf, nullptr, bias, (int)M, (int)N, (int)K, idesc, status, st, &spec);
-    if (out_dtype == MXQ_BF16) return gemm::launch_gemm_dt<MXQ_BF16>(a_codes, b_codes, a_sf, b_sf, nullptr, bias, (int)M, (int)N, (int)K, idesc, status, st, &spec);
-    return gemm::launch_gemm_dt<MXQ_F16>(a_codes, b_codes, a_sf, b_sf, nullptr, bias, (int)M, (int)N, (int)K, idesc, status, st, &spec);
+    if (out_dtype == MXQ_F32) return gemm::launch_gemm_dt<MXQ_F32>(a_codes, b_codes, a_sf, b_sf, nullptr, bias, (int)M, (int)N, (int)K, bn, idesc, status, st, &spec);
+    if (out_dtype == MXQ_BF16) return gemm::launch_gemm_dt<MXQ_BF16>(a_codes, b_codes, a_sf, b_sf, nullptr, bias, (int)M, (int)N, (int)K, bn, idesc, status, st, &spec);
+    return gemm::launch_gemm_dt<MXQ_F16>(a_codes, b_codes, a_sf, b_sf, nullptr, bias, (int)M, (int)N, (int)K, bn, idesc, status, st, &spec);
 }
 
 // ------------------------------------------------------------------------------------------------
 // fused-backend linear: quantise the activation, pack it, run the GEMM -- scratch supplied by the caller
 // ------------------------------------------------------------------------------------------------
 static int linear_with_scratch(const void* x, int x_dtype, int64_t M, int64_t K, int x_eb, int x_fb, const uint8_t* w_codes,
-                               const uint8_t* w_sf, int w_hw_format, int64_t N, void* out, int out_dtype, const void* bias,
+                               const uint8_t* w_sf, int w_hw_format, int w_tile_rows, int64_t N, void* out, int out_dtype, const void* bias,
                                uint8_t* scratch, int* status, void* stream) {
     // scratch: [M*K] element codes (re-encoded in place) | [M*K/32] reference scales | packed scale chunks
     uint8_t* codes = scratch;
@@ -671,30 +559,30 @@ static int linear_with_scratch(const void* x, int x_dtype, int64_t M, int64_t K,
     uint8_t* sf = ref_scales + ((M * K / 32 + 255) / 256) * 256;
     int x_fmt = 0;
     // MXFP8 activations: one pass straight into the operand layout; other formats take extract + pack
-    int rc = quantize_pack_left_operand(x, x_dtype, M, K, x_eb, x_fb, codes, sf, mxq_mx_sf_bytes(M, K, MXQ_OPERAND_A), &x_fmt,
+    int rc = quantize_pack_left_operand(x, x_dtype, M, K, x_eb, x_fb, codes, sf, mxq_mx_sf_bytes(M, K, MXQ_OPERAND_A, 0), &x_fmt,
                                         (cudaStream_t)stream);
-    if (rc == MXQ_OK) return mxq_mx_gemm(codes, sf, x_fmt, w_codes, w_sf, w_hw_format, out, out_dtype, bias, M, N, K, status, stream);
+    if (rc == MXQ_OK) return mxq_mx_gemm(codes, sf, x_fmt, w_codes, w_sf, w_hw_format, w_tile_rows, out, out_dtype, bias, M, N, K, status, stream);
     if (rc != MXQ_ESIZE) return rc;
     rc = mxq_mxfp_extract(x, x_dtype, ref_scales, codes, M * K, 32, x_eb, x_fb, 1, MXQ_RN, stream);
     if (rc != MXQ_OK) return rc;
     int x_hw_format = 0;
-    rc = mxq_mx_pack_operand(ref_scales, codes, M, K, x_eb, x_fb, MXQ_OPERAND_A, codes, sf, &x_hw_format, stream);
+    rc = mxq_mx_pack_operand(ref_scales, codes, M, K, x_eb, x_fb, MXQ_OPERAND_A, 0, codes, sf, &x_hw_format, stream);
     if (rc != MXQ_OK) return rc;
-    return mxq_mx_gemm(codes, sf, x_hw_format, w_codes, w_sf, w_hw_format, out, out_dtype, bias, M, N, K, status, stream);
+    return mxq_mx_gemm(codes, sf, x_hw_format, w_codes, w_sf, w_hw_format, w_tile_rows, out, out_dtype, bias, M, N, K, status, stream);
 }
 
 extern "C" int64_t mxq_mx_linear_scratch_bytes(int64_t M, int64_t K) {
     if (M <= 0 || K <= 0 || K % 32 != 0) return MXQ_EINVAL;
-    return M * K + ((M * K / 32 + 255) / 256) * 256 + mxq_mx_sf_bytes(M, K, MXQ_OPERAND_A);
+    return M * K + ((M * K / 32 + 255) / 256) * 256 + mxq_mx_sf_bytes(M, K, MXQ_OPERAND_A, 0);
 }
 
 extern "C" int mxq_mx_linear(const void* x, int x_dtype, int64_t M, int64_t K, int x_exp_bits, int x_frac_bits,
-                             const uint8_t* w_codes, const uint8_t* w_sf, int w_hw_format, int64_t N, void* out, int out_dtype,
-                             const void* bias, void* scratch, int64_t scratch_bytes, int* status, void* stream) {
+                             const uint8_t* w_codes, const uint8_t* w_sf, int w_hw_format, int w_tile_rows, int64_t N, void* out,
+                             int out_dtype, const void* bias, void* scratch, int64_t scratch_bytes, int* status, void* stream) {
     if (!x || !w_codes || !w_sf || !out || !scratch || M <= 0 || N <= 0 || K <= 0 || K % 32 != 0) return MXQ_EINVAL;
     if (reinterpret_cast<uintptr_t>(scratch) % 256 != 0) return MXQ_EINVAL;
     if (scratch_bytes < mxq_mx_linear_scratch_bytes(M, K)) return MXQ_ESIZE;
-    return linear_with_scratch(x, x_dtype, M, K, x_exp_bits, x_frac_bits, w_codes, w_sf, w_hw_format, N, out, out_dtype, bias,
+    return linear_with_scratch(x, x_dtype, M, K, x_exp_bits, x_frac_bits, w_codes, w_sf, w_hw_format, w_tile_rows, N, out, out_dtype, bias,
                                static_cast<uint8_t*>(scratch), status, stream);
 }
 
@@ -729,22 +617,22 @@ static uint8_t* static_scratch_ptr() {
 extern "C" int64_t mxq_mx_linear_static_capacity(void) { return MXQ_STATIC_SCRATCH_BYTES; }
 
 extern "C" int mxq_mx_linear_static(const void* x, int x_dtype, int64_t M, int64_t K, int x_exp_bits, int x_frac_bits,
-                                    const uint8_t* w_codes, const uint8_t* w_sf, int w_hw_format, int64_t N, void* out,
-                                    int out_dtype, const void* bias, int* status, void* stream) {
+                                    const uint8_t* w_codes, const uint8_t* w_sf, int w_hw_format, int w_tile_rows, int64_t N,
+                                    void* out, int out_dtype, const void* bias, int* status, void* stream) {
     if (!x || !w_codes || !w_sf || !out || M <= 0 || N <= 0 || K <= 0 || K % 32 != 0) return MXQ_EINVAL;
     if (mxq_mx_linear_scratch_bytes(M, K) > MXQ_STATIC_SCRATCH_BYTES) return MXQ_ESIZE;   // activation too large for the fixed scratch
     uint8_t* scratch = static_scratch_ptr();
     if (scratch == nullptr) return MXQ_ELAUNCH;
     // every byte of the scratch that the GEMM reads is written by the two kernels before it, so
     // nothing has to be cleared between calls
-    return linear_with_scratch(x, x_dtype, M, K, x_exp_bits, x_frac_bits, w_codes, w_sf, w_hw_format, N, out, out_dtype, bias,
+    return linear_with_scratch(x, x_dtype, M, K, x_exp_bits, x_frac_bits, w_codes, w_sf, w_hw_format, w_tile_rows, N, out, out_dtype, bias,
                                scratch, status, stream);
 }
 
 extern "C" int mxq_mx_quantize_pack(const void* x, int x_dtype, int64_t M, int64_t K, int exp_bits, int frac_bits,
                                     uint8_t* hw_codes, uint8_t* hw_sf, int* hw_format, void* stream) {
     if (!x || !hw_codes || !hw_sf || !hw_format || M <= 0 || K <= 0 || K % 32 != 0) return MXQ_EINVAL;
-    return quantize_pack_left_operand(x, x_dtype, M, K, exp_bits, frac_bits, hw_codes, hw_sf, mxq_mx_sf_bytes(M, K, MXQ_OPERAND_A),
+    return quantize_pack_left_operand(x, x_dtype, M, K, exp_bits, frac_bits, hw_codes, hw_sf, mxq_mx_sf_bytes(M, K, MXQ_OPERAND_A, 0),
                                       hw_format, (cudaStream_t)stream);
 }
 
@@ -753,5 +641,5 @@ extern "C" int mxq_minifloat_quantize_pack(const void* x, int x_dtype, int64_t M
     if (!x || !hw_codes || !hw_sf || !hw_format || M <= 0 || K <= 0 || K % 32 != 0) return MXQ_EINVAL;
     if (round_mode != MXQ_RN) return MXQ_ESIZE;
     return minifloat_quantize_pack_left_operand(x, x_dtype, M, K, exp_bits, frac_bits, hw_codes, hw_sf,
-                                                mxq_mx_sf_bytes(M, K, MXQ_OPERAND_A), hw_format, (cudaStream_t)stream);
+                                                mxq_mx_sf_bytes(M, K, MXQ_OPERAND_A, 0), hw_format, (cudaStream_t)stream);
 }

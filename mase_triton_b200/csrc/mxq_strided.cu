@@ -15,11 +15,9 @@
 // four 32-byte code runs of one column form one 128-byte line.
 #include "mxq_device.cuh"
 
-#ifndef MXQ_STRIDED_MINB
-#define MXQ_STRIDED_MINB 2
-#endif
-
 namespace mxq {
+
+constexpr int kStridedQdqMinBlocks = 2;   // resident CTAs per SM asked of the fused kernel (caps its registers)
 
 constexpr int kRowBlocks = 4;          // blocks along D per CTA
 constexpr int kColThreads = kThreads / kRowBlocks;
@@ -110,7 +108,7 @@ __device__ __forceinline__ bool strided_position(const StridedGeom& g, int64_t& 
 }
 
 template <class KIn, class F, int CPT, int MODE>
-__global__ void __launch_bounds__(kThreads, MODE == MODE_QDQ ? MXQ_STRIDED_MINB : 1) mxfp_strided_quant_kernel(const void* __restrict__ x, uint8_t* __restrict__ scales,
+__global__ void __launch_bounds__(kThreads, MODE == MODE_QDQ ? kStridedQdqMinBlocks : 1) mxfp_strided_quant_kernel(const void* __restrict__ x, uint8_t* __restrict__ scales,
                                                                       uint8_t* __restrict__ elements, void* __restrict__ out,
                                                                       StridedGeom g, F f) {
     int64_t o, jb, i0;

@@ -2,11 +2,12 @@
 
 Per-tensor (un-blocked) fake quantisation of activation, weight and bias followed by a
 dense linear.  ``layer_type`` names what is quantised (``Xq``/``X``, ``Wq``/``W``, ``Bq``/``B``).
-Both backends give the same values: ``"separate"`` mirrors the reference's op sequence,
-``"fused"`` (a stub in the reference) keeps activation and weight as 8-bit codes and multiplies them
-on the tensor cores (the block-scaled GEMM with every block scale at 2^0) when both are quantised to a
-finite format of at most 8 bits and ``in_features`` is a multiple of 32; otherwise it runs the same
-kernels as ``"separate"``.
+``"separate"`` mirrors the reference's op sequence (dequantise, then a library linear).  ``"fused"`` (a stub
+in the reference) runs this library's tensor-core GEMMs: with both operands quantised to E4M3, E5M2 or one
+of the narrower OCP formats and ``in_features`` a multiple of 32, activation and weight stay 8-bit codes
+(the block-scaled GEMM with every block scale at 2^0); every other layer type on bf16 / fp16 activations
+takes the ``kind::f16`` GEMM that expands weight codes in its operand loader; what neither takes raises
+``NotImplementedError``.
 """
 
 from __future__ import annotations
@@ -22,8 +23,13 @@ from .. import kernels
 from .cast import compose_minifloat_component, quantize_dequantize
 
 
+# element formats whose every value has an exact 8-bit tensor-core encoding (the pack tables of
+# mxq_mx_pack_operand): E4M3, E5M2 and the three narrower OCP formats
+_TENSOR_CORE_FORMATS = frozenset({(4, 3), (5, 2), (2, 3), (3, 2), (2, 1)})
+
+
 def _narrow(meta: MinifloatMeta | None) -> bool:
-    return meta is not None and meta.is_finite and meta.exp_bits + meta.frac_bits <= 7
+    return meta is not None and meta.is_finite and (meta.exp_bits, meta.frac_bits) in _TENSOR_CORE_FORMATS
 
 
 def _tensor_core_ok(x: Tensor, x_meta, w_element, w_tensor_meta) -> bool:
@@ -59,6 +65,27 @@ def _fused_linear(x: Tensor, x_meta: MinifloatMeta, w_element: Tensor, w_tensor_
     return out.reshape(*x.shape[:-1], out.shape[-1])
 
 
+def _tc_linear(x: Tensor, x_meta, w: Tensor | None, w_element: Tensor | None, w_tensor_meta, bias: Tensor | None, kind) -> Tensor:
+    """``backend="fused"`` for the layer types that are not "both operands as 8-bit tensor-core codes":
+    ``tcgen05.mma.kind::f16`` GEMM on bf16 / fp16 activations; an ``Xq`` activation is fake-quantised by
+    one kernel first, ``Wq`` codes are expanded inside the GEMM's operand loader."""
+    from ... import tc_linear
+
+    reason = tc_linear.why_not(x, x.shape[-1])
+    if reason is not None:
+        raise NotImplementedError(f"backend='fused' is not implemented for this call: {reason}; use backend='separate'")
+    if kind.x_quantised:
+        x = quantize_dequantize(x, x_meta)
+    if not kind.w_quantised:
+        return tc_linear.dense_linear(x, w, bias)
+    if getattr(torch, w_tensor_meta.dtype) != x.dtype:
+        raise RuntimeError(f"the weight dequantises to {w_tensor_meta.dtype}, the input is {x.dtype}")
+    shape = tuple(w_tensor_meta.shape)
+    if len(shape) == 2 and w_tensor_meta.meta.exp_bits <= 8 and w_element.dtype == torch.uint16:
+        return tc_linear.minifloat_weight_linear(x, w_element, shape, w_tensor_meta.meta, bias)
+    return tc_linear.dense_linear(x, compose_minifloat_component(w_element, w_tensor_meta).contiguous(), bias)
+
+
 def minifloat_linear(
     x: Tensor,
     x_meta: MinifloatMeta | None,
@@ -73,18 +100,16 @@ def minifloat_linear(
 ) -> Tensor:
     kind = parse_layer_type(layer_type)
     check_backend(backend)
-    if backend == "fused" and kind.x_quantised and kind.w_quantised and _tensor_core_ok(x, x_meta, w_element, w_tensor_meta):
-        if kind.b_quantised:
-            bias = compose_minifloat_component(b_element, b_tensor_meta) if b is not None else None
-        else:
-            bias = b
-        return _fused_linear(x, x_meta, w_element, w_tensor_meta, bias)
-    if kind.x_quantised:
-        x = quantize_dequantize(x, x_meta)                      # same bits as extract + compose
-    weight = compose_minifloat_component(w_element, w_tensor_meta) if kind.w_quantised else w
     if kind.b_quantised:
         # a quantised-bias layer ignores a plain bias unless codes for it exist
         bias = compose_minifloat_component(b_element, b_tensor_meta) if b is not None else None
     else:
         bias = b
+    if backend == "fused":
+        if kind.x_quantised and kind.w_quantised and _tensor_core_ok(x, x_meta, w_element, w_tensor_meta):
+            return _fused_linear(x, x_meta, w_element, w_tensor_meta, bias)
+        return _tc_linear(x, x_meta, w, w_element, w_tensor_meta, bias, kind)
+    if kind.x_quantised:
+        x = quantize_dequantize(x, x_meta)                      # same bits as extract + compose
+    weight = compose_minifloat_component(w_element, w_tensor_meta) if kind.w_quantised else w
     return torch.nn.functional.linear(x, weight, bias)

@@ -3,7 +3,8 @@
 ``layer_type`` names what is fake-quantised: activation (``Xq``, blocks along the last dim),
 weight (``Wq``, blocks along ``in_features``) and bias (``Bq``).  ``backend="separate"`` follows
 the reference's op sequence (dequantise, then a dense linear in the operand dtype);
-``backend="fused"`` is a stub in the reference and is implemented here.
+``backend="fused"`` is a stub in the reference; here it runs the tensor-core GEMMs of this library
+(``csrc/mxq_gemm.cu``, ``csrc/mxq_dq_gemm.cu``) and raises ``NotImplementedError`` for what they do not take.
 """
 
 from __future__ import annotations
@@ -13,6 +14,7 @@ from typing import Literal
 import torch
 from torch import Tensor
 
+from ... import _lib, tc_linear
 from ..._linear_common import check_backend, parse_layer_type
 from ..meta import MXFPMeta, MXFPTensorMeta
 from .. import gemm as _gemm
@@ -26,6 +28,40 @@ def parse_mxfp_linear_type(x_meta: MXFPMeta | None, w_tensor_meta: MXFPTensorMet
     """Layer-type string for the given metas: a ``q`` after X / W / B when that operand has a meta."""
     return "".join(name + ("" if meta is None else "q")
                    for name, meta in (("X", x_meta), ("W", w_tensor_meta), ("B", b_tensor_meta)))
+
+
+def _fused_linear(x: Tensor, x_meta: MXFPMeta | None, w: Tensor | None, w_scales: Tensor | None, w_elements: Tensor | None,
+                  w_tensor_meta: MXFPTensorMeta | None, bias: Tensor | None, kind) -> Tensor:
+    """``backend="fused"``: every layer type runs a hand-written tensor-core GEMM of this library.
+
+    * ``XqWq`` with 32-element blocks and is_finite elements: both operands stay quantised, block-scaled
+      ``tcgen05.mma.kind::mxf8f6f4`` GEMM (fp32 / bf16 / fp16 activations);
+    * every other combination on bf16 / fp16 activations: ``tcgen05.mma.kind::f16`` GEMM; an ``Xq``
+      activation is fake-quantised by one bandwidth-bound kernel first, a ``Wq`` weight is expanded from
+      its codes inside the GEMM's operand loader (or, for block layouts that loader does not read,
+      dequantised first);
+    * anything else raises ``NotImplementedError`` as the reference's ``fused`` does -- nothing falls back to
+      a library GEMM silently.
+    """
+    w_shape = tuple(w_tensor_meta.shape) if kind.w_quantised else tuple(w.shape)
+    K = x.shape[-1]
+    w_blocks_along_k = kind.w_quantised and len(w_shape) == 2 and w_tensor_meta.block_dim in (1, -1) and _gemm.supported(w_tensor_meta.meta)
+    if (kind.x_quantised and w_blocks_along_k and x.is_cuda and x.dtype in _lib.DTYPE_ID and _gemm.supported(x_meta)
+            and K % 32 == 0 and x.numel() > 0):
+        wq = _gemm.packed_weight(w_scales, w_elements, w_shape, w_tensor_meta.meta)
+        return _gemm.mx_linear(x, x_meta, wq, bias)
+    reason = tc_linear.why_not(x, K)
+    if reason is not None:
+        raise NotImplementedError(f"backend='fused' is not implemented for this call: {reason}; use backend='separate'")
+    if kind.x_quantised:
+        x = quantize_dequantize(x, block_dim=-1, mxfp_meta=x_meta)       # same bits as extract + compose
+    if not kind.w_quantised:
+        return tc_linear.dense_linear(x, w, bias)
+    if getattr(torch, w_tensor_meta.dtype) != x.dtype:
+        raise RuntimeError(f"the weight dequantises to {w_tensor_meta.dtype}, the input is {x.dtype}")
+    if w_blocks_along_k and K % 32 == 0:
+        return tc_linear.mxfp_weight_linear(x, w_scales, w_elements, w_shape, w_tensor_meta.meta, bias)
+    return tc_linear.dense_linear(x, compose_mxfp_tensor(w_scales, w_elements, w_tensor_meta).contiguous(), bias)
 
 
 def mxfp_linear(
@@ -49,12 +85,8 @@ def mxfp_linear(
         bias = compose_mxfp_tensor(b_scales, b_elements, b_tensor_meta) if b is not None else None
     else:
         bias = b
-    if (backend == "fused" and kind.x_quantised and kind.w_quantised and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16, torch.float32)
-            and _gemm.supported(x_meta) and _gemm.supported(w_tensor_meta.meta) and w_tensor_meta.block_dim in (1, -1)
-            and len(w_tensor_meta.shape) == 2 and x.shape[-1] % 32 == 0 and x.numel() > 0):
-        # both operands stay quantised: block-scaled tensor-core GEMM, fp32 accumulation
-        wq = _gemm.packed_weight(w_scales, w_elements, w_tensor_meta.shape, w_tensor_meta.meta)
-        return _gemm.mx_linear(x, x_meta, wq, bias)
+    if backend == "fused":
+        return _fused_linear(x, x_meta, w, w_scales, w_elements, w_tensor_meta, bias, kind)
     if kind.x_quantised:
         x = quantize_dequantize(x, block_dim=-1, mxfp_meta=x_meta)       # same bits as extract + compose
     weight = compose_mxfp_tensor(w_scales, w_elements, w_tensor_meta) if kind.w_quantised else w

@@ -20,7 +20,8 @@ from . import kernels
 from .meta import MXFPMeta
 
 _STATUS: dict[torch.device, Tensor] = {}
-_STATUS_TEXT = {1: "TMA producer wait ran out", 2: "MMA issuer wait ran out", 3: "epilogue wait ran out"}
+_STATUS_TEXT = {1: "TMA producer wait ran out", 2: "MMA issuer wait ran out", 3: "epilogue wait ran out",
+                4: "copy-out (gather) wait ran out", 5: "operand dequantiser wait ran out"}
 
 
 @dataclass
@@ -31,36 +32,59 @@ class PackedOperand:
     rows: int
     K: int
     operand: int         # 0: packed as the left operand (A), 1: as the right operand (B)
+    tile_rows: int = 0   # right operand: CTA tile width its scale factors are tiled for (0 = default 224)
 
 
 def supported(meta: MXFPMeta | None) -> bool:
-    """Formats the tensor-core path takes: 32-element blocks, is_finite element formats."""
+    """Formats the tensor-core path takes: 32-element blocks, is_finite element formats (any rounding
+    mode: the mode only matters where an activation is quantised, see :func:`pack_activation`)."""
     return meta is not None and meta.block_size == 32 and meta.element_is_finite and meta.scale_exp_bits == 8
 
 
+def one_pass_ok(meta: MXFPMeta) -> bool:
+    """Activation formats the one-kernel quantise + pack routes cover: MXFP8 elements, round to nearest."""
+    return supported(meta) and meta.element_exp_bits >= 4 and meta.round_mode == "rn"
+
+
 def status_word(device: torch.device) -> Tensor:
-    """Device int32 the kernel writes a non-zero code into if one of its bounded waits runs out."""
+    """The int32 word a GEMM kernel on ``device`` writes a non-zero code into when one of its bounded
+    waits runs out.  It lives in pinned host memory (which the GPU addresses directly), so the host can
+    look at it without synchronising: every GEMM entry of this module does so before it launches and
+    raises :class:`MXQError` for a failure left by an earlier launch."""
     device = torch.device(device)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
     if device not in _STATUS:
-        _STATUS[device] = torch.zeros(1, dtype=torch.int32, device=device)
+        _STATUS[device] = torch.zeros(1, dtype=torch.int32).pin_memory()
     return _STATUS[device]
 
 
-def check_status(device: torch.device) -> None:
-    """Synchronising check of the status word (used by tests and debugging)."""
-    code = int(status_word(device).item())
+def _raise_if_failed(device: torch.device) -> None:
+    """Non-blocking look at the status word: reports (and clears) what a finished launch left there."""
+    word = status_word(device)
+    code = int(word[0])
     if code != 0:
-        status_word(device).zero_()
-        raise _lib.MXQError(f"mx_gemm kernel reported: {_STATUS_TEXT.get(code, code)}")
+        word.zero_()
+        raise _lib.MXQError(f"an earlier tensor-core GEMM on {device} gave up: {_STATUS_TEXT.get(code, code)}; "
+                            "its output is undefined")
+
+
+def check_status(device: torch.device) -> None:
+    """Wait for the device, then raise if any GEMM launched so far reported a wait that ran out."""
+    torch.cuda.synchronize(device)
+    _raise_if_failed(device)
 
 
 OPERAND_A, OPERAND_B = 0, 1
 
 
-def pack_codes(scales: Tensor | None, elements: Tensor, rows: int, K: int, exp_bits: int, frac_bits: int, operand: int) -> PackedOperand:
+def pack_codes(scales: Tensor | None, elements: Tensor, rows: int, K: int, exp_bits: int, frac_bits: int, operand: int,
+               tile_rows: int | None = None) -> PackedOperand:
     """Element codes (one per byte, sign at bit ``exp_bits + frac_bits``) of a ``[rows, K]`` tensor and the
     E8M0 scales of its 32-element blocks along K (``None``: every scale is 2^0, i.e. per-tensor minifloat
-    codes) -> ``PackedOperand`` for the left (``OPERAND_A``) or right (``OPERAND_B``) side of the GEMM."""
+    codes) -> ``PackedOperand`` for the left (``OPERAND_A``) or right (``OPERAND_B``) side of the GEMM.
+    ``tile_rows`` (right operand only) is the CTA tile width; by default the one with the least padded
+    work for ``rows`` output features."""
     _lib.require_cuda(elements, "pack_operand")
     assert elements.dtype == torch.uint8 and K % 32 == 0 and elements.numel() == rows * K
     assert scales is None or (scales.dtype == torch.uint8 and scales.numel() == rows * K // 32)
@@ -68,46 +92,60 @@ def pack_codes(scales: Tensor | None, elements: Tensor, rows: int, K: int, exp_b
     scales = None if scales is None else scales.contiguous()
     L = _lib.load()
     dev = elements.device
+    if operand == OPERAND_A:
+        tile_rows = 0
+    elif tile_rows is None:
+        tile_rows = L.mxq_mx_best_tile_rows(rows)
     codes = torch.empty((rows, K), dtype=torch.uint8, device=dev)
-    sf = torch.empty((L.mxq_mx_sf_bytes(rows, K, operand),), dtype=torch.uint8, device=dev)
+    sf = torch.empty((L.mxq_mx_sf_bytes(rows, K, operand, tile_rows),), dtype=torch.uint8, device=dev)
     fmt = ctypes.c_int(0)
     with torch.cuda.device(dev):
         rc = L.mxq_mx_pack_operand(None if scales is None else scales.data_ptr(), elements.data_ptr(), rows, K, exp_bits, frac_bits,
-                                   operand, codes.data_ptr(), sf.data_ptr(), ctypes.addressof(fmt), _lib.stream_ptr(dev))
+                                   operand, tile_rows, codes.data_ptr(), sf.data_ptr(), ctypes.addressof(fmt), _lib.stream_ptr(dev))
     _lib.check(rc, "mxq_mx_pack_operand")
-    return PackedOperand(codes, sf, fmt.value, rows, K, operand)
+    return PackedOperand(codes, sf, fmt.value, rows, K, operand, tile_rows)
 
 
-def pack_operand(scales: Tensor, elements: Tensor, rows: int, K: int, meta: MXFPMeta, operand: int) -> PackedOperand:
+def pack_operand(scales: Tensor, elements: Tensor, rows: int, K: int, meta: MXFPMeta, operand: int,
+                 tile_rows: int | None = None) -> PackedOperand:
     """Reference ``(scales, elements)`` of a ``[rows, K]`` tensor blocked along K -> ``PackedOperand``
     laid out for the left (``OPERAND_A``) or right (``OPERAND_B``) side of the GEMM."""
     assert supported(meta)
-    return pack_codes(scales, elements, rows, K, meta.element_exp_bits, meta.element_frac_bits, operand)
+    return pack_codes(scales, elements, rows, K, meta.element_exp_bits, meta.element_frac_bits, operand, tile_rows)
 
 
-def quantize_pack(x: Tensor, meta: MXFPMeta, operand: int = OPERAND_A) -> PackedOperand:
+def quantize_pack(x: Tensor, meta: MXFPMeta, operand: int = OPERAND_A, tile_rows: int | None = None) -> PackedOperand:
     """Quantise a ``[..., K]`` tensor along its last dim and pack it."""
     K = x.shape[-1]
     rows = x.numel() // K
     scales, elements = kernels.extract_mxfp_components(x.reshape(-1), meta)
-    return pack_operand(scales, elements, rows, K, meta, operand)
+    return pack_operand(scales, elements, rows, K, meta, operand, tile_rows)
 
 
 def quantize_pack_fused(x: Tensor, meta: MXFPMeta) -> PackedOperand:
-    """One-kernel version of :func:`quantize_pack` for a left operand with MXFP8 elements."""
+    """One-kernel version of :func:`quantize_pack` for a left operand with MXFP8 elements (round to nearest)."""
     _lib.require_cuda(x, "quantize_pack_fused")
+    assert one_pass_ok(meta), "one-pass quantise + pack covers MXFP8 elements with round_mode 'rn' only"
     K = x.shape[-1]
     rows = x.numel() // K
     x2 = x.reshape(rows, K).contiguous()
     L = _lib.load()
     codes = torch.empty((rows, K), dtype=torch.uint8, device=x.device)
-    sf = torch.empty((L.mxq_mx_sf_bytes(rows, K, OPERAND_A),), dtype=torch.uint8, device=x.device)
+    sf = torch.empty((L.mxq_mx_sf_bytes(rows, K, OPERAND_A, 0),), dtype=torch.uint8, device=x.device)
     fmt = ctypes.c_int(0)
     with torch.cuda.device(x.device):
         rc = L.mxq_mx_quantize_pack(x2.data_ptr(), _lib.DTYPE_ID[x2.dtype], rows, K, meta.element_exp_bits, meta.element_frac_bits,
                                     codes.data_ptr(), sf.data_ptr(), ctypes.addressof(fmt), _lib.stream_ptr(x.device))
     _lib.check(rc, "mxq_mx_quantize_pack")
     return PackedOperand(codes, sf, fmt.value, rows, K, OPERAND_A)
+
+
+def pack_activation(x: Tensor, meta: MXFPMeta) -> PackedOperand:
+    """Quantise a ``[..., K]`` activation along its last dim, as ``meta`` says (element format and rounding
+    mode), into the left operand of the GEMM: one kernel for MXFP8 / round to nearest, extract + pack
+    otherwise.  The result can be fed to several layers that share the activation (q / k / v, gate / up)
+    through ``MXFPLinearPTQ.forward_packed`` so that it is quantised once."""
+    return quantize_pack_fused(x, meta) if one_pass_ok(meta) else quantize_pack(x, meta)
 
 
 def minifloat_quantize_pack(x: Tensor, exp_bits: int, frac_bits: int, round_mode: str) -> PackedOperand | None:
@@ -120,7 +158,7 @@ def minifloat_quantize_pack(x: Tensor, exp_bits: int, frac_bits: int, round_mode
     x2 = x.reshape(rows, K).contiguous()
     L = _lib.load()
     codes = torch.empty((rows, K), dtype=torch.uint8, device=x.device)
-    sf = torch.empty((L.mxq_mx_sf_bytes(rows, K, OPERAND_A),), dtype=torch.uint8, device=x.device)
+    sf = torch.empty((L.mxq_mx_sf_bytes(rows, K, OPERAND_A, 0),), dtype=torch.uint8, device=x.device)
     fmt = ctypes.c_int(0)
     with torch.cuda.device(x.device):
         rc = L.mxq_minifloat_quantize_pack(x2.data_ptr(), _lib.DTYPE_ID[x2.dtype], rows, K, exp_bits, frac_bits, _lib.ROUND_ID[round_mode],
@@ -148,6 +186,7 @@ def mx_gemm(a: PackedOperand, b: PackedOperand, out_dtype: torch.dtype, bias: Te
     """``a [M,K] @ b[N,K]^T (+ bias)`` on the tensor cores; returns ``[M, N]`` of ``out_dtype``."""
     assert a.K == b.K and out_dtype in _lib.DTYPE_ID and a.operand == OPERAND_A and b.operand == OPERAND_B
     dev = a.codes.device
+    _raise_if_failed(dev)
     if out is None:
         out = torch.empty((a.rows, b.rows), dtype=out_dtype, device=dev)
     if bias is not None:
@@ -155,7 +194,7 @@ def mx_gemm(a: PackedOperand, b: PackedOperand, out_dtype: torch.dtype, bias: Te
         assert bias.numel() == b.rows
     with torch.cuda.device(dev):
         rc = _lib.load().mxq_mx_gemm(a.codes.data_ptr(), a.sf.data_ptr(), a.hw_format, b.codes.data_ptr(), b.sf.data_ptr(),
-                                     b.hw_format, out.data_ptr(), _lib.DTYPE_ID[out_dtype],
+                                     b.hw_format, b.tile_rows, out.data_ptr(), _lib.DTYPE_ID[out_dtype],
                                      None if bias is None else bias.data_ptr(), a.rows, b.rows, a.K,
                                      status_word(dev).data_ptr(), _lib.stream_ptr(dev))
     _lib.check(rc, "mxq_mx_gemm")
@@ -172,39 +211,49 @@ def mx_gemm_gather(a: PackedOperand, b: PackedOperand, out_ptrs: list[int], self
     consumers on the other ranks."""
     assert a.K == b.K and out_dtype in _lib.DTYPE_ID and a.operand == OPERAND_A and b.operand == OPERAND_B
     dev = a.codes.device
+    _raise_if_failed(dev)
     if bias is not None:
         bias = bias.to(out_dtype).contiguous()
         assert bias.numel() == b.rows
     ptrs = (ctypes.c_void_p * len(out_ptrs))(*out_ptrs)
     with torch.cuda.device(dev):
         rc = _lib.load().mxq_mx_gemm_gather(a.codes.data_ptr(), a.sf.data_ptr(), a.hw_format, b.codes.data_ptr(), b.sf.data_ptr(),
-                                            b.hw_format, ctypes.addressof(ptrs), len(out_ptrs), self_index, ld, col_offset,
+                                            b.hw_format, b.tile_rows, ctypes.addressof(ptrs), len(out_ptrs), self_index, ld, col_offset,
                                             _lib.DTYPE_ID[out_dtype], None if bias is None else bias.data_ptr(),
                                             a.rows, b.rows, a.K, status_word(dev).data_ptr(), _lib.stream_ptr(dev))
     _lib.check(rc, "mxq_mx_gemm_gather")
 
 
-_SCRATCH: dict[torch.device, Tensor] = {}
+_SCRATCH: dict[tuple[torch.device, int], Tensor] = {}
 
 
 def _scratch(device: torch.device, nbytes: int) -> Tensor:
-    """Per-device scratch buffer for the quantised activation, grown on demand and re-used."""
-    buf = _SCRATCH.get(device)
+    """Scratch buffer for the quantised activation, one per (device, stream) so that layers running on
+    different streams never share it; grown on demand and re-used.  A replaced buffer goes back to
+    PyTorch's caching allocator, which keeps it tied to the stream it was allocated on."""
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    buf = _SCRATCH.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty((nbytes,), dtype=torch.uint8, device=device)
-        _SCRATCH[device] = buf
+        _SCRATCH[key] = buf
     return buf
 
 
 def mx_linear(x: Tensor, x_meta: MXFPMeta, w: PackedOperand, bias: Tensor | None = None, out: Tensor | None = None) -> Tensor:
-    """``quantise(x) @ w^T (+ bias)`` through the single C entry point ``mxq_mx_linear``: activation
-    quantisation, packing and the tensor-core GEMM are enqueued back to back on the current stream."""
+    """``quantise(x) @ w^T (+ bias)``.  Round-to-nearest activations go through the single C entry point
+    ``mxq_mx_linear`` (quantisation, packing and the tensor-core GEMM enqueued back to back on the
+    current stream); the other rounding modes are quantised by the extract kernel, which implements
+    them, packed, and multiplied by the same GEMM."""
     _lib.require_cuda(x, "mx_linear")
     assert supported(x_meta) and w.operand == OPERAND_B and x.shape[-1] == w.K
     if x.dtype not in _lib.DTYPE_ID:
         x = x.float()
     x2 = x.reshape(-1, w.K).contiguous()
     M, dev = x2.shape[0], x2.device
+    if x_meta.round_mode != "rn":
+        y = mx_gemm(quantize_pack(x2, x_meta), w, x2.dtype, bias=bias, out=out)
+        return y.reshape(*x.shape[:-1], w.rows)
+    _raise_if_failed(dev)
     L = _lib.load()
     if out is None:
         out = torch.empty((M, w.rows), dtype=x2.dtype, device=dev)
@@ -214,7 +263,7 @@ def mx_linear(x: Tensor, x_meta: MXFPMeta, w: PackedOperand, bias: Tensor | None
     scratch = _scratch(dev, nbytes)
     with torch.cuda.device(dev):
         rc = L.mxq_mx_linear(x2.data_ptr(), _lib.DTYPE_ID[x2.dtype], M, w.K, x_meta.element_exp_bits, x_meta.element_frac_bits,
-                             w.codes.data_ptr(), w.sf.data_ptr(), w.hw_format, w.rows, out.data_ptr(), _lib.DTYPE_ID[out.dtype],
+                             w.codes.data_ptr(), w.sf.data_ptr(), w.hw_format, w.tile_rows, w.rows, out.data_ptr(), _lib.DTYPE_ID[out.dtype],
                              None if bias is None else bias.data_ptr(), scratch.data_ptr(), scratch.numel(),
                              status_word(dev).data_ptr(), _lib.stream_ptr(dev))
     _lib.check(rc, "mxq_mx_linear")

@@ -91,6 +91,29 @@ class MXFPLinearPTQ(PTQLinearBase):
             layer_type=self.layer_type, backend=self.backend,
         )
 
+    def pack_input(self, input: Tensor):
+        """Quantise ``input`` as this layer's ``forward`` would (``x_mxfp_meta``) into the tensor-core operand
+        form.  Layers that read the same activation (q / k / v, gate / up) can share the result through
+        :meth:`forward_packed`, so the activation is quantised once instead of once per layer."""
+        from . import gemm as _gemm
+
+        assert "Xq" in self.layer_type and "Wq" in self.layer_type and _gemm.supported(self.x_mxfp_meta), \
+            "pack_input needs a layer with quantised activation and weight (32-element blocks)"
+        return _gemm.pack_activation(input.reshape(-1, self.in_features), self.x_mxfp_meta)
+
+    @torch.no_grad()
+    def forward_packed(self, packed, out_dtype: torch.dtype = torch.bfloat16, lead_shape: tuple[int, ...] | None = None) -> Tensor:
+        """``forward`` on an activation already quantised by :meth:`pack_input` (of this or of another layer
+        with the same ``x_mxfp_meta`` and ``in_features``); returns ``[rows, out_features]`` of ``out_dtype``,
+        reshaped to ``lead_shape + (out_features,)`` when given."""
+        from . import gemm as _gemm
+
+        assert packed.K == self.in_features and self.w_scales is not None
+        wq = _gemm.packed_weight(self.w_scales, self.w_elements, tuple(self.w_tensor_meta.shape), self.w_tensor_meta.meta)
+        # a layer with a quantised bias holds no plain one, and forward() then adds none (the reference's rule)
+        y = _gemm.mx_gemm(packed, wq, out_dtype, bias=self.bias)
+        return y if lead_shape is None else y.reshape(*lead_shape, self.out_features)
+
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, "
                 f"layer_type={self.layer_type}, w_mxfp_meta={self.w_mxfp_meta}, x_mxfp_meta={self.x_mxfp_meta}, "

@@ -163,7 +163,7 @@ class GatherFusedMXFPLinear:
         x2 = x.reshape(-1, self.K)
         M = x2.shape[0]
         assert M <= self.max_rows, "more rows than the output buffers were sized for"
-        a = g.quantize_pack_fused(x2, self.x_meta) if self.x_meta.element_exp_bits >= 4 else g.quantize_pack(x2, self.x_meta)
+        a = g.pack_activation(x2, self.x_meta)
         if self.n1 > self.n0:
             g.mx_gemm_gather(a, self.weight, self.ptrs[self._turn], self.rank, self.N, self.n0, self.dtype, self.bias)
         dist.all_reduce(self._fence, group=self.group)        # every rank's tiles are in every buffer after this

@@ -1,5 +1,6 @@
-"""Two-GPU checks of the gather-fused column-parallel linear.  They run only where two GPUs are
-visible (child processes, one per GPU, NCCL over 127.0.0.1) and are skipped elsewhere."""
+"""Multi-GPU checks of the gather-fused column-parallel linear at 2, 4 and 8 ranks (child processes, one per
+GPU, NCCL over 127.0.0.1; each size is skipped where fewer GPUs are visible), and of one process that drives
+two GPUs through the same library."""
 
 from __future__ import annotations
 
@@ -29,7 +30,7 @@ torch.cuda.set_device(rank)
 dev = torch.device("cuda", rank)
 dist.init_process_group("nccl", device_id=dev)
 g = torch.Generator().manual_seed(3)
-K, N = 512, 1792 + 448
+K, N = 512, 1792 + 448 + 64 * world
 fc = torch.nn.Linear(K, N, bias=True, dtype=torch.bfloat16)
 with torch.no_grad():
     fc.weight.copy_((0.05 * torch.randn(N, K, generator=g)).bfloat16())
@@ -59,14 +60,16 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_gather_fused_linear_matches_single_gpu(tmp_path):
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_gather_fused_linear_matches_single_gpu(tmp_path, world):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     script = tmp_path / "child.py"
     script.write_text(CHILD)
     port = str(_free_port())
     procs = []
-    for rank in range(2):
-        env = dict(os.environ, RANK=str(rank), WORLD_SIZE="2", LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=port,
+    for rank in range(world):
+        env = dict(os.environ, RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=port,
                    MXQ_ROOT=str(ROOT), NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
         procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
     outs = []
@@ -80,3 +83,26 @@ def test_gather_fused_linear_matches_single_gpu(tmp_path):
         outs.append(out)
     for rank, (p, out) in enumerate(zip(procs, outs)):
         assert p.returncode == 0 and f"rank {rank} ok" in out, out[-3000:]
+
+
+def test_one_process_two_devices(lib):
+    """The per-device set-up of the GEMM kernels (shared-memory limit, SM count, scratch, status word) is
+    kept per device: the same process runs a fused linear on cuda:0 and then on cuda:1."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from mase_triton_b200 import tc_linear
+    from mase_triton_b200.mxfp import gemm as G
+    from mase_triton_b200.mxfp.layers import MXFPLinearPTQ
+    from mase_triton_b200.mxfp.meta import MXFP8_E4M3_fn
+
+    torch.manual_seed(0)
+    fc = torch.nn.Linear(512, 768, bias=True, dtype=torch.bfloat16)
+    x = torch.randn(300, 512).bfloat16()
+    outs, dense = [], []
+    for dev in ("cuda:0", "cuda:1"):
+        layer = MXFPLinearPTQ.from_linear(fc.to(dev), MXFP8_E4M3_fn, MXFP8_E4M3_fn, None, "XqWqB", "fused")
+        outs.append(layer(x.to(dev)).cpu())
+        dense.append(tc_linear.dense_linear(x.to(dev), fc.weight.detach().to(dev), fc.bias.detach().to(dev)).cpu())
+        G.check_status(torch.device(dev))
+    assert torch.equal(outs[0], outs[1]) and torch.equal(dense[0], dense[1])
+    assert outs[0].float().abs().max() > 0

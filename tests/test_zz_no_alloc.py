@@ -21,12 +21,12 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def _linear(L, fn_name, x, w: G.PackedOperand, bias, extra_scratch=None):
+def _linear(L, fn_name, x, w: G.PackedOperand, bias, extra_scratch=None, x_meta=MXFP8_E4M3_fn):
     M, K = x.shape
     out = torch.empty((M, w.rows), dtype=x.dtype, device=x.device)
     status = torch.zeros(1, dtype=torch.int32, device=x.device)
-    head = [x.data_ptr(), _lib.DTYPE_ID[x.dtype], M, K, MXFP8_E4M3_fn.element_exp_bits, MXFP8_E4M3_fn.element_frac_bits,
-            w.codes.data_ptr(), w.sf.data_ptr(), w.hw_format, w.rows, out.data_ptr(), _lib.DTYPE_ID[out.dtype],
+    head = [x.data_ptr(), _lib.DTYPE_ID[x.dtype], M, K, x_meta.element_exp_bits, x_meta.element_frac_bits,
+            w.codes.data_ptr(), w.sf.data_ptr(), w.hw_format, w.tile_rows, w.rows, out.data_ptr(), _lib.DTYPE_ID[out.dtype],
             None if bias is None else bias.data_ptr()]
     tail = [status.data_ptr(), torch.cuda.current_stream(x.device).cuda_stream]
     if extra_scratch is not None:
@@ -44,13 +44,16 @@ def test_static_scratch_linear_matches_caller_scratch_linear(lib):
     w = (0.02 * torch.randn(N, K, device=DEV)).to(torch.bfloat16)
     wq = G.quantize_pack(w, OCP_MXFP6_E3M2, G.OPERAND_B)
     bias = torch.randn(N, device=DEV).to(torch.bfloat16)
-    # two calls in a row with different shapes and data: the second must not see the first one's leftovers
-    for M, use_bias in ((512, True), (200, False)):
+    # calls in a row with different shapes and data: a later one must not see an earlier one's leftovers.
+    # MXFP8 activations are quantised and packed in one kernel; the 6-bit activation takes the other route
+    # inside the library (extract into the scratch, then an in-place re-encode), which uses more of the array.
+    for M, use_bias, x_meta in ((512, True, MXFP8_E4M3_fn), (200, False, MXFP8_E4M3_fn), (384, True, OCP_MXFP6_E3M2),
+                                (130, False, MXFP8_E4M3_fn)):
         x = (torch.randn(M, K, device=DEV) * 2).to(torch.bfloat16)
         scratch = torch.empty(L.mxq_mx_linear_scratch_bytes(M, K), dtype=torch.uint8, device=DEV)
         b = bias if use_bias else None
-        rc_ref, y_ref, st_ref = _linear(L, "mxq_mx_linear", x, wq, b, extra_scratch=scratch)
-        rc_new, y_new, st_new = _linear(L, "mxq_mx_linear_static", x, wq, b)
+        rc_ref, y_ref, st_ref = _linear(L, "mxq_mx_linear", x, wq, b, extra_scratch=scratch, x_meta=x_meta)
+        rc_new, y_new, st_new = _linear(L, "mxq_mx_linear_static", x, wq, b, x_meta=x_meta)
         assert (rc_ref, st_ref) == (0, 0) and (rc_new, st_new) == (0, 0)
         assert torch.equal(y_new.view(torch.int16), y_ref.view(torch.int16)), f"M={M}: outputs differ"
         assert y_new.float().abs().max() > 0
