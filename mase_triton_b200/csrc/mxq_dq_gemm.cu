@@ -76,8 +76,9 @@ struct DqConsts {
     uint32_t sign_pos;      // eb + fb
     uint32_t up;            // 23 - fb: magnitude field -> top of an fp32 mantissa / bottom of its exponent
     float rebias;           // 2^(127 - bias)
-    uint32_t top_exp;       // all-ones exponent field (Inf / NaN codes when !fin), else 0xFFFFFFFF (never matches)
-    uint32_t frac_mask;
+    uint32_t top_exp;       // exponent field that decodes to Inf / NaN: all ones when !fin, 255 for 8 exponent bits (the value
+                            // 2^128 overflows fp32 as it does in the reference's fp32 arithmetic), else 0xFFFFFFFF (never matches)
+    uint32_t nan_mask;      // fraction bits that turn the Inf into a NaN (!fin only)
     // packed-bf16 route (MX codes -> bf16): field shifts inside a half word holding code << 8
     uint32_t mag_shift2, mag_mask2, sign_shift2, bias_;
 };
@@ -89,8 +90,8 @@ __device__ __forceinline__ DqConsts dq_consts(int eb, int fb, int fin) {
     c.sign_pos = (uint32_t)(eb + fb);
     c.up = (uint32_t)(23 - fb);
     c.rebias = __uint_as_float((uint32_t)(254 - bias) << 23);
-    c.top_exp = fin ? 0xFFFFFFFFu : ((1u << eb) - 1u);
-    c.frac_mask = (1u << fb) - 1u;
+    c.top_exp = !fin ? ((1u << eb) - 1u) : (eb == 8 ? 255u : 0xFFFFFFFFu);
+    c.nan_mask = !fin ? ((1u << fb) - 1u) : 0u;
     c.mag_shift2 = (uint32_t)(1 + fb);
     c.mag_mask2 = (c.mag_mask << (7 - fb)) * 0x10001u;
     c.sign_shift2 = (uint32_t)(7 - eb - fb);
@@ -102,7 +103,7 @@ __device__ __forceinline__ DqConsts dq_consts(int eb, int fb, int fin) {
 __device__ __forceinline__ float decode_scaled(uint32_t code, const DqConsts& c, float scale) {
     const uint32_t mag = code & c.mag_mask;
     float v = __fmul_rn(__uint_as_float(mag << c.up), c.rebias);      // exact: subnormal codes are fp32 subnormals here
-    if ((mag >> (23 - c.up)) == c.top_exp) v = (mag & c.frac_mask) ? __uint_as_float(0x7FC00000u) : __uint_as_float(0x7F800000u);
+    if ((mag >> (23 - c.up)) == c.top_exp) v = (mag & c.nan_mask) ? __uint_as_float(0x7FC00000u) : __uint_as_float(0x7F800000u);
     v = __fmul_rn(v, scale);
     return __uint_as_float(__float_as_uint(v) | ((code >> c.sign_pos) << 31));
 }
