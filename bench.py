@@ -214,6 +214,9 @@ def time_steps(fn, steps: int, stream=None) -> list[float]:
     return [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
 
 
+GRAPH_FALLBACKS: list[str] = []      # captures that failed and were timed launch by launch instead (reported in the line)
+
+
 def graph_time(fn, reps: int, rounds: int = 5) -> float:
     """Median device time (ms) of one call of `fn`, measured by replaying a CUDA graph of `reps`
     back-to-back calls: no host launch overhead between kernels, so short kernels are timed honestly."""
@@ -240,7 +243,8 @@ def graph_time(fn, reps: int, rounds: int = 5) -> float:
             torch.cuda.synchronize()
             ts.append(e0.elapsed_time(e1) / reps)
         return statistics.median(ts)
-    except Exception:
+    except Exception as exc:      # noqa: BLE001
+        GRAPH_FALLBACKS.append(f"{type(exc).__name__}: {exc}"[:200])
         torch.cuda.synchronize()
         return statistics.median(time_steps(fn, reps))
 
@@ -422,6 +426,7 @@ def extras_single_gpu(dev, steps: int, warmup: int, peak: float) -> dict:
     t_mf = graph_time(lambda: mf_f(xc), reps)
     t_ms = graph_time(lambda: mf_s(xc), max(3, reps // 2))
     G.check_status(dev)
+    out["graph_capture_fallbacks"] = list(GRAPH_FALLBACKS)
     out["cfg4_shape_minifloat_linear_e4m3"] = {"fused_TFLOPs": round(flops / t_mf / 1e9, 1), "separate_TFLOPs": round(flops / t_ms / 1e9, 1),
                                                "ms": {"fused": round(t_mf, 4), "separate": round(t_ms, 4)}}
     return out

@@ -18,9 +18,11 @@
 //   warp 0      TMA producer: X tile (and a raw W tile) into a 128-byte-swizzled shared-memory ring;
 //   warp 1      issues tcgen05.mma.kind::f16 (M=128, N=256, K=16), fp32 accumulators in tensor
 //               memory (two 128 x 256 blocks = all 512 columns);
-//   warps 2-5   epilogue: tcgen05.ld, bias, convert, 16-byte stores;
-//   warps 6-13  dequantisers: read code bytes and scales with plain loads three ring stages ahead
-//               (kept in registers), expand them to bf16 / fp16 exactly as the reference's compose
+//   warps 2-5   epilogue: tcgen05.ld, bias, convert, staging in shared memory, TMA store (asynchronous:
+//               the accumulator is handed back after the last tcgen05.ld, not after the global stores);
+//   warps 6-13  dequantisers: each thread owns 16 consecutive K elements of four rows of the W tile; it reads
+//               their code bytes (one 16-byte load per row) and scales three ring stages ahead (kept
+//               in registers), expands them to bf16 / fp16 exactly as the reference's compose
 //               does (decode * 2^(scale-127), rounded once to the operand dtype), write the
 //               swizzled tile with 16-byte shared stores, make them visible to the tensor cores
 //               (fence.proxy.async) and arrive on the stage's mbarrier next to the TMA bytes.
@@ -42,7 +44,9 @@ constexpr int DQ_WARPS = 8;
 constexpr int DQ_THREADS = DQ_WARPS * 32;
 constexpr int THREADS = 192 + DQ_THREADS;
 constexpr int PF = 3;                            // ring stages of codes a dequantiser thread holds in registers
-constexpr int ROWS_PER_THREAD = BN * 8 / DQ_THREADS;   // 16-byte output chunks (8 elements) per thread per stage: 8
+constexpr int SEGS = BK / 16;                    // a dequantiser thread expands 16 consecutive K elements of a row: 4 threads per row
+constexpr int ROWS_PER_PASS = DQ_THREADS / SEGS; // 64 rows of the W tile per pass over the threads
+constexpr int ROWS_PER_THREAD = BN / ROWS_PER_PASS;    // 4 rows (64 elements) per thread per stage
 
 enum : int { SRC_RAW = 0, SRC_MX = 1, SRC_MF = 2 };
 
@@ -57,7 +61,8 @@ template <int MH> struct Cfg {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;                      // multiple of 1024
     static constexpr int STAGES = MH == 2 ? 3 : 4;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + slack to align the ring
+    static constexpr int STAGING = 4 * EPI_SLOT_BYTES;                         // staging slots of the four epilogue warps
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING + BAR_BYTES + 1024;  // + slack to align the ring
 };
 
 __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
@@ -116,7 +121,7 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 
 // SRC_MX: eight code bytes (two words) and their block's scale byte -> eight DT elements
 template <int DT>
-__device__ __forceinline__ uint4 dequant_mx8(uint2 w, uint32_t sbyte, const DqConsts& c) {
+__device__ __forceinline__ uint4 dequant_mx8(uint32_t w0, uint32_t w1, uint32_t sbyte, const DqConsts& c) {
     uint32_t o[4];
     if constexpr (DT == MXQ_BF16) {
         // Two elements per 32-bit word on the packed bf16 units.  A code shifted so that its exponent field
@@ -125,21 +130,29 @@ __device__ __forceinline__ uint4 dequant_mx8(uint2 w, uint32_t sbyte, const DqCo
         // 2^(scale-bias) restores the bias and applies the block scale, rounding once to bf16 exactly like
         // the reference's fp32 product followed by .to(bfloat16).  Scales too large for that factor to be a
         // finite bf16 (and 255 = Inf) take two multiplies.
-        const uint32_t words[2] = {w.x, w.y};
+        const uint32_t words[2] = {w0, w1};
         const bool one_step = sbyte <= 127u + c.bias_;
         const uint32_t f1 = one_step ? ((sbyte + 127u - c.bias_) << 7) * 0x10001u : ((254u - c.bias_) << 7) * 0x10001u;
-        const uint32_t f2 = (sbyte == 255u ? 0x7F80u : (sbyte == 0u ? 0x0040u : (sbyte << 7))) * 0x10001u;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const uint32_t t = __byte_perm(words[j >> 1], 0u, (j & 1) ? 0x3424u : 0x1404u);     // code << 8 in each half
-            const uint32_t v = ((t >> c.mag_shift2) & c.mag_mask2) | ((t << c.sign_shift2) & 0x80008000u);
-            __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&v), *reinterpret_cast<const __nv_bfloat162*>(&f1));
-            if (!one_step) r = __hmul2(r, *reinterpret_cast<const __nv_bfloat162*>(&f2));
+            const uint32_t mag = (t >> c.mag_shift2) & c.mag_mask2;
+            // sign: bit eb+fb of the code -> bit 15 of the half (already there for the 8-bit formats)
+            const uint32_t v = mag | ((c.sign_shift2 ? (t << c.sign_shift2) : t) & 0x80008000u);
+            const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&v), *reinterpret_cast<const __nv_bfloat162*>(&f1));
             o[j] = *reinterpret_cast<const uint32_t*>(&r);
+        }
+        if (!one_step) {
+            const uint32_t f2 = (sbyte == 255u ? 0x7F80u : (sbyte << 7)) * 0x10001u;           // 2^(scale-127); here scale > 127
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&o[j]), *reinterpret_cast<const __nv_bfloat162*>(&f2));
+                o[j] = *reinterpret_cast<const uint32_t*>(&r);
+            }
         }
     } else {
         const float scale = __uint_as_float(sbyte == 0u ? 0x00400000u : (sbyte << 23));     // 255 -> +Inf as exp2(128) in fp32
-        const uint32_t words[2] = {w.x, w.y};
+        const uint32_t words[2] = {w0, w1};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const uint32_t pair = words[j >> 1] >> (16 * (j & 1));
@@ -159,25 +172,28 @@ __device__ __forceinline__ uint4 dequant_mf8(uint4 w, const DqConsts& c) {
     return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
-// what a dequantiser thread keeps in registers for one ring stage: its 8 chunks of codes (+ scale bytes)
+// what a dequantiser thread keeps in registers for one ring stage: the codes of its 16 elements in each of its
+// 4 rows (+ the scale byte of the 32-element block they belong to)
 template <int SRC> struct Staged;
-template <> struct Staged<SRC_MX> { uint2 codes[ROWS_PER_THREAD]; uint32_t sb[ROWS_PER_THREAD]; };
-template <> struct Staged<SRC_MF> { uint4 codes[ROWS_PER_THREAD]; };
+template <> struct Staged<SRC_MX> { uint4 codes[ROWS_PER_THREAD]; uint32_t sb[ROWS_PER_THREAD]; };
+template <> struct Staged<SRC_MF> { uint4 lo[ROWS_PER_THREAD], hi[ROWS_PER_THREAD]; };
 template <> struct Staged<SRC_RAW> {};
 
 // DT: MXQ_BF16 / MXQ_F16 (operand and output dtype); MH: 128-row accumulators per CTA tile; SRC: where W comes from
 template <int DT, int MH, int SRC>
 __global__ void __launch_bounds__(THREADS, 1)
 dq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const WSource wsrc,
-               void* __restrict__ out, const void* __restrict__ bias, int M, int N, int K, uint32_t idesc, int* status) {
+               void* __restrict__ out, const void* __restrict__ bias, int M, int N, int K, uint32_t idesc, int* status,
+               const __grid_constant__ OutMaps omaps, int tma_out) {
     using C = Cfg<MH>;
     constexpr int STAGES = C::STAGES;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t ring = (raw + 1023u) & ~1023u;
     uint8_t* ring_ptr = smem_raw + (ring - raw);
-    const uint32_t bars = ring + STAGES * C::STAGE_BYTES;            // full[S], empty[S], accum_full, tmem_empty[2], drain, tmem slot
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ring_ptr + STAGES * C::STAGE_BYTES + 8 * (2 * STAGES + 4));
+    // ring | staging slots of the epilogue | barriers
+    const uint32_t bars = ring + STAGES * C::STAGE_BYTES + C::STAGING;   // full[S], empty[S], accum_full, tmem_empty[2], drain, tmem slot
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ring_ptr + STAGES * C::STAGE_BYTES + C::STAGING + 8 * (2 * STAGES + 4));
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
     const uint32_t accum_bar = bars + 8u * (2 * STAGES);
@@ -269,6 +285,8 @@ dq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else if (warp < 6) {
         // ---------------- epilogue ----------------
         const int q = warp & 3;
+        uint8_t* slots = ring_ptr + STAGES * C::STAGE_BYTES + (warp - 2) * EPI_SLOT_BYTES;
+        uint32_t turn = 0;
         bool ok = true;
         uint32_t tcount = 0;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
@@ -279,8 +297,13 @@ dq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (!ok) break;
 #pragma unroll
             for (int h = 0; h < MH; ++h) {
-                const int row = mt * C::BM + h * 128 + q * 32 + lane;
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + h * BN;
+                if (tma_out) {
+                    drain_accumulator_tma<DT>(taddr, BN / 32, false, 0, 1, bias, nt * BN, mt * C::BM + h * 128 + q * 32, M, N, slots, turn, omaps,
+                                              tmem_empty_bar(h), lane);
+                    continue;
+                }
+                const int row = mt * C::BM + h * 128 + q * 32 + lane;
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; ++c) {
                     uint32_t r[32];
@@ -295,12 +318,13 @@ dq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
             }
         }
+        if (tma_out && lane == 0) bulk_wait_all();         // the stores issued by this warp have been written
     } else {
         // ---------------- dequantisers: W codes -> swizzled operand tile ----------------
         if constexpr (SRC != SRC_RAW) {
             const int t = threadIdx.x - 192;             // 0 .. 255
-            const int chunk = t & 7;                     // 8-element chunk of the 64-element K step this thread owns
-            const int row_in = t >> 3;                   // rows row_in + 32 j of the tile, j = 0 .. 7
+            const int seg = t & (SEGS - 1);              // 16-element segment of the 64-element K step this thread owns
+            const int row_in = t / SEGS;                 // rows row_in + 64 j of the tile, j = 0 .. 3
             const DqConsts dc = dq_consts(wsrc.eb, wsrc.fb, wsrc.fin);
             const int my_tiles = (num_tiles > (int)blockIdx.x) ? (num_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
             const uint32_t total = (uint32_t)my_tiles * (uint32_t)KT;
@@ -313,16 +337,18 @@ dq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int kt = (int)(item % KT);
                 int mt, nt;
                 tile_coords(tile, MT, NT, mt, nt);
-                const int k0 = kt * BK + chunk * 8;
+                const int k0 = kt * BK + seg * 16;
 #pragma unroll
                 for (int j = 0; j < ROWS_PER_THREAD; ++j) {
-                    const int64_t n = (int64_t)nt * BN + row_in + 32 * j;
+                    const int64_t n = (int64_t)nt * BN + row_in + ROWS_PER_PASS * j;
                     const bool in = n < N && k0 < K;
                     if constexpr (SRC == SRC_MX) {
-                        b.codes[j] = in ? __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(wsrc.codes) + n * K + k0)) : make_uint2(0u, 0u);
+                        b.codes[j] = in ? __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(wsrc.codes) + n * K + k0)) : make_uint4(0u, 0u, 0u, 0u);
                         b.sb[j] = in ? (uint32_t)__ldg(wsrc.scales + n * kb_per_row + (k0 >> 5)) : 127u;
                     } else {
-                        b.codes[j] = in ? __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(wsrc.codes) + n * K + k0)) : make_uint4(0u, 0u, 0u, 0u);
+                        const uint4* p = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(wsrc.codes) + n * K + k0);
+                        b.lo[j] = in ? __ldg(p) : make_uint4(0u, 0u, 0u, 0u);
+                        b.hi[j] = in ? __ldg(p + 1) : make_uint4(0u, 0u, 0u, 0u);
                     }
                 }
             };
@@ -332,12 +358,19 @@ dq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 uint8_t* tile_b = ring_ptr + s * C::STAGE_BYTES + C::A_BYTES;
 #pragma unroll
                 for (int j = 0; j < ROWS_PER_THREAD; ++j) {
-                    const int r = row_in + 32 * j;
-                    uint4 v;
-                    if constexpr (SRC == SRC_MX) v = dequant_mx8<DT>(b.codes[j], b.sb[j], dc);
-                    else v = dequant_mf8<DT>(b.codes[j], dc);
+                    const int r = row_in + ROWS_PER_PASS * j;
+                    uint4 v0, v1;
+                    if constexpr (SRC == SRC_MX) {
+                        v0 = dequant_mx8<DT>(b.codes[j].x, b.codes[j].y, b.sb[j], dc);
+                        v1 = dequant_mx8<DT>(b.codes[j].z, b.codes[j].w, b.sb[j], dc);
+                    } else {
+                        v0 = dequant_mf8<DT>(b.lo[j], dc);
+                        v1 = dequant_mf8<DT>(b.hi[j], dc);
+                    }
                     // 128-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ (r % 8) of that row
-                    *reinterpret_cast<uint4*>(tile_b + r * 128 + ((chunk ^ (r & 7)) << 4)) = v;
+                    uint8_t* row = tile_b + r * 128;
+                    *reinterpret_cast<uint4*>(row + (((2 * seg) ^ (r & 7)) << 4)) = v0;
+                    *reinterpret_cast<uint4*>(row + (((2 * seg + 1) ^ (r & 7)) << 4)) = v1;
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy stores -> visible to the MMA's reads
                 __syncwarp();
@@ -397,7 +430,9 @@ static int launch(const void* x, const void* w_raw, const WSource& wsrc, void* o
     const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
     const int tiles = ((M + C::BM - 1) / C::BM) * ((N + BN - 1) / BN);
     const int grid = tiles < sm_count() ? tiles : sm_count();
-    dq_gemm_kernel<DT, MH, SRC><<<grid, THREADS, C::SMEM_BYTES, st>>>(ma, mb, wsrc, out, bias, M, N, K, idesc, status);
+    OutMaps omaps{};
+    const int tma_out = make_out_maps(&omaps, out, M, N, N, DT) ? 1 : 0;     // else: stores from registers
+    dq_gemm_kernel<DT, MH, SRC><<<grid, THREADS, C::SMEM_BYTES, st>>>(ma, mb, wsrc, out, bias, M, N, K, idesc, status, omaps, tma_out);
     return check_launch();
 }
 
@@ -437,7 +472,7 @@ extern "C" int mxq_mxfp_weight_linear(const void* x, int dtype, const uint8_t* w
     if (!x || !w_scales || !w_elements || !out || !dq::dims_ok(M, N, K)) return MXQ_EINVAL;
     if (exp_bits <= 0 || frac_bits <= 0 || exp_bits + frac_bits > 7) return MXQ_EINVAL;
     if (K % 32 != 0) return MXQ_ESIZE;                                  // 32-element blocks along K
-    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) % 16 != 0 || reinterpret_cast<uintptr_t>(w_elements) % 8 != 0) return MXQ_EINVAL;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) % 16 != 0 || reinterpret_cast<uintptr_t>(w_elements) % 16 != 0) return MXQ_EINVAL;
     const dq::WSource src{w_elements, w_scales, exp_bits, frac_bits, 1};
     return dq::launch_dt<dq::SRC_MX>(dtype, x, nullptr, src, out, bias, (int)M, (int)N, (int)K, status, (cudaStream_t)stream);
 }

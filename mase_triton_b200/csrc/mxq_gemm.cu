@@ -42,7 +42,9 @@ constexpr int SF_REGION = 2048;                  // A chunks (<= 1024) + B chunk
 constexpr int BAR_BYTES = 256;
 constexpr int TMEM_COLS = 512;
 constexpr int SFA_COL = 448, SFB_COL = 456;      // accumulators occupy columns [0, 448)
-constexpr int THREADS = 192;
+constexpr int THREADS = 192;                     // TMA producer, MMA issuer, four epilogue warps (epilogue that stores from registers)
+constexpr int EPI_TMA_WARPS = 8;                 // epilogue warps of the asynchronous (TMA-store) epilogue: two per TMEM lane quadrant
+constexpr int THREADS_TMA = 64 + EPI_TMA_WARPS * 32;
 
 template <int MH> struct Cfg {
     static constexpr int BM = 128 * MH;
@@ -51,6 +53,7 @@ template <int MH> struct Cfg {
     static constexpr int STAGES = MH == 2 ? 3 : 4;
     static constexpr int TX_FIXED = A_BYTES + MH * 512 + 1024;       // + bn * BK for the right operand's codes
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;   // + slack to align the ring
+    static constexpr int SMEM_BYTES_TMA = SMEM_BYTES + EPI_TMA_WARPS * EPI_SLOT_BYTES;   // + staging of the asynchronous epilogue
 };
 
 // Destinations of the gather-fused kernel: the [M, N] result goes, at column offset col0 of a
@@ -100,22 +103,32 @@ __device__ __forceinline__ void forward_tile(const OutSpec& outs, int fw, int la
     }
 }
 
-// OUT_DT: MXQ_F32 / MXQ_BF16 / MXQ_F16; MH: 128-row accumulators per CTA tile; MULTI: gather-fused epilogue;
+// OUT_DT: MXQ_F32 / MXQ_BF16 / MXQ_F16; MH: 128-row accumulators per CTA tile;
+// EPI: EPI_REGS = four warps convert and store from registers, EPI_TMA = eight warps stage through shared memory and
+//      store with TMA (asynchronous: tensor memory is handed back without waiting for global memory),
+//      EPI_GATHER = EPI_REGS plus the copy-out warps of the gather-fused kernel;
 // bn: columns of the CTA tile (multiple of 16, <= BN_MAX) = rows per scale-factor tile of the right operand
-template <int OUT_DT, int MH, bool MULTI>
-__global__ void __launch_bounds__(THREADS + (MULTI ? FWD_WARPS * 32 : 0), 1)
+enum : int { EPI_REGS = 0, EPI_TMA = 1, EPI_GATHER = 2 };
+template <int EPI> constexpr int kernel_threads() { return EPI == EPI_TMA ? THREADS_TMA : THREADS + (EPI == EPI_GATHER ? FWD_WARPS * 32 : 0); }
+
+template <int OUT_DT, int MH, int EPI>
+__global__ void __launch_bounds__(kernel_threads<EPI>(), 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, void* __restrict__ out,
                const void* __restrict__ bias, int M, int N, int K, int bn, uint32_t idesc_base, int* status,
-               const __grid_constant__ OutSpec outs) {
+               const __grid_constant__ OutSpec outs, const __grid_constant__ OutMaps omaps) {
     using C = Cfg<MH>;
     constexpr int STAGES = C::STAGES;
+    constexpr bool MULTI = EPI == EPI_GATHER;
+    constexpr int EPI_WARPS = EPI == EPI_TMA ? EPI_TMA_WARPS : 4;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t ring = (raw + 1023u) & ~1023u;                    // 1024-aligned operand ring
     uint8_t* ring_ptr = smem_raw + (ring - raw);
-    const uint32_t bars = ring + STAGES * C::STAGE_BYTES;            // full[S], empty[S], accum_full, tmem_empty[2], drain, tmem slot
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ring_ptr + STAGES * C::STAGE_BYTES + 8 * (2 * STAGES + 4));
+    // ring | staging slots of the asynchronous epilogue (EPI_TMA only) | barriers
+    constexpr uint32_t STAGING = EPI == EPI_TMA ? EPI_TMA_WARPS * EPI_SLOT_BYTES : 0;
+    const uint32_t bars = ring + STAGES * C::STAGE_BYTES + STAGING;  // full[S], empty[S], accum_full, tmem_empty[2], drain, tmem slot
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ring_ptr + STAGES * C::STAGE_BYTES + STAGING + 8 * (2 * STAGES + 4));
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
     const uint32_t accum_bar = bars + 8u * (2 * STAGES);
@@ -133,8 +146,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         mbar_init(accum_bar, 1);
-        mbar_init(tmem_empty_bar(0), 4);                             // one arrival per epilogue warp
-        mbar_init(tmem_empty_bar(1), 4);
+        mbar_init(tmem_empty_bar(0), EPI_WARPS);                     // one arrival per epilogue warp
+        mbar_init(tmem_empty_bar(1), EPI_WARPS);
         mbar_init(drain_bar, 1);
         if constexpr (MULTI) {
             for (int h = 0; h < 2; ++h) {
@@ -237,7 +250,34 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             __syncwarp();
             mbar_wait(drain_bar, 0, nullptr, 0);
         }
-    } else if (warp < 6) {
+    } else if (EPI == EPI_TMA && warp < 2 + EPI_WARPS) {
+        // ---------------- epilogue: TMEM -> registers -> shared staging -> TMA store ----------------
+        if constexpr (EPI == EPI_TMA) {
+            const int e = warp - 2, q = warp & 3;          // two warps per TMEM lane quadrant; each takes every other chunk
+            const int grp = e >> 2;
+            const int n_chunks = (bn + 31) >> 5;
+            const bool tail16 = (bn & 16) != 0;
+            uint8_t* slots = ring_ptr + STAGES * C::STAGE_BYTES + e * EPI_SLOT_BYTES;
+            uint32_t turn = 0;
+            bool ok = true;
+            uint32_t tcount = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+                int mt, nt;
+                tile_coords(tile, MT, NT, mt, nt);
+                ok = mbar_wait(accum_bar, tcount & 1, status, ST_EPILOGUE_TIMEOUT);
+                tc_fence_after();
+                if (!ok) break;
+#pragma unroll
+                for (int h = 0; h < MH; ++h) {
+                    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + h * BN_MAX;
+                    // the group that took the even chunks of accumulator 0 takes the odd ones of accumulator 1
+                    drain_accumulator_tma<OUT_DT>(taddr, n_chunks, tail16, (grp ^ h) & 1, 2, bias, nt * bn, mt * C::BM + h * 128 + q * 32, M, N,
+                                                  slots, turn, omaps, tmem_empty_bar(h), lane);
+                }
+            }
+            if (lane == 0) bulk_wait_all();                // the stores issued by this warp have been written
+        }
+    } else if (EPI != EPI_TMA && warp < 6) {
         // ---------------- epilogue: TMEM -> registers -> global ----------------
         const int q = warp & 3;                            // TMEM lane quadrant this warp may access
         const int full_chunks = bn >> 5;                   // 32-column chunks, then possibly one of 16 columns
@@ -417,20 +457,21 @@ static bool make_operand_map(CUtensorMap* map, const void* codes, int64_t rows, 
 }
 
 // outs == nullptr: plain epilogue into `out`; otherwise the gather-fused epilogue into outs->ptr[]
-template <int OUT_DT, int MH, bool MULTI>
+template <int OUT_DT, int MH, int EPI>
 static int launch_gemm(const uint8_t* a_codes, const uint8_t* b_codes, const uint8_t* sfa, const uint8_t* sfb, void* out,
-                       const void* bias, int M, int N, int K, int bn, uint32_t idesc, int* status, cudaStream_t st, const OutSpec* outs) {
+                       const void* bias, int M, int N, int K, int bn, uint32_t idesc, int* status, cudaStream_t st, const OutSpec* outs,
+                       const OutMaps& omaps) {
     using C = Cfg<MH>;
-    constexpr int SMEM = C::SMEM_BYTES;
+    constexpr int SMEM = EPI == EPI_TMA ? C::SMEM_BYTES_TMA : C::SMEM_BYTES;
     static bool attr_done[MAX_DEVICES] = {false};
-    const cudaError_t attr_err = raise_smem_limit(mx_gemm_kernel<OUT_DT, MH, MULTI>, SMEM, attr_done);
+    const cudaError_t attr_err = raise_smem_limit(mx_gemm_kernel<OUT_DT, MH, EPI>, SMEM, attr_done);
     if (attr_err != cudaSuccess) { set_last_cuda_error(attr_err); return MXQ_ELAUNCH; }
     CUtensorMap ma, mb;
     if (!make_operand_map(&ma, a_codes, M, K, C::BM) || !make_operand_map(&mb, b_codes, N, K, bn)) return MXQ_ELAUNCH;
     const int tiles = ((M + C::BM - 1) / C::BM) * ((N + bn - 1) / bn);
     const int grid = tiles < sm_count() ? tiles : sm_count();          // persistent: one CTA per SM
-    mx_gemm_kernel<OUT_DT, MH, MULTI><<<grid, THREADS + (MULTI ? FWD_WARPS * 32 : 0), SMEM, st>>>(ma, mb, sfa, sfb, out, bias, M, N, K, bn, idesc, status,
-                                                                    MULTI ? *outs : OutSpec{});
+    mx_gemm_kernel<OUT_DT, MH, EPI><<<grid, kernel_threads<EPI>(), SMEM, st>>>(ma, mb, sfa, sfb, out, bias, M, N, K, bn, idesc, status,
+                                                                         EPI == EPI_GATHER ? *outs : OutSpec{}, omaps);
     return check_launch();
 }
 
@@ -438,12 +479,18 @@ template <int OUT_DT>
 static int launch_gemm_dt(const uint8_t* a_codes, const uint8_t* b_codes, const uint8_t* sfa, const uint8_t* sfb, void* out,
                           const void* bias, int M, int N, int K, int bn, uint32_t idesc, int* status, cudaStream_t st,
                           const OutSpec* outs = nullptr) {
+    OutMaps omaps{};
     if (outs != nullptr) {
-        if (M <= 128) return launch_gemm<OUT_DT, 1, true>(a_codes, b_codes, sfa, sfb, nullptr, bias, M, N, K, bn, idesc, status, st, outs);
-        return launch_gemm<OUT_DT, 2, true>(a_codes, b_codes, sfa, sfb, nullptr, bias, M, N, K, bn, idesc, status, st, outs);
+        if (M <= 128) return launch_gemm<OUT_DT, 1, EPI_GATHER>(a_codes, b_codes, sfa, sfb, nullptr, bias, M, N, K, bn, idesc, status, st, outs, omaps);
+        return launch_gemm<OUT_DT, 2, EPI_GATHER>(a_codes, b_codes, sfa, sfb, nullptr, bias, M, N, K, bn, idesc, status, st, outs, omaps);
     }
-    if (M <= 128) return launch_gemm<OUT_DT, 1, false>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, bn, idesc, status, st, nullptr);
-    return launch_gemm<OUT_DT, 2, false>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, bn, idesc, status, st, nullptr);
+    // the asynchronous epilogue needs an output TMA can describe (16-byte aligned base and row pitch)
+    if (make_out_maps(&omaps, out, M, N, N, OUT_DT)) {
+        if (M <= 128) return launch_gemm<OUT_DT, 1, EPI_TMA>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, bn, idesc, status, st, nullptr, omaps);
+        return launch_gemm<OUT_DT, 2, EPI_TMA>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, bn, idesc, status, st, nullptr, omaps);
+    }
+    if (M <= 128) return launch_gemm<OUT_DT, 1, EPI_REGS>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, bn, idesc, status, st, nullptr, omaps);
+    return launch_gemm<OUT_DT, 2, EPI_REGS>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, bn, idesc, status, st, nullptr, omaps);
 }
 
 // instruction descriptor: A/B formats, K-major operands, N >> 3, E8M0 scales, M >> 4

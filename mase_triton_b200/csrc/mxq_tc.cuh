@@ -172,6 +172,134 @@ __device__ __forceinline__ void store_chunk(void* __restrict__ out, const void* 
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Asynchronous epilogue: tensor memory -> registers -> a small shared-memory staging slot -> TMA store.
+// The warp never waits for global memory: it hands the accumulator back to the MMA warp as soon as its
+// last tcgen05.ld has completed, and the bulk tensor stores drain behind it.  Two tcgen05.ld are kept
+// in flight (the next chunk is requested before the current one is converted).  Rows past M and
+// columns past N are clipped by the tensor map, so no bounds logic is needed.
+// ------------------------------------------------------------------------------------------------
+constexpr int EPI_SLOT_BYTES = 4096;             // staging per epilogue warp: two 2 KiB slots (16-bit out) or one 4 KiB slot (fp32)
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// the two output maps of a kernel: `main` = boxes of 64 bytes x 32 rows with the 64-byte swizzle, `tail` = boxes of
+// 16 columns x 32 rows, unswizzled (16-bit outputs whose tile width is an odd multiple of 16)
+struct OutMaps { CUtensorMap main, tail; };
+
+template <int OUT_DT>
+__device__ __forceinline__ float bias_at(const void* bias, int col) {
+    if constexpr (OUT_DT == MXQ_F32) return reinterpret_cast<const float*>(bias)[col];
+    else if constexpr (OUT_DT == MXQ_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[col]);
+    else return __half2float(reinterpret_cast<const __half*>(bias)[col]);
+}
+
+// one chunk (W = 32 or 16 accumulator columns of this lane's row) -> staging slot -> TMA store at (col0, row0 + lane)
+template <int OUT_DT, int W>
+__device__ __forceinline__ void emit_chunk_tma(const uint32_t (&r)[32], const void* bias, int col0, int row0, int N, uint8_t* slot,
+                                               const OutMaps& maps, int lane) {
+    float v[W];
+#pragma unroll
+    for (int i = 0; i < W; ++i) v[i] = __uint_as_float(r[i]);
+    if (bias != nullptr) {
+#pragma unroll
+        for (int i = 0; i < W; ++i) if (col0 + i < N) v[i] += bias_at<OUT_DT>(bias, col0 + i);
+    }
+    const uint32_t sw = (uint32_t)((lane >> 1) & 3);                 // 64-byte swizzle: 16-byte unit u of row r sits at unit u ^ ((r >> 1) & 3)
+    if constexpr (OUT_DT == MXQ_F32) {
+        // W floats = W / 16 boxes of 16 columns (64 bytes per row)
+#pragma unroll
+        for (int b = 0; b < W / 16; ++b) {
+            uint8_t* box = slot + b * 2048 + lane * 64;
+#pragma unroll
+            for (uint32_t u = 0; u < 4; ++u)
+                *reinterpret_cast<float4*>(box + ((u ^ sw) << 4)) = make_float4(v[16 * b + 4 * u], v[16 * b + 4 * u + 1], v[16 * b + 4 * u + 2], v[16 * b + 4 * u + 3]);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+#pragma unroll
+            for (int b = 0; b < W / 16; ++b) tma_store_2d(&maps.main, col0 + 16 * b, row0, smem_u32(slot + b * 2048));
+            bulk_commit();
+        }
+    } else {
+        uint32_t pk[W / 2];
+#pragma unroll
+        for (int i = 0; i < W; i += 2) {
+            if constexpr (OUT_DT == MXQ_BF16) { const __nv_bfloat162 h = __floats2bfloat162_rn(v[i], v[i + 1]); pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h); }
+            else { const __half2 h = __floats2half2_rn(v[i], v[i + 1]); pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h); }
+        }
+        if constexpr (W == 32) {
+            uint8_t* box = slot + lane * 64;
+#pragma unroll
+            for (uint32_t u = 0; u < 4; ++u)
+                *reinterpret_cast<uint4*>(box + ((u ^ sw) << 4)) = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
+        } else {
+            uint8_t* box = slot + lane * 32;                         // 16 columns: 32 bytes per row, unswizzled
+#pragma unroll
+            for (uint32_t u = 0; u < 2; ++u)
+                *reinterpret_cast<uint4*>(box + (u << 4)) = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+            tma_store_2d(W == 32 ? &maps.main : &maps.tail, col0, row0, smem_u32(slot));
+            bulk_commit();
+        }
+    }
+}
+
+// This warp's share of one accumulator: chunks first, first + step, ... of the n_chunks 32-column chunks (the last
+// one 16 wide when tail16).  `taddr` = tensor-memory address of column 0 of the accumulator in this warp's lane
+// quadrant; `slots` = this warp's EPI_SLOT_BYTES of staging (1024-byte aligned); `turn` alternates the two slots.
+// Arrives on `release_bar` right after the last tensor-memory read.
+template <int OUT_DT>
+__device__ __forceinline__ void drain_accumulator_tma(uint32_t taddr, int n_chunks, bool tail16, int first, int step, const void* bias,
+                                                      int col_base, int row0, int M, int N, uint8_t* slots, uint32_t& turn, const OutMaps& maps,
+                                                      uint32_t release_bar, int lane) {
+    constexpr bool TWO_SLOTS = OUT_DT != MXQ_F32;
+    uint32_t ra[32], rb[32];
+    auto request = [&](uint32_t (&r)[32], int c) {
+        if (tail16 && c == n_chunks - 1) tmem_ld_32x32b_x16(taddr + c * 32, r);
+        else tmem_ld_32x32b_x32(taddr + c * 32, r);
+    };
+    auto release = [&]() {                      // no tensor-memory read of this warp is outstanding any more
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(release_bar);
+    };
+    auto emit = [&](const uint32_t (&r)[32], int c) {
+        if (row0 >= M || col_base + c * 32 >= N) return;             // nothing of this box lies inside the matrix
+        // the slot about to be written must have been read by the store issued from it earlier
+        if (lane == 0) { if constexpr (TWO_SLOTS) bulk_wait_read<1>(); else bulk_wait_read<0>(); }
+        __syncwarp();
+        uint8_t* slot = slots + (TWO_SLOTS ? (turn & 1u) * 2048u : 0u);
+        ++turn;
+        if (tail16 && c == n_chunks - 1) emit_chunk_tma<OUT_DT, 16>(r, bias, col_base + c * 32, row0, N, slot, maps, lane);
+        else emit_chunk_tma<OUT_DT, 32>(r, bias, col_base + c * 32, row0, N, slot, maps, lane);
+    };
+    int c = first;
+    if (c >= n_chunks) { release(); return; }
+    request(ra, c);
+    while (c < n_chunks) {
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int c1 = c + step;
+        if (c1 < n_chunks) request(rb, c1); else release();
+        emit(ra, c);
+        if (c1 >= n_chunks) break;
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int c2 = c1 + step;
+        if (c2 < n_chunks) request(ra, c2); else release();
+        emit(rb, c1);
+        c = c2;
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -186,6 +314,27 @@ static EncodeTiledFn encode_tiled_fn() {
             fn = reinterpret_cast<EncodeTiledFn>(p);
     });
     return fn;
+}
+
+// Output maps of the asynchronous epilogue for a row-major [M, N] matrix of dtype `dt` with `ld` elements per row.
+// False when the matrix cannot be described (base or row pitch not a multiple of 16 bytes): the caller then uses
+// the epilogue that stores from registers.
+static bool make_out_maps(OutMaps* maps, void* out, int64_t M, int64_t N, int64_t ld, int dt) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const int esz = dt == MXQ_F32 ? 4 : 2;
+    if (reinterpret_cast<uintptr_t>(out) % 16 != 0 || (ld * esz) % 16 != 0) return false;
+    const CUtensorMapDataType type = dt == MXQ_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : (dt == MXQ_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+    const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)(ld * esz)};
+    const cuuint32_t estr[2] = {1, 1};
+    const cuuint32_t box_main[2] = {(cuuint32_t)(64 / esz), 32};
+    const cuuint32_t box_tail[2] = {16, 32};
+    if (fn(&maps->main, type, 2, out, dims, strides, box_main, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+           CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return false;
+    return fn(&maps->tail, type, 2, out, dims, strides, box_tail, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              dt == MXQ_F32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // Per-device facts and one-time set-up (a process may drive several GPUs): the SM count, and for every
