@@ -197,6 +197,19 @@ int mxq_mx_gemm(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw_format, co
                 const void* bias, int64_t M, int64_t N, int64_t K, int* status, void* stream);
 
 /*
+ * ---- Dense storage of element codes ----
+ * The reference keeps one MXFP element code per byte (`elements`, src/mase_triton/mxfp/fake.py:57-59;
+ * the Parameter `w_elements` of MXFPLinearPTQ, src/mase_triton/mxfp/layers.py:66-80) although a code
+ * has 1 + exp_bits + frac_bits significant bits.  mxq_pack_codes writes n codes of `bits` bits (4, 6
+ * or 8) as a little-endian bit stream of mxq_packed_bytes(n, bits) = n * bits / 8 bytes (code i in
+ * bits [i * bits, (i + 1) * bits)); mxq_unpack_codes restores one code per byte.  n must be a
+ * multiple of 16 (else MXQ_ESIZE), both buffers 16-byte aligned.  No counterpart in the reference.
+ */
+int64_t mxq_packed_bytes(int64_t n, int bits);
+int mxq_pack_codes(const uint8_t* codes, uint8_t* packed, int64_t n, int bits, void* stream);
+int mxq_unpack_codes(const uint8_t* packed, uint8_t* codes, int64_t n, int bits, void* stream);
+
+/*
  * ---- Tensor-core GEMMs for the layer types whose operands are not both block-quantised ----
  * out[M,N] = x[M,K] * W[N,K]^T (+ bias[N]); x, out and bias are bf16 or fp16 (`dtype`: MXQ_BF16 /
  * MXQ_F16; MXQ_F32 returns MXQ_ESIZE), fp32 accumulation in tensor memory (tcgen05.mma.kind::f16,

@@ -39,9 +39,11 @@ SIGNATURES = {
     "mxq_dense_linear": [_p, _p, _i, _p, _p, _i64, _i64, _i64, _p, _p],
     "mxq_mxfp_weight_linear": [_p, _i, _p, _p, _i, _i, _p, _p, _i64, _i64, _i64, _p, _p],
     "mxq_minifloat_weight_linear": [_p, _i, _p, _i, _i, _i, _p, _p, _i64, _i64, _i64, _p, _p],
+    "mxq_pack_codes": [_p, _p, _i64, _i, _p],
+    "mxq_unpack_codes": [_p, _p, _i64, _i, _p],
     "mxq_version": [],
 }
-_I64_FUNCS = {"mxq_mx_sf_bytes": [_i64, _i64, _i, _i], "mxq_mx_linear_scratch_bytes": [_i64, _i64],
+_I64_FUNCS = {"mxq_mx_sf_bytes": [_i64, _i64, _i, _i], "mxq_packed_bytes": [_i64, _i], "mxq_mx_linear_scratch_bytes": [_i64, _i64],
               "mxq_mx_linear_static_capacity": []}
 _STRING_FUNCS = {"mxq_status_string": [_i], "mxq_last_cuda_error": []}
 

@@ -15,7 +15,7 @@ from pathlib import Path
 
 CSRC = Path(__file__).resolve().parent / "csrc"
 LIB = CSRC / "libmxq.so"
-SOURCES = ["mxq_api.cu", "mxq_elementwise.cu", "mxq_strided.cu", "mxq_gemm.cu", "mxq_dq_gemm.cu"]
+SOURCES = ["mxq_api.cu", "mxq_elementwise.cu", "mxq_strided.cu", "mxq_gemm.cu", "mxq_dq_gemm.cu", "mxq_bitpack.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--threads", "4"]
 

@@ -208,6 +208,94 @@ __device__ __forceinline__ void e2m1_bf16_quantise(const Pack<16>& p, const E2M1
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// The same idea for the other element formats (E4M3, E5M2, E2M3, E3M2) of bf16 inputs: two elements
+// per 32-bit word on the packed bf16 units.  For a quotient q = |x| * 2^-se (exact in bf16):
+//   * normal range (biased exponent >= 1): the 7-bit mantissa, tagged with exponent 0, plus 2^(7-fb)
+//     rounds half to even to fb fraction bits, so the sum's low bits are 2^fb + fr with fr in
+//     [0, 2^fb]; the code is q's exponent field, re-biased by flipping its bit eb-1 (127 - bias is
+//     2^(eb-1) modulo 2^eb), with fr OR-ed in -- fr = 2^fb lands on the exponent's low bit, which is the
+//     reference's OR-merge with its lost carry (minifloat/fake.py:70-75); the dequantised value is fr
+//     OR-ed under q's own exponent field;
+//   * below 2^(1-bias): the single subnormal binade (fake.py:56-60) encodes as (fr | 2^fb) >> 1 unless
+//     fr is zero, anything below 2^-bias as zero.  For the 8-bit formats such elements are rare and the lanes of a
+//     warp skip this part together when none of them has one;
+//   * an element is kept (else it is +0) when it is not a flushed input and its fp32 quotient does not
+//     round to zero: one packed comparison against a per-block threshold; the sign rides along.
+// A bf16 input has 7 mantissa bits, so the reference's cut to 15 bits (fake.py:45) changes nothing.
+// ------------------------------------------------------------------------------------------------
+template <class F> struct PkFmt {
+    static constexpr int EB = F{}.eb(), FB = F{}.fb();
+    static constexpr int BIAS = (1 << (EB - 1)) - 1;
+    static constexpr uint32_t rep(uint32_t half) { return half * 0x10001u; }
+    static constexpr uint32_t ROUND_C = rep((uint32_t)(127 + 7 - FB) << 7);                      // 2^(7-fb)
+    static constexpr uint32_t SUM_BASE = rep(((uint32_t)(127 + 7 - FB) << 7) + (1u << FB));      // bits of 2^(7-fb) with mantissa field 2^fb
+    static constexpr uint32_t EXP_FLIP = rep((1u << (EB - 1)) << FB);
+    static constexpr uint32_t MAG_MASK = rep((1u << (EB + FB)) - 1u);
+    static constexpr uint32_t EXP_MASK = rep(((1u << EB) - 1u) << FB);
+    static constexpr uint32_t FR_ONE = rep(1u << FB);
+    static constexpr uint32_t SUB_MASK = rep((2u << FB) - 1u);
+    static constexpr uint32_t SIGN_BIT = rep(1u << (EB + FB));
+    static constexpr uint32_t NORMAL_MIN = rep((uint32_t)(128 - BIAS) << 7);                     // 2^(1-bias)
+    static constexpr uint32_t BINADE_MIN = rep((uint32_t)(127 - BIAS) << 7);                     // 2^-bias
+    static constexpr uint32_t REBIAS = rep((uint32_t)(254 - BIAS) << 7);                         // 2^(127-bias)
+    static constexpr bool RARE_SUBRANGE = EB >= 4;       // block maximum >= 2^(emax-bias): elements 2^14 (E4M3) / 2^29 (E5M2) below it
+};
+
+// one 16-byte access of a lane (8 bf16 inputs) of a finite block.
+// VALUES: 8 bf16 results in out[0..4); else 8 magnitude+sign code bytes in out[0..2)
+template <class F, bool VALUES>
+__device__ __forceinline__ void pk_bf16_quantise(const Pack<16>& p, const E2M1Block& b, uint32_t* out) {
+    using P = PkFmt<F>;
+    uint32_t qb[4], fr[4], res[4];
+    uint32_t any_sub = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t aw = p.w[i] & 0x7FFF7FFFu;
+        qb[i] = bf2_bits(__hmul2(bf2(aw), bf2(b.inv2)));
+        const uint32_t sum = bf2_bits(__hadd2(bf2((qb[i] & 0x007F007Fu) | 0x3F803F80u), bf2(P::ROUND_C)));
+        fr[i] = sum - P::SUM_BASE;                                           // 0 .. 2^fb in each half
+        if constexpr (VALUES) res[i] = (qb[i] & 0x7F807F80u) | (fr[i] << (7 - P::FB));
+        else res[i] = (((qb[i] >> (7 - P::FB)) ^ P::EXP_FLIP) & P::EXP_MASK) | fr[i];
+        any_sub |= __hlt2_mask(bf2(qb[i]), bf2(P::NORMAL_MIN));
+    }
+    if (!P::RARE_SUBRANGE || __any_sync(__activemask(), any_sub != 0u)) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t lt = __hlt2_mask(bf2(qb[i]), bf2(P::NORMAL_MIN));
+            const uint32_t ge = __hge2_mask(bf2(qb[i]), bf2(P::BINADE_MIN));
+            // (fr | 2^fb) >> 1 when the rounded mantissa field is not zero (fake.py:58), zero otherwise and below the binade
+            const uint32_t nz = (((fr[i] + 0x7FFF7FFFu) >> 15) & 0x00010001u) * 0xFFFFu;
+            const uint32_t sub = ((fr[i] | P::FR_ONE) >> 1) & P::SUB_MASK & ge & nz;
+            if constexpr (VALUES) {
+                // sub * 2^(1-bias-fb): the field placed at the top of a bf16 mantissa is sub * 2^(-fb-126)
+                const uint32_t v = bf2_bits(__hmul2(bf2(sub << (7 - P::FB)), bf2(P::REBIAS)));
+                res[i] = (lt & v) | (~lt & res[i]);
+            } else {
+                res[i] = (lt & sub) | (~lt & res[i]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t w = p.w[i];
+        const uint32_t keep = __hgt2_mask(bf2(w & 0x7FFF7FFFu), bf2(b.ts2));
+        if constexpr (VALUES) {
+            const uint32_t o = bf2_bits(__hmul2(bf2(res[i]), bf2(b.sf2)));
+            res[i] = ((o & 0x7FFF7FFFu) | (w & 0x80008000u)) & keep;
+        } else {
+            res[i] = (res[i] | ((w >> (15 - P::EB - P::FB)) & P::SIGN_BIT)) & keep;
+        }
+    }
+    if constexpr (VALUES) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) out[i] = res[i];
+    } else {
+        out[0] = __byte_perm(res[0], res[1], 0x6420);
+        out[1] = __byte_perm(res[2], res[3], 0x6420);
+    }
+}
+
 template <class KIn, class F, int U, int MODE, bool FULL>
 __device__ __forceinline__ void mxfp_b32_quant_tile(const char* __restrict__ src, uint8_t* __restrict__ scales,
                                                     char* __restrict__ dst, int64_t first, int64_t left, const F& f,
@@ -250,6 +338,46 @@ __device__ __forceinline__ void mxfp_b32_quant_tile(const char* __restrict__ src
         const uint32_t h = __shfl_sync(0xFFFFFFFFu, hdr, (lane & ~(G - 1)) + j);
         if (!FULL && j * kThreads >= left) continue;
         char* d = dst + (size_t)j * kThreads * OB;
+        if constexpr (std::is_same<KIn, KBF16>::value && !(F{}.eb() == 2 && F{}.fb() == 1)) {
+            // bf16 inputs, 8- and 6-bit element formats: packed bf16 arithmetic, two elements per word
+            if (!(h & 1u)) {
+                const E2M1Block b = e2m1_block(h);
+                if constexpr (MODE == MODE_QDQ) {
+                    Pack<16> o;
+                    pk_bf16_quantise<F, true>(p[j], b, o.w);
+                    store_pack<16>(d, o);
+                } else {
+                    Pack<V> o;
+                    pk_bf16_quantise<F, false>(p[j], b, o.w);
+                    if constexpr (MODE == MODE_HWPACK) {
+                        // a block holding a magnitude the hardware format reads as NaN/Inf (reference E4M3 0x7F,
+                        // reference E5M2 exponent 31) is stored as (scale + 1, elements / 2); a carry out of the
+                        // magnitude byte marks such a code
+                        constexpr uint32_t probe = (F{}.eb() == 4) ? 0x01010101u : 0x04040404u;
+                        uint32_t bad = ((((o.w[0] & 0x7F7F7F7Fu) + probe) | ((o.w[1] & 0x7F7F7F7Fu) + probe)) & 0x80808080u) ? 1u : 0u;
+                        const uint32_t group_mask = ((G == 8) ? 0xFFu : 0xFu) << (lane & ~(G - 1));
+#pragma unroll
+                        for (int s2 = 1; s2 < G; s2 <<= 1) bad |= __shfl_xor_sync(group_mask, bad, s2);
+                        if (bad) {
+                            const Pack<V> src = o;
+#pragma unroll
+                            for (int i = 0; i < V; ++i) {
+                                const uint32_t c = pack_get<1>(src, i);
+                                uint32_t mag = c & 0x7Fu;
+                                mag = (mag >= (2u << f.fb())) ? mag - (1u << f.fb()) : (mag + ((mag >> 1) & 1u)) >> 1;
+                                pack_set<1>(o, i, mag | (c & 0x80u));
+                            }
+                        }
+                        if (sub == 0) {
+                            const uint32_t sb = (h >> 8) & 0xFFu;
+                            scales[sf_chunk_offset((uint32_t)((first + (int64_t)j * kThreads) / G), geom)] = (uint8_t)((bad && sb < 255u) ? sb + 1u : sb);
+                        }
+                    }
+                    store_pack<V>(d, o);
+                }
+                continue;
+            }
+        }
         if constexpr (std::is_same<KIn, KBF16>::value && F{}.eb() == 2 && F{}.fb() == 1 && MODE != MODE_HWPACK) {
             if (!(h & 1u)) {
                 const E2M1Block b = e2m1_block(h);

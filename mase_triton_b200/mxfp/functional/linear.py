@@ -30,6 +30,16 @@ def parse_mxfp_linear_type(x_meta: MXFPMeta | None, w_tensor_meta: MXFPTensorMet
                    for name, meta in (("X", x_meta), ("W", w_tensor_meta), ("B", b_tensor_meta)))
 
 
+def block_scaled_ok(x: Tensor, x_meta: MXFPMeta | None, w_tensor_meta: MXFPTensorMeta | None) -> bool:
+    """True when ``x`` and a weight described by ``w_tensor_meta`` can both stay quantised on the block-scaled
+    tensor-core GEMM: 32-element blocks along ``in_features``, is_finite elements, CUDA, a kernel dtype."""
+    if x_meta is None or w_tensor_meta is None:
+        return False
+    shape = tuple(w_tensor_meta.shape)
+    return (len(shape) == 2 and w_tensor_meta.block_dim in (1, -1) and _gemm.supported(w_tensor_meta.meta) and _gemm.supported(x_meta)
+            and x.is_cuda and x.dtype in _lib.DTYPE_ID and x.shape[-1] == shape[1] and shape[1] % 32 == 0 and x.numel() > 0)
+
+
 def _fused_linear(x: Tensor, x_meta: MXFPMeta | None, w: Tensor | None, w_scales: Tensor | None, w_elements: Tensor | None,
                   w_tensor_meta: MXFPTensorMeta | None, bias: Tensor | None, kind) -> Tensor:
     """``backend="fused"``: every layer type runs a hand-written tensor-core GEMM of this library.
@@ -46,8 +56,7 @@ def _fused_linear(x: Tensor, x_meta: MXFPMeta | None, w: Tensor | None, w_scales
     w_shape = tuple(w_tensor_meta.shape) if kind.w_quantised else tuple(w.shape)
     K = x.shape[-1]
     w_blocks_along_k = kind.w_quantised and len(w_shape) == 2 and w_tensor_meta.block_dim in (1, -1) and _gemm.supported(w_tensor_meta.meta)
-    if (kind.x_quantised and w_blocks_along_k and x.is_cuda and x.dtype in _lib.DTYPE_ID and _gemm.supported(x_meta)
-            and K % 32 == 0 and x.numel() > 0):
+    if kind.x_quantised and kind.w_quantised and block_scaled_ok(x, x_meta, w_tensor_meta):
         wq = _gemm.packed_weight(w_scales, w_elements, w_shape, w_tensor_meta.meta)
         return _gemm.mx_linear(x, x_meta, wq, bias)
     reason = tc_linear.why_not(x, K)

@@ -63,6 +63,11 @@ class MXFPLinearPTQ(PTQLinearBase):
 
         self.weight = self.w_scales = self.w_elements = self.w_tensor_meta = None
         self.bias = self.b_scales = self.b_elements = self.b_tensor_meta = None
+        # tensor-core form of the quantised weight (hardware codes + tiled scale factors), built on first use.
+        # Non-persistent buffers: they follow .to() / .cuda() with the module and stay out of state_dict().
+        self.register_buffer("_tc_codes", None, persistent=False)
+        self.register_buffer("_tc_sf", None, persistent=False)
+        self._tc_info = None          # (versions of the code tensors it was built from, hw_format, tile_rows)
 
         if "Wq" in layer_type:
             if w_scales is None:
@@ -82,8 +87,45 @@ class MXFPLinearPTQ(PTQLinearBase):
         elif bias is not None:
             self.bias = self._frozen(bias.to(dtype=dtype, device=device))
 
+    def tensor_core_weight(self):
+        """The quantised weight re-encoded for the block-scaled GEMM, kept on the module: rebuilt only when the
+        code tensors were written (``load_state_dict``, in-place edits), moved - not rebuilt - by ``.to()``."""
+        from . import gemm as _gemm
+
+        versions = (self.w_elements._version, self.w_scales._version)
+        stale = (self._tc_codes is None or self._tc_info is None or self._tc_info[0] != versions
+                 or self._tc_codes.device != self.w_elements.device)
+        if stale:
+            n, k = self.w_tensor_meta.shape
+            p = _gemm.pack_operand(self.w_scales.data, self.w_elements.data, n, k, self.w_tensor_meta.meta, _gemm.OPERAND_B)
+            self._tc_codes, self._tc_sf = p.codes, p.sf
+            self._tc_info = (versions, p.hw_format, p.tile_rows)
+        n, k = self.w_tensor_meta.shape
+        return _gemm.PackedOperand(self._tc_codes, self._tc_sf, self._tc_info[1], n, k, _gemm.OPERAND_B, self._tc_info[2])
+
+    def export_packed(self) -> dict:
+        """A ``torch.save``-able dict holding this layer with its element codes bit-packed to their true width
+        (4 / 6 / 8 bits) and its tensor metas; see ``mase_triton_b200.mxfp.storage``."""
+        from .storage import export_packed
+
+        return export_packed(self)
+
+    @classmethod
+    def from_packed(cls, record: dict, device="cuda", backend: str | None = None):
+        """Rebuild a layer from :meth:`export_packed` output on ``device``."""
+        from .storage import import_packed
+
+        return import_packed(record, device, backend)
+
     @torch.no_grad()
     def forward(self, input: Tensor) -> Tensor:
+        if (self.backend == "fused" and "Xq" in self.layer_type and "Wq" in self.layer_type
+                and MXFP_F.linear.block_scaled_ok(input, self.x_mxfp_meta, self.w_tensor_meta)):
+            # both operands stay quantised: the module's own tensor-core form of the weight, no per-call packing.
+            # A layer with a quantised bias holds no plain one and then adds none (the reference's rule).
+            from . import gemm as _gemm
+
+            return _gemm.mx_linear(input, self.x_mxfp_meta, self.tensor_core_weight(), self.bias)
         return MXFP_F.mxfp_linear(
             x=input, x_meta=self.x_mxfp_meta,
             w=self.weight, w_scales=self.w_scales, w_elements=self.w_elements, w_tensor_meta=self.w_tensor_meta,
@@ -109,7 +151,7 @@ class MXFPLinearPTQ(PTQLinearBase):
         from . import gemm as _gemm
 
         assert packed.K == self.in_features and self.w_scales is not None
-        wq = _gemm.packed_weight(self.w_scales, self.w_elements, tuple(self.w_tensor_meta.shape), self.w_tensor_meta.meta)
+        wq = self.tensor_core_weight()
         # a layer with a quantised bias holds no plain one, and forward() then adds none (the reference's rule)
         y = _gemm.mx_gemm(packed, wq, out_dtype, bias=self.bias)
         return y if lead_shape is None else y.reshape(*lead_shape, self.out_features)
