@@ -119,45 +119,52 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     else { const __half2 h = __floats2half2_rn(lo, hi); return *reinterpret_cast<const uint32_t*>(&h); }
 }
 
-// SRC_MX: eight code bytes (two words) and their block's scale byte -> eight DT elements
-template <int DT>
-__device__ __forceinline__ uint4 dequant_mx8(uint32_t w0, uint32_t w1, uint32_t sbyte, const DqConsts& c) {
-    uint32_t o[4];
-    if constexpr (DT == MXQ_BF16) {
-        // Two elements per 32-bit word on the packed bf16 units.  A code shifted so that its exponent field
-        // sits at the bottom of bf16's exponent field and its fraction at the top of bf16's mantissa is the
-        // value times 2^(bias-127) (subnormal codes become bf16 subnormals, still exact); one multiply by
-        // 2^(scale-bias) restores the bias and applies the block scale, rounding once to bf16 exactly like
-        // the reference's fp32 product followed by .to(bfloat16).  Scales too large for that factor to be a
-        // finite bf16 (and 255 = Inf) take two multiplies.
-        const uint32_t words[2] = {w0, w1};
-        const bool one_step = sbyte <= 127u + c.bias_;
-        const uint32_t f1 = one_step ? ((sbyte + 127u - c.bias_) << 7) * 0x10001u : ((254u - c.bias_) << 7) * 0x10001u;
+// SRC_MX -> bf16, element format known at compile time: sixteen code bytes (one 16-byte load) and their block's
+// scale byte -> sixteen bf16 values.  Two elements per 32-bit word on the packed bf16 units: a code shifted so
+// that its exponent field sits at the bottom of bf16's exponent field and its fraction at the top of bf16's
+// mantissa is the value times 2^(bias-127) (subnormal codes become bf16 subnormals, still exact); one multiply
+// by 2^(scale-bias) restores the bias and applies the block scale, rounding once to bf16 exactly like the
+// reference's fp32 product followed by .to(bfloat16).  Scales too large for that factor to be a finite bf16
+// (and 255 = Inf) take a second multiply.
+template <int EB, int FB>
+__device__ __forceinline__ void dequant_mx16_bf16(const uint4& w, uint32_t sbyte, uint4& lo, uint4& hi) {
+    constexpr uint32_t BIAS = (1u << (EB - 1)) - 1u;
+    constexpr uint32_t MAG_MASK2 = (((1u << (EB + FB)) - 1u) << (7 - FB)) * 0x10001u;
+    constexpr int SIGN_SHIFT = 7 - EB - FB;                           // 0 for the 8-bit formats
+    const bool one_step = sbyte <= 127u + BIAS;
+    const uint32_t f1 = (((one_step ? sbyte + 127u : 254u) - BIAS) << 7) * 0x10001u;
+    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+    uint32_t o[8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t t = __byte_perm(words[j >> 1], 0u, (j & 1) ? 0x3424u : 0x1404u);     // code << 8 in each half
-            const uint32_t mag = (t >> c.mag_shift2) & c.mag_mask2;
-            // sign: bit eb+fb of the code -> bit 15 of the half (already there for the 8-bit formats)
-            const uint32_t v = mag | ((c.sign_shift2 ? (t << c.sign_shift2) : t) & 0x80008000u);
-            const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&v), *reinterpret_cast<const __nv_bfloat162*>(&f1));
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t t = __byte_perm(words[j >> 1], 0u, (j & 1) ? 0x3424u : 0x1404u);     // code << 8 in each half
+        const uint32_t sg = SIGN_SHIFT ? (t << SIGN_SHIFT) : t;
+        const uint32_t v = ((t >> (1 + FB)) & MAG_MASK2) | (sg & 0x80008000u);
+        const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&v), *reinterpret_cast<const __nv_bfloat162*>(&f1));
+        o[j] = *reinterpret_cast<const uint32_t*>(&r);
+    }
+    if (!one_step) {
+        const uint32_t f2 = (sbyte == 255u ? 0x7F80u : (sbyte << 7)) * 0x10001u;           // 2^(scale-127); here scale > 127
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&o[j]), *reinterpret_cast<const __nv_bfloat162*>(&f2));
             o[j] = *reinterpret_cast<const uint32_t*>(&r);
         }
-        if (!one_step) {
-            const uint32_t f2 = (sbyte == 255u ? 0x7F80u : (sbyte << 7)) * 0x10001u;           // 2^(scale-127); here scale > 127
+    }
+    lo = make_uint4(o[0], o[1], o[2], o[3]);
+    hi = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+// SRC_MX, any dtype / format (fp32 arithmetic): eight code bytes (two words) and their block's scale byte -> eight DT elements
+template <int DT>
+__device__ __forceinline__ uint4 dequant_mx8(uint32_t w0, uint32_t w1, uint32_t sbyte, const DqConsts& c) {
+    const float scale = __uint_as_float(sbyte == 0u ? 0x00400000u : (sbyte << 23));     // 255 -> +Inf as exp2(128) in fp32
+    const uint32_t words[2] = {w0, w1};
+    uint32_t o[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&o[j]), *reinterpret_cast<const __nv_bfloat162*>(&f2));
-                o[j] = *reinterpret_cast<const uint32_t*>(&r);
-            }
-        }
-    } else {
-        const float scale = __uint_as_float(sbyte == 0u ? 0x00400000u : (sbyte << 23));     // 255 -> +Inf as exp2(128) in fp32
-        const uint32_t words[2] = {w0, w1};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t pair = words[j >> 1] >> (16 * (j & 1));
-            o[j] = pack2<DT>(decode_scaled(pair & 0xFFu, c, scale), decode_scaled((pair >> 8) & 0xFFu, c, scale));
-        }
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t pair = words[j >> 1] >> (16 * (j & 1));
+        o[j] = pack2<DT>(decode_scaled(pair & 0xFFu, c, scale), decode_scaled((pair >> 8) & 0xFFu, c, scale));
     }
     return make_uint4(o[0], o[1], o[2], o[3]);
 }
@@ -328,31 +335,49 @@ dq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const DqConsts dc = dq_consts(wsrc.eb, wsrc.fb, wsrc.fin);
             const int my_tiles = (num_tiles > (int)blockIdx.x) ? (num_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
             const uint32_t total = (uint32_t)my_tiles * (uint32_t)KT;
-            const int64_t kb_per_row = K / 32;
+            constexpr int CODE_BYTES = SRC == SRC_MX ? 1 : 2;
             Staged<SRC> buf[PF];
 
-            // loads of one stage's codes into registers; rows past N and columns past K read as zero codes
-            auto fetch = [&](uint32_t item, Staged<SRC>& b) {
-                const int tile = (int)blockIdx.x + (int)(item / KT) * (int)gridDim.x;
-                const int kt = (int)(item % KT);
+            // where the next stage to fetch comes from: advanced one K step at a time, so that the per-row addresses are
+            // kept as running pointers and the (tile -> column tile) division happens once per tile
+            int f_tile = blockIdx.x, f_kt = 0;
+            const uint8_t* cptr[ROWS_PER_THREAD];
+            const uint8_t* sptr[ROWS_PER_THREAD];
+            uint32_t row_ok = 0;
+            auto open_tile = [&]() {
                 int mt, nt;
-                tile_coords(tile, MT, NT, mt, nt);
-                const int k0 = kt * BK + seg * 16;
+                tile_coords(f_tile, MT, NT, mt, nt);
+                row_ok = 0;
 #pragma unroll
                 for (int j = 0; j < ROWS_PER_THREAD; ++j) {
                     const int64_t n = (int64_t)nt * BN + row_in + ROWS_PER_PASS * j;
-                    const bool in = n < N && k0 < K;
-                    if constexpr (SRC == SRC_MX) {
-                        b.codes[j] = in ? __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(wsrc.codes) + n * K + k0)) : make_uint4(0u, 0u, 0u, 0u);
-                        b.sb[j] = in ? (uint32_t)__ldg(wsrc.scales + n * kb_per_row + (k0 >> 5)) : 127u;
-                    } else {
-                        const uint4* p = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(wsrc.codes) + n * K + k0);
-                        b.lo[j] = in ? __ldg(p) : make_uint4(0u, 0u, 0u, 0u);
-                        b.hi[j] = in ? __ldg(p + 1) : make_uint4(0u, 0u, 0u, 0u);
-                    }
+                    if (n < N) row_ok |= 1u << j;
+                    cptr[j] = reinterpret_cast<const uint8_t*>(wsrc.codes) + (n * K + seg * 16) * CODE_BYTES;
+                    sptr[j] = wsrc.scales + n * (int64_t)(K / 32) + (seg >> 1);
                 }
             };
-            auto expand = [&](uint32_t item, const Staged<SRC>& b) -> bool {
+            auto fetch = [&](Staged<SRC>& b) {                        // loads of one stage's codes; rows past N, columns past K read as zero codes
+                const bool k_ok = f_kt * BK + seg * 16 < K;
+#pragma unroll
+                for (int j = 0; j < ROWS_PER_THREAD; ++j) {
+                    const bool in = k_ok && ((row_ok >> j) & 1u);
+                    if constexpr (SRC == SRC_MX) {
+                        b.codes[j] = in ? __ldg(reinterpret_cast<const uint4*>(cptr[j])) : make_uint4(0u, 0u, 0u, 0u);
+                        b.sb[j] = in ? (uint32_t)__ldg(sptr[j]) : 127u;
+                    } else {
+                        b.lo[j] = in ? __ldg(reinterpret_cast<const uint4*>(cptr[j])) : make_uint4(0u, 0u, 0u, 0u);
+                        b.hi[j] = in ? __ldg(reinterpret_cast<const uint4*>(cptr[j]) + 1) : make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    cptr[j] += BK * CODE_BYTES;
+                    sptr[j] += BK / 32;
+                }
+                if (++f_kt == KT) {
+                    f_kt = 0;
+                    f_tile += gridDim.x;
+                    if (f_tile < num_tiles) open_tile();
+                }
+            };
+            auto expand = [&](uint32_t item, const Staged<SRC>& b, auto expand_mx16) -> bool {
                 const int s = item % STAGES;
                 if (item >= (uint32_t)STAGES && !mbar_wait(empty_bar(s), ((item / STAGES) & 1) ^ 1, status, ST_DEQUANT_TIMEOUT)) return false;
                 uint8_t* tile_b = ring_ptr + s * C::STAGE_BYTES + C::A_BYTES;
@@ -360,13 +385,8 @@ dq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 for (int j = 0; j < ROWS_PER_THREAD; ++j) {
                     const int r = row_in + ROWS_PER_PASS * j;
                     uint4 v0, v1;
-                    if constexpr (SRC == SRC_MX) {
-                        v0 = dequant_mx8<DT>(b.codes[j].x, b.codes[j].y, b.sb[j], dc);
-                        v1 = dequant_mx8<DT>(b.codes[j].z, b.codes[j].w, b.sb[j], dc);
-                    } else {
-                        v0 = dequant_mf8<DT>(b.lo[j], dc);
-                        v1 = dequant_mf8<DT>(b.hi[j], dc);
-                    }
+                    if constexpr (SRC == SRC_MX) expand_mx16(b.codes[j], b.sb[j], v0, v1);
+                    else { v0 = dequant_mf8<DT>(b.lo[j], dc); v1 = dequant_mf8<DT>(b.hi[j], dc); }
                     // 128-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ (r % 8) of that row
                     uint8_t* row = tile_b + r * 128;
                     *reinterpret_cast<uint4*>(row + (((2 * seg) ^ (r & 7)) << 4)) = v0;
@@ -377,20 +397,39 @@ dq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (lane == 0) mbar_arrive(full_bar(s));
                 return true;
             };
-
+            auto run = [&](auto expand_mx16) {
+                if (total == 0) return;
+                open_tile();
 #pragma unroll
-            for (int d = 0; d < PF; ++d)
-                if ((uint32_t)d < total) fetch((uint32_t)d, buf[d]);
-            bool ok = true;
-            for (uint32_t base = 0; base < total && ok; base += PF) {
+                for (int d = 0; d < PF; ++d)
+                    if ((uint32_t)d < total) fetch(buf[d]);
+                bool ok = true;
+                for (uint32_t base = 0; base < total && ok; base += PF) {
 #pragma unroll
-                for (int d = 0; d < PF; ++d) {
-                    const uint32_t item = base + d;
-                    if (item < total && ok) {
-                        ok = expand(item, buf[d]);
-                        if (ok && item + PF < total) fetch(item + PF, buf[d]);
+                    for (int d = 0; d < PF; ++d) {
+                        const uint32_t item = base + d;
+                        if (item < total && ok) {
+                            ok = expand(item, buf[d], expand_mx16);
+                            if (ok && item + PF < total) fetch(buf[d]);
+                        }
                     }
                 }
+            };
+            auto generic = [&](const uint4& w, uint32_t sb, uint4& lo, uint4& hi) {
+                lo = dequant_mx8<DT>(w.x, w.y, sb, dc);
+                hi = dequant_mx8<DT>(w.z, w.w, sb, dc);
+            };
+            if constexpr (SRC == SRC_MX && DT == MXQ_BF16) {
+                // the five MX element formats get their shifts and masks as immediates
+                const int fmt = wsrc.eb * 8 + wsrc.fb;
+                if (fmt == 4 * 8 + 3) run([](const uint4& w, uint32_t sb, uint4& lo, uint4& hi) { dequant_mx16_bf16<4, 3>(w, sb, lo, hi); });
+                else if (fmt == 5 * 8 + 2) run([](const uint4& w, uint32_t sb, uint4& lo, uint4& hi) { dequant_mx16_bf16<5, 2>(w, sb, lo, hi); });
+                else if (fmt == 3 * 8 + 2) run([](const uint4& w, uint32_t sb, uint4& lo, uint4& hi) { dequant_mx16_bf16<3, 2>(w, sb, lo, hi); });
+                else if (fmt == 2 * 8 + 3) run([](const uint4& w, uint32_t sb, uint4& lo, uint4& hi) { dequant_mx16_bf16<2, 3>(w, sb, lo, hi); });
+                else if (fmt == 2 * 8 + 1) run([](const uint4& w, uint32_t sb, uint4& lo, uint4& hi) { dequant_mx16_bf16<2, 1>(w, sb, lo, hi); });
+                else run(generic);
+            } else {
+                run(generic);
             }
         }
     }
