@@ -772,6 +772,109 @@ __global__ void __launch_bounds__(kThreads) minifloat_hwpack_kernel(const void* 
     if ((lane & (G - 1)) == 0) hw_sf[sf_chunk_offset((uint32_t)(idx / G), geom)] = (uint8_t)(bad ? 128u : 127u);
 }
 
+// Four hardware magnitude+sign code bytes of a block that is stored with its scale raised by one: every
+// magnitude becomes the code of half the value -- exponent minus one for codes with exponent >= 2, a
+// round-half-to-even shift for the two lowest binades -- on all four bytes of the word at once.
+template <int FB>
+__device__ __forceinline__ uint32_t halve_codes4(uint32_t c) {
+    constexpr uint32_t ONE = 0x01010101u;
+    const uint32_t mag = c & 0x7F7F7F7Fu;
+    // per byte: 0xFF where mag >= 2 << FB (adding 0x80 - (2 << FB) carries into bit 7 exactly then)
+    const uint32_t big = (((mag + ONE * (0x80u - (2u << FB))) >> 7) & ONE) * 0xFFu;
+    const uint32_t normal = mag - (big & (ONE << FB));                       // no borrow: those bytes are >= 2 << FB
+    const uint32_t small = ((mag + ((mag >> 1) & ONE)) >> 1) & 0x7F7F7F7Fu;   // bytes < 2 << FB: no carry out of the byte
+    return (big & normal) | (~big & small) | (c & 0x80808080u);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Activation -> tensor-core left operand in one pass (MXFP8 elements): hardware codes [M, K] and the scale
+// factors in the chunked order of mxq_gemm.cu.  A flat pass over x like the extract kernel (a lane owns 16
+// bytes per access, four accesses in flight, the 4 or 8 lanes of a 32-element block reduce its maximum with
+// shuffles; bf16 inputs take the packed two-per-word quantiser), plus:
+//   * a block holding a magnitude the hardware format reads as NaN/Inf (reference E4M3 0x7F, reference E5M2
+//     exponent 31) is stored as (scale + 1, elements / 2), four code bytes per instruction;
+//   * the scale bytes of four consecutive blocks of a row are adjacent in their chunk, so one lane gathers them
+//     with shuffles and stores one 32-bit word instead of four scattered bytes (K % 128 == 0).
+// ------------------------------------------------------------------------------------------------
+template <class KIn, class F, bool WORDS>
+__global__ void __launch_bounds__(kThreads) mx_quant_pack_flat_kernel(const void* __restrict__ x, uint8_t* __restrict__ hw_codes,
+                                                                      uint8_t* __restrict__ hw_sf, int64_t n_vec, PackGeom geom) {
+    constexpr int V = 16 / KIn::size;              // elements per lane per access: 8 or 4
+    constexpr int G = 32 / V;                      // lanes that share a 32-element block: 4 or 8
+    constexpr int U = 4;
+    const int lane = threadIdx.x & 31;
+    const int sub = lane & (G - 1);
+    const int64_t first = (int64_t)blockIdx.x * (kThreads * U) + threadIdx.x;
+    const F f{};
+    constexpr uint32_t probe = (F{}.eb() == 4) ? 0x01010101u : 0x04040404u;    // carry out of the magnitude byte: a code the hardware reads as NaN / Inf
+    Pack<16> p[U];
+    uint32_t amax[U];
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+        const int64_t vec = first + (int64_t)j * kThreads;
+        p[j] = vec < n_vec ? load_pack<16>(reinterpret_cast<const char*>(x) + vec * 16) : Pack<16>{{0u, 0u, 0u, 0u}};
+    }
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+        float m = __uint_as_float(pack_absmax_bits<KIn>(p[j]));
+#pragma unroll
+        for (int o = 1; o < G; o <<= 1) m = max_abs_nan(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+        amax[j] = __float_as_uint(m);
+    }
+    // lane `sub` of each group derives the header of access `sub` (U <= G)
+    uint32_t mine = amax[0];
+#pragma unroll
+    for (int j = 1; j < U; ++j) mine = (sub == j) ? amax[j] : mine;
+    const uint32_t hdr = block_header(mine, f);
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+        const uint32_t h = __shfl_sync(0xFFFFFFFFu, hdr, (lane & ~(G - 1)) + j);
+        const int64_t vec = first + (int64_t)j * kThreads;
+        Pack<V> o;
+        uint32_t sbyte = (h >> 8) & 0xFFu;
+        if (!(h & 1u)) {
+            if constexpr (std::is_same<KIn, KBF16>::value) {
+                pk_bf16_quantise<F, false>(p[j], e2m1_block(h), o.w);
+            } else {
+                const float inv = __uint_as_float(h & 0x7F800000u);
+                uint32_t qb[V], mag[V];
+#pragma unroll
+                for (int i = 0; i < V; ++i) {
+                    qb[i] = mx_quotient_bits(pack_bits<KIn>(p[j], i), inv);
+                    mag[i] = (uint32_t)encode_mag_fp(qb[i], f);
+                }
+#pragma unroll
+                for (int i = 0; i < V; i += 4) o.w[i >> 2] = pack4_codes(&mag[i], &qb[i], f);
+            }
+            uint32_t bad = 0;
+#pragma unroll
+            for (int i = 0; i < V / 4; ++i) bad |= ((o.w[i] & 0x7F7F7F7Fu) + probe) & 0x80808080u;
+            // only the lanes of this block vote: another group of the warp may hold an Inf/NaN block
+            const uint32_t group_mask = ((G == 8) ? 0xFFu : 0xFu) << (lane & ~(G - 1));
+            if (__any_sync(group_mask, bad != 0u)) {
+#pragma unroll
+                for (int i = 0; i < V / 4; ++i) o.w[i] = halve_codes4<F{}.fb()>(o.w[i]);
+                if (sbyte < 255u) sbyte += 1u;
+            }
+        } else {
+            // Inf/NaN block: scale byte 255 is NaN for the tensor cores too; the codes do not matter
+#pragma unroll
+            for (int i = 0; i < V / 4; ++i) o.w[i] = 0u;
+            sbyte = 255u;
+        }
+        if (vec < n_vec) store_pack<V>(hw_codes + vec * V, o);
+        const uint32_t blk = (uint32_t)(vec / G);
+        if constexpr (WORDS) {
+            // blocks blk .. blk + 3 (blk % 4 == 0) are K blocks 0 .. 3 of one row and one 128-column step
+            uint32_t w = sbyte | (__shfl_down_sync(0xFFFFFFFFu, sbyte, G) << 8);        // this block and the next
+            w |= __shfl_down_sync(0xFFFFFFFFu, w, 2 * G) << 16;                             // ... and the pair after them
+            if ((lane & (4 * G - 1)) == 0 && vec < n_vec) *reinterpret_cast<uint32_t*>(hw_sf + sf_chunk_offset(blk, geom)) = w;
+        } else {
+            if (sub == 0 && vec < n_vec) hw_sf[sf_chunk_offset(blk, geom)] = (uint8_t)sbyte;
+        }
+    }
+}
+
 // Quantise a [M, K] activation to MXFP8 (32-element blocks along K) straight into the tensor-core
 // operand layout of mxq_gemm.cu: hardware FP8 codes [M, K] and left-operand scale-factor chunks.
 // One pass over x instead of extract + pack. Declared in mxq_internal.h; returns MXQ_ESIZE when the
@@ -781,29 +884,29 @@ int quantize_pack_left_operand(const void* x, int x_dtype, int64_t M, int64_t K,
                                uint8_t* hw_sf, int64_t sf_bytes, int* hw_format, cudaStream_t st) {
     const bool e4m3 = (eb == 4 && fb == 3), e5m2 = (eb == 5 && fb == 2);
     if (!(e4m3 || e5m2) || K % 32 != 0 || M * K / 32 >= (1ll << 31)) return MXQ_ESIZE;
-    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(hw_codes)) % 16 != 0) return MXQ_ESIZE;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(hw_codes) | reinterpret_cast<uintptr_t>(hw_sf)) % 16 != 0) return MXQ_ESIZE;
     *hw_format = e5m2 ? 1 : 0;
-    // padding rows / K blocks of the chunked scale array must read as 2^0
-    if (cudaMemsetAsync(hw_sf, 127, (size_t)sf_bytes, st) != cudaSuccess) return check_launch();
+    // padding rows / K blocks of the chunked scale array must read as 2^0; none exist for whole tiles
+    if ((M % 256 != 0 || K % 128 != 0) && cudaMemsetAsync(hw_sf, 127, (size_t)sf_bytes, st) != cudaSuccess) return check_launch();
     PackGeom g;
     g.kbpr = (uint32_t)(K / 32);
     g.shift = 0;
     while ((1u << g.shift) < g.kbpr) ++g.shift;
     g.magic = (uint32_t)((((uint64_t)1 << (31 + g.shift)) + g.kbpr - 1) / g.kbpr);
     g.KT = (uint32_t)((K + 127) / 128);
+    const bool words = K % 128 == 0;
     int rc = MXQ_OK;
     with_kind(x_dtype, [&](auto kin) {
         using KIn = decltype(kin);
         constexpr int V = 16 / KIn::size;
-        constexpr int U = 4;
         const int64_t n_vec = M * K / V;
-        const int64_t grid = (n_vec + kThreads * U - 1) / (kThreads * U);
-        if (e4m3)
-            mxfp_b32_quant_kernel<KIn, FmtCT<4, 3, true, RM_RN>, U, MODE_HWPACK><<<(unsigned)grid, kThreads, 0, st>>>(
-                x, hw_sf, hw_codes, nullptr, n_vec, FmtCT<4, 3, true, RM_RN>{}, g);
-        else
-            mxfp_b32_quant_kernel<KIn, FmtCT<5, 2, true, RM_RN>, U, MODE_HWPACK><<<(unsigned)grid, kThreads, 0, st>>>(
-                x, hw_sf, hw_codes, nullptr, n_vec, FmtCT<5, 2, true, RM_RN>{}, g);
+        const unsigned grid = (unsigned)((n_vec + kThreads * 4 - 1) / (kThreads * 4));
+        auto go = [&](auto fmt) {
+            using F = decltype(fmt);
+            if (words) mx_quant_pack_flat_kernel<KIn, F, true><<<grid, kThreads, 0, st>>>(x, hw_codes, hw_sf, n_vec, g);
+            else mx_quant_pack_flat_kernel<KIn, F, false><<<grid, kThreads, 0, st>>>(x, hw_codes, hw_sf, n_vec, g);
+        };
+        if (e4m3) go(FmtCT<4, 3, true, RM_RN>{}); else go(FmtCT<5, 2, true, RM_RN>{});
         rc = check_launch();
     });
     return rc;
