@@ -511,7 +511,7 @@ def extras_multi_gpu(dev, dist, rank: int, world: int, local: int, steps: int, p
     torch.cuda.empty_cache()
 
     # ---- column-parallel linears: configuration 4 and the seven projections of configuration 5 ----
-    def column_parallel(name: str, x: torch.Tensor, w: torch.Tensor, x_meta, w_meta, n_calls: int) -> dict:
+    def column_parallel(name: str, x: torch.Tensor, w: torch.Tensor, x_meta, w_meta, n_calls: int, tile_rows=None) -> dict:
         n_out, n_in = w.shape
         fc = torch.nn.Linear(n_in, n_out, bias=False, device=dev, dtype=torch.bfloat16)
         with torch.no_grad():
@@ -522,7 +522,7 @@ def extras_multi_gpu(dev, dist, rank: int, world: int, local: int, steps: int, p
         rows_x = xg.numel() // n_in
         want = layer(xg).reshape(rows_x, n_out)                       # the whole layer on this GPU
         via_nccl = parallel.column_parallel_mxfp_linear(layer)
-        fused = parallel.GatherFusedMXFPLinear(layer, max_rows=rows_x, dtype=torch.bfloat16)
+        fused = parallel.GatherFusedMXFPLinear(layer, max_rows=rows_x, dtype=torch.bfloat16, tile_rows=tile_rows)
         got_nccl = via_nccl(xg).reshape(rows_x, n_out).contiguous()
         got_fused = fused(xg).reshape(rows_x, n_out)
         G.check_status(dev)
@@ -563,6 +563,9 @@ def extras_multi_gpu(dev, dist, rank: int, world: int, local: int, steps: int, p
         res, _, _ = column_parallel("cfg4", xc, wc, MXFP8_E4M3_fn, MXFP8_E4M3_fn, 50)
         res["collective"] = "all-gather of bf16 [M, N/g] shards: NCCL, or peer stores issued by the GEMM kernel + a one-element all-reduce as fence"
         out["cfg4_column_parallel"] = res
+        # the same with 192-column tiles: every forwarded row segment is then a whole number of 128-byte lines
+        res192, _, _ = column_parallel("cfg4 (192-column tiles)", xc, wc, MXFP8_E4M3_fn, MXFP8_E4M3_fn, 50, tile_rows=192)
+        out["cfg4_column_parallel"]["with_192_column_tiles"] = {k: res192[k] for k in ("ms", "fused_kernel_nvlink_egress_GBps_per_gpu", "fused_kernel_frac_of_roofline")}
         del xc, wc
         sweep, tot_fl, tot = {}, 0.0, {}
         inputs = {}

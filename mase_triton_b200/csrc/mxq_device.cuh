@@ -194,7 +194,6 @@ __device__ __forceinline__ uint32_t pack4_codes(const uint32_t* mag, const uint3
 // what an MXFP quantiser writes
 constexpr int MODE_QDQ = 0;      // dequantised values (fused quantize_dequantize)
 constexpr int MODE_CODES = 1;    // reference scales + element codes
-constexpr int MODE_HWPACK = 2;   // tensor-core operand: hardware FP8 codes + scale-factor chunks (left operand)
 
 // ------------------------------------------------------------------------------------------------
 // host-side dispatch

@@ -298,8 +298,7 @@ __device__ __forceinline__ void pk_bf16_quantise(const Pack<16>& p, const E2M1Bl
 
 template <class KIn, class F, int U, int MODE, bool FULL>
 __device__ __forceinline__ void mxfp_b32_quant_tile(const char* __restrict__ src, uint8_t* __restrict__ scales,
-                                                    char* __restrict__ dst, int64_t first, int64_t left, const F& f,
-                                                    const PackGeom& geom) {
+                                                    char* __restrict__ dst, int64_t first, int64_t left, const F& f) {
     constexpr bool WRITE_CODES = (MODE != MODE_QDQ);
     constexpr int V = 16 / KIn::size;     // elements per lane per access: 4 (fp32) or 8 (16-bit)
     // fp32 inputs have issue slots to spare for the bookkeeping of the warp-level sub-range skip and
@@ -349,36 +348,12 @@ __device__ __forceinline__ void mxfp_b32_quant_tile(const char* __restrict__ src
                 } else {
                     Pack<V> o;
                     pk_bf16_quantise<F, false>(p[j], b, o.w);
-                    if constexpr (MODE == MODE_HWPACK) {
-                        // a block holding a magnitude the hardware format reads as NaN/Inf (reference E4M3 0x7F,
-                        // reference E5M2 exponent 31) is stored as (scale + 1, elements / 2); a carry out of the
-                        // magnitude byte marks such a code
-                        constexpr uint32_t probe = (F{}.eb() == 4) ? 0x01010101u : 0x04040404u;
-                        uint32_t bad = ((((o.w[0] & 0x7F7F7F7Fu) + probe) | ((o.w[1] & 0x7F7F7F7Fu) + probe)) & 0x80808080u) ? 1u : 0u;
-                        const uint32_t group_mask = ((G == 8) ? 0xFFu : 0xFu) << (lane & ~(G - 1));
-#pragma unroll
-                        for (int s2 = 1; s2 < G; s2 <<= 1) bad |= __shfl_xor_sync(group_mask, bad, s2);
-                        if (bad) {
-                            const Pack<V> src = o;
-#pragma unroll
-                            for (int i = 0; i < V; ++i) {
-                                const uint32_t c = pack_get<1>(src, i);
-                                uint32_t mag = c & 0x7Fu;
-                                mag = (mag >= (2u << f.fb())) ? mag - (1u << f.fb()) : (mag + ((mag >> 1) & 1u)) >> 1;
-                                pack_set<1>(o, i, mag | (c & 0x80u));
-                            }
-                        }
-                        if (sub == 0) {
-                            const uint32_t sb = (h >> 8) & 0xFFu;
-                            scales[sf_chunk_offset((uint32_t)((first + (int64_t)j * kThreads) / G), geom)] = (uint8_t)((bad && sb < 255u) ? sb + 1u : sb);
-                        }
-                    }
                     store_pack<V>(d, o);
                 }
                 continue;
             }
         }
-        if constexpr (std::is_same<KIn, KBF16>::value && F{}.eb() == 2 && F{}.fb() == 1 && MODE != MODE_HWPACK) {
+        if constexpr (std::is_same<KIn, KBF16>::value && F{}.eb() == 2 && F{}.fb() == 1) {
             if (!(h & 1u)) {
                 const E2M1Block b = e2m1_block(h);
                 if constexpr (WRITE_CODES) {
@@ -449,27 +424,6 @@ __device__ __forceinline__ void mxfp_b32_quant_tile(const char* __restrict__ src
                     mag[i] = (uint32_t)encode_mag_fp(qb[i], f);
                 }
             }
-            if constexpr (MODE == MODE_HWPACK) {
-                // a block holding a magnitude the hardware format reads as NaN/Inf (reference E4M3 0x7F,
-                // reference E5M2 exponent 31) is stored as (scale + 1, elements / 2)
-                constexpr uint32_t hw_max = (F{}.eb() == 4) ? 0x7Eu : 0x7Bu;
-                uint32_t bad = 0;
-#pragma unroll
-                for (int i = 0; i < V; ++i) bad |= (mag[i] > hw_max) ? 1u : 0u;
-                // only the lanes of this block take part: other groups may sit in another branch or be past the end
-                const uint32_t group_mask = ((G == 8) ? 0xFFu : 0xFu) << (lane & ~(G - 1));
-#pragma unroll
-                for (int o = 1; o < G; o <<= 1) bad |= __shfl_xor_sync(group_mask, bad, o);
-                if (bad) {
-#pragma unroll
-                    for (int i = 0; i < V; ++i)
-                        mag[i] = (mag[i] >= (2u << f.fb())) ? mag[i] - (1u << f.fb()) : (mag[i] + ((mag[i] >> 1) & 1u)) >> 1;
-                }
-                if (sub == 0) {
-                    const uint32_t sb = (h >> 8) & 0xFFu;
-                    scales[sf_chunk_offset((uint32_t)((first + (int64_t)j * kThreads) / G), geom)] = (uint8_t)((bad && sb < 255u) ? sb + 1u : sb);
-                }
-            }
             if constexpr (WRITE_CODES) {
                 Pack<V> o;
 #pragma unroll
@@ -480,12 +434,6 @@ __device__ __forceinline__ void mxfp_b32_quant_tile(const char* __restrict__ src
             uint32_t code[V];
 #pragma unroll
             for (int i = 0; i < V; ++i) code[i] = mx_encode(pack_bits<KIn>(p[j], i), 128, f);
-            if constexpr (MODE == MODE_HWPACK) {
-                // Inf/NaN block: scale byte 255 is NaN for the tensor cores too; the codes do not matter
-#pragma unroll
-                for (int i = 0; i < V; ++i) code[i] = 0;
-                if (sub == 0) scales[sf_chunk_offset((uint32_t)((first + (int64_t)j * kThreads) / G), geom)] = 255;
-            }
             if constexpr (WRITE_CODES) {
                 Pack<V> o;
 #pragma unroll
@@ -505,15 +453,15 @@ __device__ __forceinline__ void mxfp_b32_quant_tile(const char* __restrict__ src
 template <class KIn, class F, int U, int MODE>
 __global__ void __launch_bounds__(kThreads) mxfp_b32_quant_kernel(const void* __restrict__ x, uint8_t* __restrict__ scales,
                                                                   uint8_t* __restrict__ elements, void* __restrict__ out,
-                                                                  int64_t n_vec, F f, PackGeom geom) {
+                                                                  int64_t n_vec, F f) {
     constexpr int V = 16 / KIn::size;
     const int64_t first = (int64_t)blockIdx.x * (kThreads * U) + threadIdx.x;
     const char* src = reinterpret_cast<const char*>(x) + first * 16;
     char* dst = MODE != MODE_QDQ ? reinterpret_cast<char*>(elements) + first * V : reinterpret_cast<char*>(out) + first * 16;
     if ((int64_t)(blockIdx.x + 1) * (kThreads * U) <= n_vec)
-        mxfp_b32_quant_tile<KIn, F, U, MODE, true>(src, scales, dst, first, 0, f, geom);
+        mxfp_b32_quant_tile<KIn, F, U, MODE, true>(src, scales, dst, first, 0, f);
     else
-        mxfp_b32_quant_tile<KIn, F, U, MODE, false>(src, scales, dst, first, n_vec - first, f, geom);
+        mxfp_b32_quant_tile<KIn, F, U, MODE, false>(src, scales, dst, first, n_vec - first, f);
 }
 
 template <class KOut, class F, int U>
@@ -662,7 +610,7 @@ static int mxfp_quant_dispatch(const void* x, int x_dtype, uint8_t* scales, uint
                     const int64_t n_vec = n / V;
                     const int64_t grid = (n_vec + kThreads * U - 1) / (kThreads * U);
                     mxfp_b32_quant_kernel<KIn, decltype(f), U, WRITE_CODES ? MODE_CODES : MODE_QDQ><<<(unsigned)grid, kThreads, 0, st>>>(
-                        x, scales, elements, out, n_vec, f, PackGeom{});
+                        x, scales, elements, out, n_vec, f);
                     rc = check_launch();
                 });
             };

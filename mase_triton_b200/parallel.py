@@ -125,7 +125,7 @@ class GatherFusedMXFPLinear:
     the next one.
     """
 
-    def __init__(self, layer, max_rows: int, dtype: torch.dtype = torch.bfloat16, group=None):
+    def __init__(self, layer, max_rows: int, dtype: torch.dtype = torch.bfloat16, group=None, tile_rows: int | None = None):
         import torch.distributed._symmetric_memory as symm_mem
 
         from .mxfp import gemm as _gemm
@@ -142,7 +142,9 @@ class GatherFusedMXFPLinear:
         bpr = K // B
         scales = layer.w_scales.data.reshape(N * bpr, 1)[self.n0 * bpr:self.n1 * bpr]
         elements = layer.w_elements.data.reshape(N * bpr, B)[self.n0 * bpr:self.n1 * bpr]
-        self.weight = _gemm.pack_operand(scales, elements, self.n1 - self.n0, K, layer.w_tensor_meta.meta, _gemm.OPERAND_B)
+        # tile_rows: columns of the GEMM's CTA tile (None: least padded work).  192 makes every forwarded row segment
+        # of a 16-bit output a whole number of 128-byte lines, which the NVLink stores prefer when the link is the bound
+        self.weight = _gemm.pack_operand(scales, elements, self.n1 - self.n0, K, layer.w_tensor_meta.meta, _gemm.OPERAND_B, tile_rows)
         self.bias = None if layer.bias is None else layer.bias.data[self.n0:self.n1].to(dtype).contiguous()
         self.x_meta, self.N, self.K, self.dtype, self.max_rows = layer.x_mxfp_meta, N, K, dtype, max_rows
         dev = layer.w_elements.device
