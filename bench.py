@@ -552,6 +552,7 @@ def extras_multi_gpu(dev, dist, rank: int, world: int, local: int, steps: int, p
                "fused_kernel_nvlink_egress_GBps_per_gpu": round(egress / t_kernel / 1e6, 1),
                "fused_kernel_frac_of_roofline": round(max(t_gemm, link_ms) / t_kernel, 3),
                "roofline_ms": {"gemm": round(t_gemm, 4), "link_at_770_GBps": round(link_ms, 4)},
+               "link_note": "770 GB/s is the measured peer-copy rate; a plain copy kernel in which every rank stores to all its peers at once reached 660-680 GB/s per GPU on four GPUs",
                "verified": "NCCL-gathered and gather-fused outputs equal the single-GPU layer bit for bit on every rank",
                "timing": f"one event pair around {n_calls} back-to-back calls, max over ranks"}
         del layer, via_nccl, fused, a, o, xg
@@ -563,9 +564,9 @@ def extras_multi_gpu(dev, dist, rank: int, world: int, local: int, steps: int, p
         res, _, _ = column_parallel("cfg4", xc, wc, MXFP8_E4M3_fn, MXFP8_E4M3_fn, 50)
         res["collective"] = "all-gather of bf16 [M, N/g] shards: NCCL, or peer stores issued by the GEMM kernel + a one-element all-reduce as fence"
         out["cfg4_column_parallel"] = res
-        # the same with 192-column tiles: every forwarded row segment is then a whole number of 128-byte lines
-        res192, _, _ = column_parallel("cfg4 (192-column tiles)", xc, wc, MXFP8_E4M3_fn, MXFP8_E4M3_fn, 50, tile_rows=192)
-        out["cfg4_column_parallel"]["with_192_column_tiles"] = {k: res192[k] for k in ("ms", "fused_kernel_nvlink_egress_GBps_per_gpu", "fused_kernel_frac_of_roofline")}
+        # the same with 224-column tiles (no padded work for 1792 / 3584 / 7168 features per rank, but row segments of 448 bytes)
+        res224, _, _ = column_parallel("cfg4 (224-column tiles)", xc, wc, MXFP8_E4M3_fn, MXFP8_E4M3_fn, 50, tile_rows=224)
+        out["cfg4_column_parallel"]["with_224_column_tiles"] = {k: res224[k] for k in ("ms", "fused_kernel_nvlink_egress_GBps_per_gpu", "fused_kernel_frac_of_roofline")}
         del xc, wc
         sweep, tot_fl, tot = {}, 0.0, {}
         inputs = {}

@@ -142,8 +142,12 @@ class GatherFusedMXFPLinear:
         bpr = K // B
         scales = layer.w_scales.data.reshape(N * bpr, 1)[self.n0 * bpr:self.n1 * bpr]
         elements = layer.w_elements.data.reshape(N * bpr, B)[self.n0 * bpr:self.n1 * bpr]
-        # tile_rows: columns of the GEMM's CTA tile (None: least padded work).  192 makes every forwarded row segment
-        # of a 16-bit output a whole number of 128-byte lines, which the NVLink stores prefer when the link is the bound
+        # tile_rows: columns of the GEMM's CTA tile.  192 makes every forwarded row segment of a 16-bit output a whole
+        # number of 128-byte lines, which the stores over NVLink prefer (+12 % egress on four GPUs); it is the default
+        # where sending the shard to the peers takes longer than computing it (about (g - 1) * 1600 * bytes per element
+        # > in_features), else the width with the least padded work is used.
+        if tile_rows is None and (world - 1) * 1600 * (4 if dtype == torch.float32 else 2) > K and (self.n1 - self.n0) >= 192:
+            tile_rows = 192
         self.weight = _gemm.pack_operand(scales, elements, self.n1 - self.n0, K, layer.w_tensor_meta.meta, _gemm.OPERAND_B, tile_rows)
         self.bias = None if layer.bias is None else layer.bias.data[self.n0:self.n1].to(dtype).contiguous()
         self.x_meta, self.N, self.K, self.dtype, self.max_rows = layer.x_mxfp_meta, N, K, dtype, max_rows
