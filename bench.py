@@ -342,16 +342,22 @@ def extras_single_gpu(dev, steps: int, warmup: int, peak: float) -> dict:
     xq_s = MXFPLinearPTQ.from_linear(fc, MXFP8_E4M3_fn, None, None, "XqWB", "separate")
     t = {"XWq_fused": graph_time(lambda: wq_f(xc), reps), "XWq_separate": graph_time(lambda: wq_s(xc), max(3, reps // 2)),
          "XqW_fused": graph_time(lambda: xq_f(xc), reps), "XqW_separate": graph_time(lambda: xq_s(xc), max(3, reps // 2)),
+         "XWq_codes_expanded_in_the_loader": graph_time(
+             lambda: tc_linear.mxfp_weight_linear(xc, wq_f.w_scales, wq_f.w_elements, (N, K), MXFP8_E4M3_fn), reps),
          "dense_gemm": graph_time(lambda: tc_linear.dense_linear(xc, wc), reps),
          "library_dense_gemm": graph_time(lambda: torch.nn.functional.linear(xc, wc), reps)}
+    x_short = xc[:512].contiguous()
+    t_short = {"XWq_fused": graph_time(lambda: wq_f(x_short), reps * 4), "XWq_separate": graph_time(lambda: wq_s(x_short), reps * 4)}
     G.check_status(dev)
     rel_wq = ((wq_f(xc).float() - wq_s(xc).float()).abs().mean() / wq_s(xc).float().abs().mean()).item()
     out["cfg4_shape_mixed_layer_types_kind_f16_gemm"] = {
         "TFLOPs": {k: round(flops / v / 1e9, 1) for k, v in t.items()}, "ms": {k: round(v, 4) for k, v in t.items()},
         "mean_rel_diff_XWq_fused_vs_separate": round(rel_wq, 8),
+        "short_activation_512_rows_ms": {k: round(v, 4) for k, v in t_short.items()},
+        "XWq_route": "512 rows: codes expanded in the GEMM's loader; 8192 rows: expanded once by the compose kernel, same GEMM on dense operands",
         "frac_of_measured_bf16_burst": {k: round(flops / v / 1e9 / bf16_peak, 3) for k, v in t.items()},
         "note": "fused = this library's tcgen05 kind::f16 GEMM (256x256 tiles); separate = dequantise kernels + torch.nn.functional.linear"}
-    del fc, fused, sep, wq_f, wq_s, xq_f, xq_s, a, b, o, xc, wc
+    del fc, fused, sep, wq_f, wq_s, xq_f, xq_s, a, b, o, xc, wc, x_short
     torch.cuda.empty_cache()
 
     # configuration 5: seven projections of one Llama-3-8B-shaped layer, W MXFP6 E3M2, x MXFP8 E4M3, 16x2048 tokens.
@@ -631,10 +637,14 @@ def small_cases():
         if which == "dense":            # the kind::f16 GEMM on two dense bf16 operands
             from mase_triton_b200 import tc_linear
             return (lambda: tc_linear.dense_linear(x, w)), flops
+        if which == "xwq_loader":       # weight-only quantisation, codes expanded in the GEMM's operand loader whatever M is
+            from mase_triton_b200 import tc_linear
+            ws, we = mxk.extract_mxfp_components(w.reshape(-1), MXFP8_E4M3_fn)
+            return (lambda: tc_linear.mxfp_weight_linear(x, ws, we, (N, K), MXFP8_E4M3_fn)), flops
         fc = torch.nn.Linear(K, N, bias=False, device=dev, dtype=torch.bfloat16)
         with torch.no_grad():
             fc.weight.copy_(w)
-        if which == "xwq":              # weight-only quantisation: codes expanded in the GEMM's operand loader
+        if which == "xwq":              # weight-only quantised layer: the route the layer picks for this M
             layer = MXFPLinearPTQ.from_linear(fc, None, MXFP8_E4M3_fn, None, "XWqB", "fused")
             return (lambda: layer(x)), flops
         layer = MXFPLinearPTQ.from_linear(fc, MXFP8_E4M3_fn, MXFP8_E4M3_fn, None, "XqWqB", "fused" if which == "linear" else "separate")
@@ -666,7 +676,13 @@ def small_cases():
         layer = MinifloatLinearPTQ.from_linear(fc, FP8_E4M3_fn, FP8_E4M3_fn, None, "XqWqB", backend)
         return (lambda: layer(x)), 2.0 * M * N * K
 
-    cases = {"minifloat_qdq_f32": minifloat_qdq_f32}
+    def quant_pack_case():
+        """activation -> left operand of the block-scaled GEMM in one pass (bf16 [16384, 8192], MXFP8 E4M3)"""
+        from mase_triton_b200.mxfp import gemm as G
+        x = synthetic.cfg3_mxfp4_bf16(shape=(16384, 8192)).to(dev)
+        return (lambda: G.quantize_pack_fused(x, MXFP8_E4M3_fn)), x.numel() * (2 + 1 + 1 / 32)
+
+    cases = {"minifloat_qdq_f32": minifloat_qdq_f32, "mx_quant_pack_bf16": quant_pack_case}
     for backend in ("fused", "separate"):
         cases[f"mx_minifloat_linear_{backend}_cfg4"] = (lambda b=backend: minifloat_linear_case(8192, 14336, 4096, b))
     for which in ("extract", "qdq"):
@@ -674,7 +690,7 @@ def small_cases():
             cases[f"mxfp8_{which}_dim0_{route}_f32"] = (lambda w=which, r=route: strided_case(synthetic.cfg1_mxfp8_fp32, MXFP8_E4M3_fn, 4, w, r))
             cases[f"mxfp4_{which}_dim0_{route}_bf16"] = (lambda w=which, r=route: strided_case(synthetic.cfg3_mxfp4_bf16, OCP_MXFP4_E2M1, 2, w, r))
     cases["mx_gemm_gather_local_cfg4"] = (lambda: gemm_case(8192, 14336, 4096, "gather_local"))
-    for which in ("gemm", "linear", "separate", "xwq", "dense"):
+    for which in ("gemm", "linear", "separate", "xwq", "xwq_loader", "dense"):
         cases[f"mx_{which}_small"] = (lambda w=which: gemm_case(2048, 4096, 4096, w))
         cases[f"mx_{which}_cfg4"] = (lambda w=which: gemm_case(8192, 14336, 4096, w))
     for which in ("extract", "compose", "qdq"):

@@ -50,13 +50,13 @@ struct FmtRT {
 // memory: the compiler cannot fold k, so it emits an integer multiply-add, which issues on the
 // fp32/FMA pipe instead of the (saturated) integer ALU pipe.
 #if defined(__CUDACC__)
-static __constant__ int mxq_rt_k[10] = {1, 4, 256, 65536, 1 << 24, 1 << 20, 1 << 21, 1 << 22, 0, 64};
+static __constant__ int mxq_rt_k[12] = {1, 4, 256, 65536, 1 << 24, 1 << 20, 1 << 21, 1 << 22, 0, 64, 16, 32};
 #endif
 MXQ_HD int rt_k(int i) {
 #if defined(__CUDA_ARCH__)
     return mxq_rt_k[i];
 #else
-    return i == 0 ? 1 : i == 1 ? 4 : i == 2 ? 256 : i == 3 ? 65536 : i == 4 ? (1 << 24) : i <= 7 ? (1 << (15 + i)) : i == 9 ? 64 : 0;
+    return i == 0 ? 1 : i == 1 ? 4 : i == 2 ? 256 : i == 3 ? 65536 : i == 4 ? (1 << 24) : i <= 7 ? (1 << (15 + i)) : i == 9 ? 64 : i == 10 ? 16 : i == 11 ? 32 : 0;
 #endif
 }
 // 2^(23 - fb) for fb = 1..3 as a run-time factor (entries 7, 6, 5)

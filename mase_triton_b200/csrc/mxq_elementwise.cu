@@ -296,6 +296,172 @@ __device__ __forceinline__ void pk_bf16_quantise(const Pack<16>& p, const E2M1Bl
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// bf16 inputs: what the lanes of a block share, and the short form of the quantiser for the 8-bit formats.
+//   * every lane keeps the packed maximum AND minimum of its eight |x| (NaN wins the maximum); the maxima are
+//     reduced over the block's lanes as packed pairs, the two halves are only compared on the lane that derives the header;
+//   * that lane also derives the packed constants the block's lanes need and hands them over in one word:
+//     2^-se and a second bf16 threshold (its own per format, see bf16_block_word);
+//   * E4M3 / E5M2: when every |x| of the lanes that vote together is at least 2^(1-bias+se) -- no element in the
+//     sub-range, none flushed or rounding to zero, which is nearly always so for these formats -- the code is
+//     built from the SIGNED quotient with no per-element case analysis: exponent field and rounded fraction
+//     OR-ed per word, the re-bias (one XOR) and the sign bits (one byte gather) applied to four packed codes
+//     at a time.  Otherwise the lanes take pk_bf16_quantise, which handles every case.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void bf16_abs_range(const Pack<16>& p, uint32_t& mx2, uint32_t& mn2) {
+    const __nv_bfloat162 a0 = __habs2(bf2(p.w[0])), a1 = __habs2(bf2(p.w[1])), a2 = __habs2(bf2(p.w[2])), a3 = __habs2(bf2(p.w[3]));
+    mx2 = bf2_bits(__hmax2_nan(__hmax2_nan(a0, a1), __hmax2_nan(a2, a3)));
+    mn2 = bf2_bits(__hmin2(__hmin2(a0, a1), __hmin2(a2, a3)));
+}
+
+// fp32 bits of the larger half of a packed pair of bf16 magnitudes; NaN wins
+__device__ __forceinline__ uint32_t bf16x2_max_bits(uint32_t m2) {
+    return __float_as_uint(max_abs_nan(__uint_as_float(m2 << 16), __uint_as_float(m2 & 0xFFFF0000u)));
+}
+
+// Low half: bf16 bits of 2^-se.  High half, by format: E2M1 -- the keep threshold (e2m1_block's ts2); E4M3 / E5M2 --
+// 2^(1-bias+se), the smallest |x| of the short form (+Inf, i.e. never, for blocks so small that flushed inputs
+// could lie above it); others: unused.  Bit 31: the block holds Inf / NaN.
+template <class F>
+__device__ __forceinline__ uint32_t bf16_block_word(uint32_t hdr) {
+    const int sb = (int)((hdr >> 8) & 0xFFu);
+    uint32_t second = 0u;
+    if constexpr (F{}.eb() == 2 && F{}.fb() == 1) {
+        second = (uint32_t)max((sb - 150) * 128, 0x7F);
+    } else if constexpr (PkFmt<F>::RARE_SUBRANGE) {
+        const int e = sb + 1 - PkFmt<F>::BIAS;
+        second = e >= 2 ? (uint32_t)e << 7 : 0x7F80u;
+    }
+    return ((hdr >> 16) & 0x7F80u) | (second << 16) | (hdr << 31);
+}
+
+// short form (see above): 8 bf16 inputs of a lane -> 8 code bytes (out[0..2)) or 8 bf16 results (out[0..4))
+template <class F, bool VALUES>
+__device__ __forceinline__ void pk_bf16_quantise_normal(const Pack<16>& p, uint32_t inv2, uint32_t sf2, uint32_t* out) {
+    using P = PkFmt<F>;
+    static_assert(P::EB + P::FB == 7, "the sign gather assumes 8-bit codes");
+    uint32_t qb[4], r[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        qb[i] = bf2_bits(__hmul2(bf2(p.w[i]), bf2(inv2)));                  // signed quotient
+        const uint32_t sum = bf2_bits(__hadd2(bf2((qb[i] & 0x007F007Fu) | 0x3F803F80u), bf2(P::ROUND_C)));
+        if constexpr (VALUES) {
+            // (sum - SUM_BASE) << (7 - fb) as one multiply-add; OR-ed under the quotient's sign and exponent, times 2^se
+            const uint32_t z = sum * (uint32_t)rt_k(P::FB == 3 ? 10 : 11) - P::SUM_BASE * (1u << (7 - P::FB));
+            r[i] = bf2_bits(__hmul2(bf2((qb[i] & 0xFF80FF80u) | z), bf2(sf2)));
+        } else {
+            const uint32_t fr = sum * (uint32_t)rt_k(0) - P::SUM_BASE;       // 0 .. 2^fb in each half
+            r[i] = ((qb[i] >> (7 - P::FB)) & P::EXP_MASK) | fr;             // exponent field not re-biased yet
+        }
+    }
+    if constexpr (VALUES) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) out[i] = r[i];
+    } else {
+        constexpr uint32_t FLIP4 = ((1u << (P::EB - 1)) << P::FB) * 0x01010101u;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const uint32_t mag4 = __byte_perm(r[2 * i], r[2 * i + 1], 0x6420) ^ FLIP4;
+            const uint32_t sgn4 = __byte_perm(qb[2 * i], qb[2 * i + 1], 0x7531);        // the halves' upper bytes: sign on top
+            out[i] = mag4 | (sgn4 & 0x80808080u);
+        }
+    }
+}
+
+// One 16-byte access of a lane of a finite block, every format: picks the short form where it applies.
+// `w2` is the block word, `mn2` this lane's packed minimum, `h` the block header (only read on the full path).
+template <class F, bool VALUES>
+__device__ __forceinline__ void bf16_quantise_access(const Pack<16>& p, uint32_t w2, uint32_t mn2, uint32_t h, uint32_t sf2, uint32_t* out) {
+    const uint32_t inv2 = __byte_perm(w2, 0u, 0x1010);
+    const uint32_t second2 = __byte_perm(w2, 0u, 0x3232);
+    if constexpr (F{}.eb() == 2 && F{}.fb() == 1) {
+        // (a vote that skips the keep threshold when no lane holds an element at or below it was measured: no gain)
+        E2M1Block b;
+        b.inv2 = inv2; b.sf2 = sf2; b.ts2 = second2;
+        e2m1_bf16_quantise<VALUES>(p, b, out);
+    } else if constexpr (PkFmt<F>::RARE_SUBRANGE) {
+        const bool any_below = __any_sync(__activemask(), __hlt2_mask(bf2(mn2), bf2(second2)) != 0u);
+        if (!any_below) pk_bf16_quantise_normal<F, VALUES>(p, inv2, sf2, out);
+        else pk_bf16_quantise<F, VALUES>(p, e2m1_block(h), out);
+    } else {
+        pk_bf16_quantise<F, VALUES>(p, e2m1_block(h), out);
+    }
+}
+
+// bf16 inputs: the tile of mxfp_b32_quant_kernel (8 elements per lane per access, 4 lanes per block)
+template <class F, int U, int MODE, bool FULL>
+__device__ __forceinline__ void mxfp_b32_quant_tile_bf16(const char* __restrict__ src, uint8_t* __restrict__ scales,
+                                                         char* __restrict__ dst, int64_t first, int64_t left, const F& f) {
+    constexpr bool WRITE_CODES = (MODE != MODE_QDQ);
+    constexpr int V = 8, G = 4;
+    static_assert(U <= G, "one lane of the group per in-flight access");
+    constexpr int OB = WRITE_CODES ? V : 16;
+    const int lane = threadIdx.x & 31;
+    const int sub = lane & (G - 1);
+
+    Pack<16> p[U];
+    uint32_t mx2[U], mn2[U];
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+        if (FULL || j * kThreads < left) p[j] = load_pack<16>(src + (size_t)j * kThreads * 16);
+        else p[j] = Pack<16>{{0u, 0u, 0u, 0u}};
+    }
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+        bf16_abs_range(p[j], mx2[j], mn2[j]);
+#pragma unroll
+        for (int o = 1; o < G; o <<= 1) mx2[j] = bf2_bits(__hmax2_nan(bf2(mx2[j]), bf2(__shfl_xor_sync(0xFFFFFFFFu, mx2[j], o))));
+    }
+    // lane `sub` of each group derives the header and the block word of access `sub`
+    uint32_t mine = mx2[0];
+#pragma unroll
+    for (int j = 1; j < U; ++j) mine = (sub == j) ? mx2[j] : mine;
+    const uint32_t hdr = block_header(bf16x2_max_bits(mine), f);
+    const uint32_t word = bf16_block_word<F>(hdr);
+    const uint32_t sb = (hdr >> 8) & 0xFFu;
+    const uint32_t sf2_mine = (sb == 0u ? 0x0040u : (sb << 7)) * 0x10001u;
+    if (MODE == MODE_CODES && sub < U && (FULL || sub * kThreads < left))
+        scales[(first + sub * kThreads) / G] = (uint8_t)sb;
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+        const int owner = (lane & ~(G - 1)) + j;
+        const uint32_t h = __shfl_sync(0xFFFFFFFFu, hdr, owner);
+        const uint32_t w2 = __shfl_sync(0xFFFFFFFFu, word, owner);
+        uint32_t sf2 = 0u;
+        if constexpr (MODE == MODE_QDQ) sf2 = __shfl_sync(0xFFFFFFFFu, sf2_mine, owner);
+        if (!FULL && j * kThreads >= left) continue;
+        char* d = dst + (size_t)j * kThreads * OB;
+        if (!(h & 1u)) {
+            if constexpr (MODE == MODE_QDQ) {
+                Pack<16> o;
+                bf16_quantise_access<F, true>(p[j], w2, mn2[j], h, sf2, o.w);
+                store_pack<16>(d, o);
+            } else {
+                Pack<V> o;
+                bf16_quantise_access<F, false>(p[j], w2, mn2[j], h, sf2, o.w);
+                store_pack<V>(d, o);
+            }
+        } else {
+            // Inf / NaN block: the generic codec with the reference's fixed exponent
+            uint32_t code[V];
+#pragma unroll
+            for (int i = 0; i < V; ++i) code[i] = mx_encode(pack_bits<KBF16>(p[j], i), 128, f);
+            if constexpr (WRITE_CODES) {
+                Pack<V> o;
+#pragma unroll
+                for (int i = 0; i < V; ++i) pack_set<1>(o, i, code[i]);
+                store_pack<V>(d, o);
+            } else {
+                const float sf = scale_from_byte((h >> 8) & 0xFFu);
+                uint32_t y[V];
+#pragma unroll
+                for (int i = 0; i < V; ++i) y[i] = mx_decode(code[i], sf, f);
+                store_results<KBF16, V>(d, y, false);
+            }
+        }
+    }
+}
+
 template <class KIn, class F, int U, int MODE, bool FULL>
 __device__ __forceinline__ void mxfp_b32_quant_tile(const char* __restrict__ src, uint8_t* __restrict__ scales,
                                                     char* __restrict__ dst, int64_t first, int64_t left, const F& f) {
@@ -337,37 +503,6 @@ __device__ __forceinline__ void mxfp_b32_quant_tile(const char* __restrict__ src
         const uint32_t h = __shfl_sync(0xFFFFFFFFu, hdr, (lane & ~(G - 1)) + j);
         if (!FULL && j * kThreads >= left) continue;
         char* d = dst + (size_t)j * kThreads * OB;
-        if constexpr (std::is_same<KIn, KBF16>::value && !(F{}.eb() == 2 && F{}.fb() == 1)) {
-            // bf16 inputs, 8- and 6-bit element formats: packed bf16 arithmetic, two elements per word
-            if (!(h & 1u)) {
-                const E2M1Block b = e2m1_block(h);
-                if constexpr (MODE == MODE_QDQ) {
-                    Pack<16> o;
-                    pk_bf16_quantise<F, true>(p[j], b, o.w);
-                    store_pack<16>(d, o);
-                } else {
-                    Pack<V> o;
-                    pk_bf16_quantise<F, false>(p[j], b, o.w);
-                    store_pack<V>(d, o);
-                }
-                continue;
-            }
-        }
-        if constexpr (std::is_same<KIn, KBF16>::value && F{}.eb() == 2 && F{}.fb() == 1) {
-            if (!(h & 1u)) {
-                const E2M1Block b = e2m1_block(h);
-                if constexpr (WRITE_CODES) {
-                    Pack<V> o;
-                    e2m1_bf16_quantise<false>(p[j], b, o.w);
-                    store_pack<V>(d, o);
-                } else {
-                    Pack<16> o;
-                    e2m1_bf16_quantise<true>(p[j], b, o.w);
-                    store_pack<16>(d, o);
-                }
-                continue;
-            }
-        }
         if constexpr (MODE == MODE_QDQ) {
             if (!(h & 1u)) {
                 const float inv = __uint_as_float(h & 0x7F800000u);
@@ -458,10 +593,14 @@ __global__ void __launch_bounds__(kThreads) mxfp_b32_quant_kernel(const void* __
     const int64_t first = (int64_t)blockIdx.x * (kThreads * U) + threadIdx.x;
     const char* src = reinterpret_cast<const char*>(x) + first * 16;
     char* dst = MODE != MODE_QDQ ? reinterpret_cast<char*>(elements) + first * V : reinterpret_cast<char*>(out) + first * 16;
-    if ((int64_t)(blockIdx.x + 1) * (kThreads * U) <= n_vec)
-        mxfp_b32_quant_tile<KIn, F, U, MODE, true>(src, scales, dst, first, 0, f);
-    else
-        mxfp_b32_quant_tile<KIn, F, U, MODE, false>(src, scales, dst, first, n_vec - first, f);
+    const bool full = (int64_t)(blockIdx.x + 1) * (kThreads * U) <= n_vec;
+    if constexpr (std::is_same<KIn, KBF16>::value) {
+        if (full) mxfp_b32_quant_tile_bf16<F, U, MODE, true>(src, scales, dst, first, 0, f);
+        else mxfp_b32_quant_tile_bf16<F, U, MODE, false>(src, scales, dst, first, n_vec - first, f);
+    } else {
+        if (full) mxfp_b32_quant_tile<KIn, F, U, MODE, true>(src, scales, dst, first, 0, f);
+        else mxfp_b32_quant_tile<KIn, F, U, MODE, false>(src, scales, dst, first, n_vec - first, f);
+    }
 }
 
 template <class KOut, class F, int U>
@@ -755,8 +894,9 @@ __global__ void __launch_bounds__(kThreads) mx_quant_pack_flat_kernel(const void
     const int64_t first = (int64_t)blockIdx.x * (kThreads * U) + threadIdx.x;
     const F f{};
     constexpr uint32_t probe = (F{}.eb() == 4) ? 0x01010101u : 0x04040404u;    // carry out of the magnitude byte: a code the hardware reads as NaN / Inf
+    constexpr bool BF16 = std::is_same<KIn, KBF16>::value;
     Pack<16> p[U];
-    uint32_t amax[U];
+    uint32_t amax[U], amin[U];             // bf16: packed pairs (see bf16_abs_range); else fp32 bits of the maximum
 #pragma unroll
     for (int j = 0; j < U; ++j) {
         const int64_t vec = first + (int64_t)j * kThreads;
@@ -764,25 +904,38 @@ __global__ void __launch_bounds__(kThreads) mx_quant_pack_flat_kernel(const void
     }
 #pragma unroll
     for (int j = 0; j < U; ++j) {
-        float m = __uint_as_float(pack_absmax_bits<KIn>(p[j]));
+        if constexpr (BF16) {
+            bf16_abs_range(p[j], amax[j], amin[j]);
 #pragma unroll
-        for (int o = 1; o < G; o <<= 1) m = max_abs_nan(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
-        amax[j] = __float_as_uint(m);
+            for (int o = 1; o < G; o <<= 1) amax[j] = bf2_bits(__hmax2_nan(bf2(amax[j]), bf2(__shfl_xor_sync(0xFFFFFFFFu, amax[j], o))));
+        } else {
+            float m = __uint_as_float(pack_absmax_bits<KIn>(p[j]));
+#pragma unroll
+            for (int o = 1; o < G; o <<= 1) m = max_abs_nan(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+            amax[j] = __float_as_uint(m);
+            amin[j] = 0u;
+        }
     }
     // lane `sub` of each group derives the header of access `sub` (U <= G)
     uint32_t mine = amax[0];
 #pragma unroll
     for (int j = 1; j < U; ++j) mine = (sub == j) ? amax[j] : mine;
-    const uint32_t hdr = block_header(mine, f);
+    const uint32_t hdr = block_header(BF16 ? bf16x2_max_bits(mine) : mine, f);
+    const uint32_t word = BF16 ? bf16_block_word<F>(hdr) : 0u;
+    uint32_t sb_of[U];
 #pragma unroll
     for (int j = 0; j < U; ++j) {
-        const uint32_t h = __shfl_sync(0xFFFFFFFFu, hdr, (lane & ~(G - 1)) + j);
+        const int owner = (lane & ~(G - 1)) + j;
+        const uint32_t h = __shfl_sync(0xFFFFFFFFu, hdr, owner);
+        uint32_t w2 = 0u;
+        if constexpr (BF16) w2 = __shfl_sync(0xFFFFFFFFu, word, owner);
         const int64_t vec = first + (int64_t)j * kThreads;
         Pack<V> o;
         uint32_t sbyte = (h >> 8) & 0xFFu;
+        uint32_t bad = 0;                       // non-zero: a code of this lane is one the hardware reads as NaN / Inf
         if (!(h & 1u)) {
-            if constexpr (std::is_same<KIn, KBF16>::value) {
-                pk_bf16_quantise<F, false>(p[j], e2m1_block(h), o.w);
+            if constexpr (BF16) {
+                bf16_quantise_access<F, false>(p[j], w2, amin[j], h, 0u, o.w);
             } else {
                 const float inv = __uint_as_float(h & 0x7F800000u);
                 uint32_t qb[V], mag[V];
@@ -794,32 +947,42 @@ __global__ void __launch_bounds__(kThreads) mx_quant_pack_flat_kernel(const void
 #pragma unroll
                 for (int i = 0; i < V; i += 4) o.w[i >> 2] = pack4_codes(&mag[i], &qb[i], f);
             }
-            uint32_t bad = 0;
 #pragma unroll
             for (int i = 0; i < V / 4; ++i) bad |= ((o.w[i] & 0x7F7F7F7Fu) + probe) & 0x80808080u;
-            // only the lanes of this block vote: another group of the warp may hold an Inf/NaN block
-            const uint32_t group_mask = ((G == 8) ? 0xFFu : 0xFu) << (lane & ~(G - 1));
-            if (__any_sync(group_mask, bad != 0u)) {
-#pragma unroll
-                for (int i = 0; i < V / 4; ++i) o.w[i] = halve_codes4<F{}.fb()>(o.w[i]);
-                if (sbyte < 255u) sbyte += 1u;
-            }
         } else {
             // Inf/NaN block: scale byte 255 is NaN for the tensor cores too; the codes do not matter
 #pragma unroll
             for (int i = 0; i < V / 4; ++i) o.w[i] = 0u;
             sbyte = 255u;
         }
-        if (vec < n_vec) store_pack<V>(hw_codes + vec * V, o);
-        const uint32_t blk = (uint32_t)(vec / G);
-        if constexpr (WORDS) {
-            // blocks blk .. blk + 3 (blk % 4 == 0) are K blocks 0 .. 3 of one row and one 128-column step
-            uint32_t w = sbyte | (__shfl_down_sync(0xFFFFFFFFu, sbyte, G) << 8);        // this block and the next
-            w |= __shfl_down_sync(0xFFFFFFFFu, w, 2 * G) << 16;                             // ... and the pair after them
-            if ((lane & (4 * G - 1)) == 0 && vec < n_vec) *reinterpret_cast<uint32_t*>(hw_sf + sf_chunk_offset(blk, geom)) = w;
-        } else {
-            if (sub == 0 && vec < n_vec) hw_sf[sf_chunk_offset(blk, geom)] = (uint8_t)sbyte;
+        // the lanes of a block agree with xor-shuffles that every lane of the warp executes (a vote with a mask per
+        // group compiles to a loop over the groups); lanes of Inf/NaN blocks contribute nothing
+#pragma unroll
+        for (int w = 1; w < G; w <<= 1) bad |= __shfl_xor_sync(0xFFFFFFFFu, bad, w);
+        if (bad != 0u) {
+#pragma unroll
+            for (int i = 0; i < V / 4; ++i) o.w[i] = halve_codes4<F{}.fb()>(o.w[i]);
+            if (sbyte < 255u) sbyte += 1u;
         }
+        if (vec < n_vec) store_pack<V>(hw_codes + vec * V, o);
+        sb_of[j] = sbyte;
+    }
+    // lane `sub` of each group stores the scale byte of access `sub`, so that the position in the chunked array is
+    // worked out once per lane instead of once per access
+    uint32_t sb_mine = sb_of[0];
+#pragma unroll
+    for (int j = 1; j < U; ++j) sb_mine = (sub == j) ? sb_of[j] : sb_mine;
+    const int64_t vec_mine = first - sub + (int64_t)(sub < U ? sub : 0) * kThreads;      // first lane of the group, access `sub`
+    const bool mine_ok = sub < U && vec_mine < n_vec;
+    const uint32_t blk = (uint32_t)(vec_mine / G);
+    if constexpr (WORDS) {
+        // blocks blk .. blk + 3 (blk % 4 == 0: the groups 0..3 or 4..7 of the warp) are K blocks 0 .. 3 of one row and
+        // one 128-column step; their bytes are adjacent in the chunk: gather them from the lanes G, 2G, 3G further on
+        uint32_t w = sb_mine | (__shfl_down_sync(0xFFFFFFFFu, sb_mine, G) << 8);
+        w |= __shfl_down_sync(0xFFFFFFFFu, w, 2 * G) << 16;
+        if ((lane & (4 * G - 1)) < G && mine_ok) *reinterpret_cast<uint32_t*>(hw_sf + sf_chunk_offset(blk, geom)) = w;
+    } else {
+        if (mine_ok) hw_sf[sf_chunk_offset(blk, geom)] = (uint8_t)sb_mine;
     }
 }
 

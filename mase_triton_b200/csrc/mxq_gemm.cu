@@ -51,7 +51,7 @@ template <int MH> struct Cfg {
     static constexpr int A_BYTES = BM * BK;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SF_REGION;       // multiple of 1024
     static constexpr int STAGES = MH == 2 ? 3 : 4;
-    static constexpr int TX_FIXED = A_BYTES + MH * 512 + 1024;       // + bn * BK for the right operand's codes
+    static constexpr int TX_FIXED = A_BYTES + MH * 512 + 1024;       // + the bytes of bn * BK codes of the right operand
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;   // + slack to align the ring
     static constexpr int SMEM_BYTES_TMA = SMEM_BYTES + EPI_TMA_WARPS * EPI_SLOT_BYTES;   // + staging of the asynchronous epilogue
 };
@@ -141,7 +141,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int KT = (K + BK - 1) / BK;
     const int MT = (M + C::BM - 1) / C::BM, NT = (N + bn - 1) / bn;
     const int num_tiles = MT * NT;
-    const uint32_t tx_bytes = (uint32_t)(C::TX_FIXED + bn * BK);
+    // the right operand's copy counts the bytes it reads: dense 6-bit (formats 3, 4) and 4-bit (5) codes are narrower
+    const uint32_t b_fmt = (idesc_base >> 10) & 7u;
+    const uint32_t b_bits = b_fmt <= 1u ? 8u : (b_fmt == 5u ? 4u : 6u);
+    const uint32_t tx_bytes = (uint32_t)C::TX_FIXED + (uint32_t)(bn * BK) * b_bits / 8u;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -386,6 +389,10 @@ __global__ void __launch_bounds__(256) mx_pack_kernel(const uint8_t* __restrict_
     uint8_t* sf_dst = hw_sf + ((tile * KT + kb / 4) * 2 + lr / 128) * 512 + (in_chunk % 32) * 16 + (in_chunk / 32) * 4 + (kb % 4);
     if (lr >= tile_rows || r >= rows || kb >= kb_per_row) { *sf_dst = 127; return; }   // padding: scale 1.0 (codes there are TMA zero fill)
     const int64_t blk = r * kb_per_row + kb;
+    if (hw_codes == nullptr) {                        // scale chunks only: the codes keep their own (sub-byte) format
+        *sf_dst = scales != nullptr ? scales[blk] : (uint8_t)127;
+        return;
+    }
     // `elements` and `hw_codes` may be the same buffer: the whole block is read before it is written
     const uint4* src = reinterpret_cast<const uint4*>(elements + blk * 32);
     uint4 c[2] = {src[0], src[1]};
@@ -445,14 +452,29 @@ static bool build_pack_tables(int eb, int fb, PackTables* t, int* hw_fmt) {
     return true;
 }
 
-static bool make_operand_map(CUtensorMap* map, const void* codes, int64_t rows, int64_t K, int box_rows) {
+// hardware operand formats (the instruction descriptor's encoding): one byte per code for the 8-bit formats; the
+// 6- and 4-bit formats are dense bit streams in memory that TMA spreads to 16 codes per 16 bytes of shared memory
+constexpr int HW_E4M3 = 0, HW_E5M2 = 1, HW_E2M3 = 3, HW_E3M2 = 4, HW_E2M1 = 5;
+static int hw_code_bits(int hw_format) {
+    switch (hw_format) {
+        case HW_E4M3: case HW_E5M2: return 8;
+        case HW_E2M3: case HW_E3M2: return 6;
+        case HW_E2M1: return 4;
+        default: return 0;
+    }
+}
+
+static bool make_operand_map(CUtensorMap* map, const void* codes, int64_t rows, int64_t K, int box_rows, int hw_format = HW_E4M3) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)K};
+    const int bits = hw_code_bits(hw_format);
+    const CUtensorMapDataType dt = bits == 8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : bits == 6 ? CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};                  // in codes, whatever their width
+    const cuuint64_t strides[1] = {(cuuint64_t)(K * bits / 8)};
     const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(codes), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    return fn(map, dt, 2, const_cast<void*>(codes), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -467,7 +489,7 @@ static int launch_gemm(const uint8_t* a_codes, const uint8_t* b_codes, const uin
     const cudaError_t attr_err = raise_smem_limit(mx_gemm_kernel<OUT_DT, MH, EPI>, SMEM, attr_done);
     if (attr_err != cudaSuccess) { set_last_cuda_error(attr_err); return MXQ_ELAUNCH; }
     CUtensorMap ma, mb;
-    if (!make_operand_map(&ma, a_codes, M, K, C::BM) || !make_operand_map(&mb, b_codes, N, K, bn)) return MXQ_ELAUNCH;
+    if (!make_operand_map(&ma, a_codes, M, K, C::BM) || !make_operand_map(&mb, b_codes, N, K, bn, (int)((idesc >> 10) & 7u))) return MXQ_ELAUNCH;
     const int tiles = ((M + C::BM - 1) / C::BM) * ((N + bn - 1) / bn);
     const int grid = tiles < sm_count() ? tiles : sm_count();          // persistent: one CTA per SM
     mx_gemm_kernel<OUT_DT, MH, EPI><<<grid, kernel_threads<EPI>(), SMEM, st>>>(ma, mb, sfa, sfb, out, bias, M, N, K, bn, idesc, status,
@@ -513,6 +535,16 @@ using namespace mxq;
 // rows per scale-factor tile: 256 for the left operand; for the right one the CTA tile width it will be multiplied with
 static int sf_tile_rows(int operand, int tile_rows) { return operand == MXQ_OPERAND_A ? gemm::A_TILE_ROWS : gemm::resolve_b_tile(tile_rows); }
 
+// the left operand is one byte per code; the right one may also be a dense 6- or 4-bit stream (whole 128-code K steps,
+// 32-byte aligned rows: what the packed tensor-map types ask for)
+static bool operand_formats_ok(int a_hw_format, int b_hw_format, const uint8_t* b_codes, int64_t K) {
+    if (a_hw_format != gemm::HW_E4M3 && a_hw_format != gemm::HW_E5M2) return false;
+    const int bits = gemm::hw_code_bits(b_hw_format);
+    if (bits == 0) return false;
+    if (bits != 8 && (K % 128 != 0 || reinterpret_cast<uintptr_t>(b_codes) % 32 != 0)) return false;
+    return true;
+}
+
 extern "C" int mxq_mx_best_tile_rows(int64_t N) {
     // fewest padded columns first, the wider tile on a tie; widths below 160 only cost arithmetic intensity
     if (N <= 0) return gemm::BN_MAX;
@@ -545,12 +577,35 @@ extern "C" int mxq_mx_pack_operand(const uint8_t* scales, const uint8_t* element
     return check_launch();
 }
 
+extern "C" int mxq_mx_pack_operand_native(const uint8_t* scales, const uint8_t* elements, int64_t rows, int64_t K, int eb, int fb,
+                                          int tile_rows, uint8_t* hw_codes, uint8_t* hw_sf, int* hw_format, void* stream) {
+    if (rows <= 0 || K <= 0 || !elements || !hw_codes || !hw_sf || !hw_format) return MXQ_EINVAL;
+    int fmt;
+    if (eb == 2 && fb == 3) fmt = gemm::HW_E2M3;
+    else if (eb == 3 && fb == 2) fmt = gemm::HW_E3M2;
+    else if (eb == 2 && fb == 1) fmt = gemm::HW_E2M1;
+    else return MXQ_ESIZE;
+    if (K % 128 != 0 || reinterpret_cast<uintptr_t>(hw_codes) % 32 != 0 || reinterpret_cast<uintptr_t>(elements) % 16 != 0) return MXQ_ESIZE;
+    const int tile = sf_tile_rows(MXQ_OPERAND_B, tile_rows);
+    if (tile <= 0) return MXQ_EINVAL;
+    // the reference's code bytes are the hardware's codes (sign, exponent, fraction in the low bits, the same subnormals,
+    // no Inf / NaN): only the scale bytes move, and the codes are squeezed to their width
+    const int64_t total = ((rows + tile - 1) / tile) * 256 * ((K / 128) * 4);
+    gemm::mx_pack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(scales, elements, nullptr, hw_sf, rows, K, tile,
+                                                                                          gemm::PackTables{});
+    int rc = check_launch();
+    if (rc != MXQ_OK) return rc;
+    rc = mxq_pack_codes(elements, hw_codes, rows * K, gemm::hw_code_bits(fmt), stream);
+    if (rc == MXQ_OK) *hw_format = fmt;
+    return rc;
+}
+
 extern "C" int mxq_mx_gemm(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw_format, const uint8_t* b_codes,
                            const uint8_t* b_sf, int b_hw_format, int b_tile_rows, void* out, int out_dtype, const void* bias,
                            int64_t M, int64_t N, int64_t K, int* status, void* stream) {
     if (M <= 0 || N <= 0 || K <= 0 || K % 32 != 0 || M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return MXQ_EINVAL;
     if (!a_codes || !a_sf || !b_codes || !b_sf || !out) return MXQ_EINVAL;
-    if ((a_hw_format | b_hw_format) & ~1) return MXQ_EINVAL;
+    if (!operand_formats_ok(a_hw_format, b_hw_format, b_codes, K)) return MXQ_EINVAL;
     const int bn = gemm::resolve_b_tile(b_tile_rows);
     if (bn <= 0) return MXQ_EINVAL;
     if ((reinterpret_cast<uintptr_t>(a_codes) | reinterpret_cast<uintptr_t>(b_codes) | reinterpret_cast<uintptr_t>(a_sf) |
@@ -569,7 +624,7 @@ extern "C" int mxq_mx_gemm_gather(const uint8_t* a_codes, const uint8_t* a_sf, i
                                   int* status, void* stream) {
     if (M <= 0 || N <= 0 || K <= 0 || K % 32 != 0 || M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return MXQ_EINVAL;
     if (!a_codes || !a_sf || !b_codes || !b_sf || !outs || n_outs < 1 || n_outs > gemm::MAX_DEST || self_index < 0 || self_index >= n_outs) return MXQ_EINVAL;
-    if ((a_hw_format | b_hw_format) & ~1) return MXQ_EINVAL;
+    if (!operand_formats_ok(a_hw_format, b_hw_format, b_codes, K)) return MXQ_EINVAL;
     const int bn = gemm::resolve_b_tile(b_tile_rows);
     if (bn <= 0) return MXQ_EINVAL;
     if (col_offset < 0 || ld_out < col_offset + N) return MXQ_EINVAL;

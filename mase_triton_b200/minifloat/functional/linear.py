@@ -68,7 +68,8 @@ def _fused_linear(x: Tensor, x_meta: MinifloatMeta, w_element: Tensor, w_tensor_
 def _tc_linear(x: Tensor, x_meta, w: Tensor | None, w_element: Tensor | None, w_tensor_meta, bias: Tensor | None, kind) -> Tensor:
     """``backend="fused"`` for the layer types that are not "both operands as 8-bit tensor-core codes":
     ``tcgen05.mma.kind::f16`` GEMM on bf16 / fp16 activations; an ``Xq`` activation is fake-quantised by
-    one kernel first, ``Wq`` codes are expanded inside the GEMM's operand loader."""
+    one kernel first, ``Wq`` codes are expanded inside the GEMM's operand loader while the activation is short and
+    once by the compose kernel otherwise (``tc_linear.expand_in_loader``)."""
     from ... import tc_linear
 
     reason = tc_linear.why_not(x, x.shape[-1])
@@ -81,7 +82,8 @@ def _tc_linear(x: Tensor, x_meta, w: Tensor | None, w_element: Tensor | None, w_
     if getattr(torch, w_tensor_meta.dtype) != x.dtype:
         raise RuntimeError(f"the weight dequantises to {w_tensor_meta.dtype}, the input is {x.dtype}")
     shape = tuple(w_tensor_meta.shape)
-    if len(shape) == 2 and w_tensor_meta.meta.exp_bits <= 8 and w_element.dtype == torch.uint16:
+    if (len(shape) == 2 and w_tensor_meta.meta.exp_bits <= 8 and w_element.dtype == torch.uint16
+            and tc_linear.expand_in_loader(x.numel() // x.shape[-1], shape[0])):
         return tc_linear.minifloat_weight_linear(x, w_element, shape, w_tensor_meta.meta, bias)
     return tc_linear.dense_linear(x, compose_minifloat_component(w_element, w_tensor_meta).contiguous(), bias)
 

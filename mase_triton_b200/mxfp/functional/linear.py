@@ -48,8 +48,8 @@ def _fused_linear(x: Tensor, x_meta: MXFPMeta | None, w: Tensor | None, w_scales
       ``tcgen05.mma.kind::mxf8f6f4`` GEMM (fp32 / bf16 / fp16 activations);
     * every other combination on bf16 / fp16 activations: ``tcgen05.mma.kind::f16`` GEMM; an ``Xq``
       activation is fake-quantised by one bandwidth-bound kernel first, a ``Wq`` weight is expanded from
-      its codes inside the GEMM's operand loader (or, for block layouts that loader does not read,
-      dequantised first);
+      its codes inside the GEMM's operand loader while the activation is short, and once by the compose
+      kernel otherwise (``tc_linear.expand_in_loader``; also for block layouts that loader does not read);
     * anything else raises ``NotImplementedError`` as the reference's ``fused`` does -- nothing falls back to
       a library GEMM silently.
     """
@@ -68,7 +68,7 @@ def _fused_linear(x: Tensor, x_meta: MXFPMeta | None, w: Tensor | None, w_scales
         return tc_linear.dense_linear(x, w, bias)
     if getattr(torch, w_tensor_meta.dtype) != x.dtype:
         raise RuntimeError(f"the weight dequantises to {w_tensor_meta.dtype}, the input is {x.dtype}")
-    if w_blocks_along_k and K % 32 == 0:
+    if w_blocks_along_k and K % 32 == 0 and tc_linear.expand_in_loader(x.numel() // K, w_shape[0]):
         return tc_linear.mxfp_weight_linear(x, w_scales, w_elements, w_shape, w_tensor_meta.meta, bias)
     return tc_linear.dense_linear(x, compose_mxfp_tensor(w_scales, w_elements, w_tensor_meta).contiguous(), bias)
 

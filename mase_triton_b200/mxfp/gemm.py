@@ -26,9 +26,9 @@ _STATUS_TEXT = {1: "TMA producer wait ran out", 2: "MMA issuer wait ran out", 3:
 
 @dataclass
 class PackedOperand:
-    codes: Tensor        # uint8 [rows, K], hardware element codes
+    codes: Tensor        # uint8 [rows, K] hardware element codes ([rows, K * bits / 8] for the 6- / 4-bit formats)
     sf: Tensor           # uint8, hardware scale-factor chunks
-    hw_format: int       # 0 = E4M3, 1 = E5M2
+    hw_format: int       # 0 = E4M3, 1 = E5M2; right operand only: 3 = E2M3, 4 = E3M2, 5 = E2M1 as dense bit streams
     rows: int
     K: int
     operand: int         # 0: packed as the left operand (A), 1: as the right operand (B)
@@ -78,13 +78,23 @@ def check_status(device: torch.device) -> None:
 OPERAND_A, OPERAND_B = 0, 1
 
 
+def native_ok(exp_bits: int, frac_bits: int, K: int, operand: int) -> bool:
+    """Whether the tensor cores can read the codes in their own 6- / 4-bit width (right operand, FP6 / FP4 element
+    formats, whole 128-code K steps)."""
+    return operand == OPERAND_B and K % 128 == 0 and (exp_bits, frac_bits) in ((2, 3), (3, 2), (2, 1))
+
+
+NATIVE_SUBBYTE_DEFAULT = False
+
+
 def pack_codes(scales: Tensor | None, elements: Tensor, rows: int, K: int, exp_bits: int, frac_bits: int, operand: int,
-               tile_rows: int | None = None) -> PackedOperand:
+               tile_rows: int | None = None, native: bool | None = None) -> PackedOperand:
     """Element codes (one per byte, sign at bit ``exp_bits + frac_bits``) of a ``[rows, K]`` tensor and the
     E8M0 scales of its 32-element blocks along K (``None``: every scale is 2^0, i.e. per-tensor minifloat
     codes) -> ``PackedOperand`` for the left (``OPERAND_A``) or right (``OPERAND_B``) side of the GEMM.
     ``tile_rows`` (right operand only) is the CTA tile width; by default the one with the least padded
-    work for ``rows`` output features."""
+    work for ``rows`` output features.  ``native`` keeps FP6 / FP4 codes of a right operand at their own width
+    (a dense bit stream, three quarters / half of the bytes) instead of widening them to E4M3 bytes."""
     _lib.require_cuda(elements, "pack_operand")
     assert elements.dtype == torch.uint8 and K % 32 == 0 and elements.numel() == rows * K
     assert scales is None or (scales.dtype == torch.uint8 and scales.numel() == rows * K // 32)
@@ -96,9 +106,21 @@ def pack_codes(scales: Tensor | None, elements: Tensor, rows: int, K: int, exp_b
         tile_rows = 0
     elif tile_rows is None:
         tile_rows = L.mxq_mx_best_tile_rows(rows)
-    codes = torch.empty((rows, K), dtype=torch.uint8, device=dev)
+    if native is None:
+        native = NATIVE_SUBBYTE_DEFAULT
+    native = native and native_ok(exp_bits, frac_bits, K, operand)
     sf = torch.empty((L.mxq_mx_sf_bytes(rows, K, operand, tile_rows),), dtype=torch.uint8, device=dev)
     fmt = ctypes.c_int(0)
+    if native:
+        bits = 1 + exp_bits + frac_bits
+        codes = torch.empty((rows, K * bits // 8), dtype=torch.uint8, device=dev)
+        with torch.cuda.device(dev):
+            rc = L.mxq_mx_pack_operand_native(None if scales is None else scales.data_ptr(), elements.data_ptr(), rows, K, exp_bits,
+                                              frac_bits, tile_rows, codes.data_ptr(), sf.data_ptr(), ctypes.addressof(fmt),
+                                              _lib.stream_ptr(dev))
+        _lib.check(rc, "mxq_mx_pack_operand_native")
+        return PackedOperand(codes, sf, fmt.value, rows, K, operand, tile_rows)
+    codes = torch.empty((rows, K), dtype=torch.uint8, device=dev)
     with torch.cuda.device(dev):
         rc = L.mxq_mx_pack_operand(None if scales is None else scales.data_ptr(), elements.data_ptr(), rows, K, exp_bits, frac_bits,
                                    operand, tile_rows, codes.data_ptr(), sf.data_ptr(), ctypes.addressof(fmt), _lib.stream_ptr(dev))
@@ -107,11 +129,11 @@ def pack_codes(scales: Tensor | None, elements: Tensor, rows: int, K: int, exp_b
 
 
 def pack_operand(scales: Tensor, elements: Tensor, rows: int, K: int, meta: MXFPMeta, operand: int,
-                 tile_rows: int | None = None) -> PackedOperand:
+                 tile_rows: int | None = None, native: bool | None = None) -> PackedOperand:
     """Reference ``(scales, elements)`` of a ``[rows, K]`` tensor blocked along K -> ``PackedOperand``
     laid out for the left (``OPERAND_A``) or right (``OPERAND_B``) side of the GEMM."""
     assert supported(meta)
-    return pack_codes(scales, elements, rows, K, meta.element_exp_bits, meta.element_frac_bits, operand, tile_rows)
+    return pack_codes(scales, elements, rows, K, meta.element_exp_bits, meta.element_frac_bits, operand, tile_rows, native)
 
 
 def quantize_pack(x: Tensor, meta: MXFPMeta, operand: int = OPERAND_A, tile_rows: int | None = None) -> PackedOperand:

@@ -92,3 +92,14 @@ def minifloat_weight_linear(x: Tensor, w_element: Tensor, shape: tuple[int, int]
                                                      status_word(dev).data_ptr(), _lib.stream_ptr(dev))
     _lib.check(rc, "mxq_minifloat_weight_linear")
     return out.reshape(*x.shape[:-1], N)
+
+
+def expand_in_loader(rows: int, out_features: int) -> bool:
+    """Where a weight-only-quantised linear expands its codes.  Inside the GEMM's loader every 256-row tile of
+    the activation expands the weight again, so that route pays while the activation is at most two tiles tall and
+    the weight has enough column tiles to occupy the GPU (then the dense weight never exists in memory and the
+    codes are read once).  Taller activations expand the weight once with the compose kernel (same values bit
+    for bit) and run the same GEMM on dense operands: measured on B200 with a 14336 x 4096 MXFP8 weight,
+    0.080 / 0.155 / 0.98 ms in the loader against 0.085 / 0.128 / 0.65 ms expanded once at 512 / 1024 / 8192 rows."""
+    return rows <= 512 and out_features >= 8192
+

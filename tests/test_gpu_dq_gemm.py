@@ -247,3 +247,22 @@ def test_fused_activation_honours_round_mode(lib, round_mode, fmt):
     a = G.pack_activation(x.to(DEV), x_meta)
     b = G.quantize_pack(x.to(DEV), x_meta)
     assert torch.equal(a.codes, b.codes) and torch.equal(a.sf, b.sf)
+
+
+@pytest.mark.parametrize("kind", ["mxfp", "minifloat"])
+def test_weight_only_layer_routes_agree(lib, kind):
+    """A weight-only-quantised layer expands its codes inside the GEMM's loader for short activations of wide
+    layers and once (compose kernel + the same GEMM on dense operands) otherwise: both give the same bytes."""
+    torch.manual_seed(23)
+    N, K = 8192, 256
+    fc = torch.nn.Linear(K, N, bias=True, device=DEV, dtype=torch.bfloat16)
+    if kind == "mxfp":
+        layer = MXFPLinearPTQ.from_linear(fc, None, OCP_MXFP6_E3M2, None, "XWqB", backend="fused")
+    else:
+        layer = MinifloatLinearPTQ.from_linear(fc, None, FP8_E4M3_fn, None, "XWqB", backend="fused")
+    assert tc_linear.expand_in_loader(512, N) and not tc_linear.expand_in_loader(513, N) and not tc_linear.expand_in_loader(64, 4096)
+    x = torch.randn(768, K, device=DEV, dtype=torch.bfloat16)
+    tall = layer(x)                       # 768 rows: expanded once
+    short = layer(x[:512])                # 512 rows: expanded in the loader
+    G.check_status(DEV)
+    assert torch.equal(tall[:512], short)

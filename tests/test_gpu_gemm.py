@@ -227,3 +227,31 @@ def test_gemm_random_shapes(lib):
         y32 = x_dq @ w_dq.t() + (bias.float() if bias is not None else 0)
         assert y.shape == (M, N) and y.dtype == dtype
         assert within_tolerance(y, y32), f"trial {trial}: M={M} N={N} K={K} {xm.tag} x {wm.tag} {dtype}"
+
+
+@pytest.mark.parametrize("w_meta", [OCP_MXFP6_E2M3, OCP_MXFP6_E3M2, OCP_MXFP4_E2M1], ids=lambda m: m.tag)
+@pytest.mark.parametrize("x_meta", [MXFP8_E4M3_fn, MXFP8_E5M2_fn], ids=lambda m: m.tag)
+@pytest.mark.parametrize("M,N,K", [(256, 448, 128), (300, 1000, 640), (128, 4096, 1024), (1, 16, 128)])
+def test_native_subbyte_weight_equals_widened(lib, x_meta, w_meta, M, N, K):
+    """FP6 / FP4 weights kept at their own width (dense 6- / 4-bit streams read through the packed tensor-map types)
+    give the same products as the same codes widened to E4M3 bytes: the output bytes must be identical, with every
+    code of the format present in the weight."""
+    torch.manual_seed(M + N + K)
+    x = (torch.randn(M, K, device=DEV) * 2).to(torch.bfloat16)
+    bits = 1 + w_meta.element_exp_bits + w_meta.element_frac_bits
+    w_elements = torch.randint(0, 1 << bits, (N * K // 32, 32), device=DEV, dtype=torch.uint8)
+    w_elements.view(-1)[: 1 << bits] = torch.arange(1 << bits, device=DEV, dtype=torch.uint8)
+    w_scales = torch.randint(118, 130, (N * K // 32, 1), device=DEV, dtype=torch.uint8)
+    a = G.quantize_pack(x, x_meta)
+    wide = G.pack_operand(w_scales, w_elements, N, K, w_meta, G.OPERAND_B, native=False)
+    dense = G.pack_operand(w_scales, w_elements, N, K, w_meta, G.OPERAND_B, native=True)
+    assert dense.hw_format in (3, 4, 5) and dense.codes.numel() == N * K * bits // 8 and wide.codes.numel() == N * K
+    assert torch.equal(dense.sf, wide.sf)
+    w32 = mxk.compose_mxfp_tensor(w_scales, w_elements, w_meta, torch.float32).reshape(N, K)
+    y32 = dequant(x, x_meta) @ w32.t()
+    for dt in (torch.bfloat16, torch.float32):
+        y_wide = G.mx_gemm(a, wide, dt)
+        y_dense = G.mx_gemm(a, dense, dt)
+        G.check_status(DEV)
+        assert within_tolerance(y_dense, y32), f"max err {(y_dense.float() - y32).abs().max().item()}"
+        assert torch.equal(y_dense, y_wide)
