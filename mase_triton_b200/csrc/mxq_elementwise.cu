@@ -462,6 +462,38 @@ __device__ __forceinline__ void mxfp_b32_quant_tile_bf16(const char* __restrict_
     }
 }
 
+// fp32 inputs, E4M3 / E5M2 codes: the short form of the element encode, as pk_bf16_quantise_normal.  When every
+// |x| of the lanes that vote together is at least 2^(1-bias+se) (`lim`), nothing is flushed, in the sub-range or
+// rounding to zero, so four codes are: exponent field (low eb bits, re-biased later) OR rounded fraction per
+// element from the SIGNED quotient, packed, re-biased with one XOR, signs gathered from the quotients' top bytes.
+template <class F>
+__device__ __forceinline__ uint32_t f32_codes4_normal(const uint32_t* x_bits, float inv, const F& f) {
+    constexpr int fb = F{}.fb(), eb = F{}.eb();
+    constexpr uint32_t cbits = (uint32_t)(127 + 23 - fb) << 23;           // 2^(23-fb)
+    uint32_t qb[4], mag[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        qb[i] = __float_as_uint(__fmul_rn(__uint_as_float(x_bits[i]), inv));
+        // the reference's cut of the mantissa to 15 bits (minifloat/fake.py:45) commutes with the exact scaling
+        const float m = __uint_as_float((qb[i] & 0x007FFF00u) | 0x3F800000u);
+        const uint32_t fr = (uint32_t)mad_add((int)__float_as_uint(__fadd_rn(m, __uint_as_float(cbits))), -(int)(cbits + (1u << fb)));
+        mag[i] = ((qb[i] >> (23 - fb)) & (((1u << eb) - 1u) << fb)) | fr;
+    }
+    return pack4_codes(mag, qb, f) ^ (((1u << (eb - 1)) << fb) * 0x01010101u);
+}
+
+// per-block bound of the short form as fp32 bits, from the block header (+Inf: never)
+template <class F>
+__device__ __forceinline__ uint32_t short_form_limit_bits(uint32_t hdr) {
+    const int e = (int)((hdr >> 8) & 0xFFu) + 1 - PkFmt<F>::BIAS;
+    return (uint32_t)(e >= 2 ? e : 255) << 23;
+}
+
+__device__ __forceinline__ float f32x4_absmin(const Pack<16>& p) {
+    return fminf(fminf(fabsf(__uint_as_float(p.w[0])), fabsf(__uint_as_float(p.w[1]))),
+                 fminf(fabsf(__uint_as_float(p.w[2])), fabsf(__uint_as_float(p.w[3]))));
+}
+
 template <class KIn, class F, int U, int MODE, bool FULL>
 __device__ __forceinline__ void mxfp_b32_quant_tile(const char* __restrict__ src, uint8_t* __restrict__ scales,
                                                     char* __restrict__ dst, int64_t first, int64_t left, const F& f) {
@@ -496,13 +528,30 @@ __device__ __forceinline__ void mxfp_b32_quant_tile(const char* __restrict__ src
 #pragma unroll
     for (int j = 1; j < U; ++j) mine = (sub == j) ? amax[j] : mine;
     const uint32_t hdr = block_header(mine, f);
+    // fp32 inputs, 8-bit element codes: the short form where no element of the voting lanes is below its block's bound
+    constexpr bool kShortForm = (MODE == MODE_CODES) && KIn::size == 4 && PkFmt<F>::RARE_SUBRANGE;
+    uint32_t lim_mine = 0u;
+    if constexpr (kShortForm) lim_mine = short_form_limit_bits<F>(hdr);
     if (MODE == MODE_CODES && sub < U && (FULL || sub * kThreads < left))
         scales[(first + sub * kThreads) / G] = (uint8_t)(hdr >> 8);
 #pragma unroll
     for (int j = 0; j < U; ++j) {
         const uint32_t h = __shfl_sync(0xFFFFFFFFu, hdr, (lane & ~(G - 1)) + j);
+        uint32_t lim = 0u;
+        if constexpr (kShortForm) lim = __shfl_sync(0xFFFFFFFFu, lim_mine, (lane & ~(G - 1)) + j);
         if (!FULL && j * kThreads >= left) continue;
         char* d = dst + (size_t)j * kThreads * OB;
+        if constexpr (kShortForm) {
+            if (!(h & 1u)) {
+                const bool any_below = __any_sync(__activemask(), f32x4_absmin(p[j]) < __uint_as_float(lim));
+                if (!any_below) {
+                    Pack<V> o;
+                    o.w[0] = f32_codes4_normal(p[j].w, __uint_as_float(h & 0x7F800000u), f);
+                    store_pack<V>(d, o);
+                    continue;
+                }
+            }
+        }
         if constexpr (MODE == MODE_QDQ) {
             if (!(h & 1u)) {
                 const float inv = __uint_as_float(h & 0x7F800000u);
@@ -921,14 +970,16 @@ __global__ void __launch_bounds__(kThreads) mx_quant_pack_flat_kernel(const void
 #pragma unroll
     for (int j = 1; j < U; ++j) mine = (sub == j) ? amax[j] : mine;
     const uint32_t hdr = block_header(BF16 ? bf16x2_max_bits(mine) : mine, f);
-    const uint32_t word = BF16 ? bf16_block_word<F>(hdr) : 0u;
+    constexpr bool F32 = KIn::size == 4;
+    // the second per-block word: bf16 -- see bf16_block_word; fp32 -- the bound of the short form
+    const uint32_t word = BF16 ? bf16_block_word<F>(hdr) : (F32 ? short_form_limit_bits<F>(hdr) : 0u);
     uint32_t sb_of[U];
 #pragma unroll
     for (int j = 0; j < U; ++j) {
         const int owner = (lane & ~(G - 1)) + j;
         const uint32_t h = __shfl_sync(0xFFFFFFFFu, hdr, owner);
         uint32_t w2 = 0u;
-        if constexpr (BF16) w2 = __shfl_sync(0xFFFFFFFFu, word, owner);
+        if constexpr (BF16 || F32) w2 = __shfl_sync(0xFFFFFFFFu, word, owner);
         const int64_t vec = first + (int64_t)j * kThreads;
         Pack<V> o;
         uint32_t sbyte = (h >> 8) & 0xFFu;
@@ -938,14 +989,20 @@ __global__ void __launch_bounds__(kThreads) mx_quant_pack_flat_kernel(const void
                 bf16_quantise_access<F, false>(p[j], w2, amin[j], h, 0u, o.w);
             } else {
                 const float inv = __uint_as_float(h & 0x7F800000u);
-                uint32_t qb[V], mag[V];
+                bool short_form = false;
+                if constexpr (F32) short_form = !__any_sync(__activemask(), f32x4_absmin(p[j]) < __uint_as_float(w2));
+                if (short_form) {
+                    o.w[0] = f32_codes4_normal(p[j].w, inv, f);
+                } else {
+                    uint32_t qb[V], mag[V];
 #pragma unroll
-                for (int i = 0; i < V; ++i) {
-                    qb[i] = mx_quotient_bits(pack_bits<KIn>(p[j], i), inv);
-                    mag[i] = (uint32_t)encode_mag_fp(qb[i], f);
+                    for (int i = 0; i < V; ++i) {
+                        qb[i] = mx_quotient_bits(pack_bits<KIn>(p[j], i), inv);
+                        mag[i] = (uint32_t)encode_mag_fp(qb[i], f);
+                    }
+#pragma unroll
+                    for (int i = 0; i < V; i += 4) o.w[i >> 2] = pack4_codes(&mag[i], &qb[i], f);
                 }
-#pragma unroll
-                for (int i = 0; i < V; i += 4) o.w[i >> 2] = pack4_codes(&mag[i], &qb[i], f);
             }
 #pragma unroll
             for (int i = 0; i < V / 4; ++i) bad |= ((o.w[i] & 0x7F7F7F7Fu) + probe) & 0x80808080u;
