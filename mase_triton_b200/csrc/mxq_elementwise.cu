@@ -314,9 +314,24 @@ __device__ __forceinline__ void bf16_abs_range(const Pack<16>& p, uint32_t& mx2,
     mn2 = bf2_bits(__hmin2(__hmin2(a0, a1), __hmin2(a2, a3)));
 }
 
-// fp32 bits of the larger half of a packed pair of bf16 magnitudes; NaN wins
+// fp32 bits of the larger half of a packed pair of bf16 magnitudes; NaN wins (as 15-bit patterns the magnitudes
+// order like integers, NaN above Inf above every finite value)
 __device__ __forceinline__ uint32_t bf16x2_max_bits(uint32_t m2) {
-    return __float_as_uint(max_abs_nan(__uint_as_float(m2 << 16), __uint_as_float(m2 & 0xFFFF0000u)));
+    return max(m2 & 0xFFFFu, m2 >> 16) << 16;
+}
+
+// block_header for the maximum of bf16 inputs (fp32 bits with 16 zero low bits): such a maximum is never among the
+// last floats below a power of two, so the round-up of the reference's log2 (shared_exponent) cannot apply and the
+// shared exponent is the exponent field minus the format's largest exponent
+template <class F>
+__device__ __forceinline__ uint32_t block_header_bf16(uint32_t amax_bits, const F& f) {
+    const int emax_b = fmt_emax(f) - fmt_bias(f);
+    const uint32_t E = amax_bits >> 23;
+    const uint32_t special = E == 255u ? 1u : 0u;
+    const int se = max((int)E - 127 - emax_b, -127);
+    const uint32_t sbyte = E == 0u ? 0u : (special ? 255u : (uint32_t)(se + 127));
+    const uint32_t inv_field = (E == 0u || special) ? 127u : (uint32_t)(127 - se);
+    return (inv_field << 23) | (sbyte << 8) | special;
 }
 
 // Low half: bf16 bits of 2^-se.  High half, by format: E2M1 -- the keep threshold (e2m1_block's ts2); E4M3 / E5M2 --
@@ -416,7 +431,7 @@ __device__ __forceinline__ void mxfp_b32_quant_tile_bf16(const char* __restrict_
     uint32_t mine = mx2[0];
 #pragma unroll
     for (int j = 1; j < U; ++j) mine = (sub == j) ? mx2[j] : mine;
-    const uint32_t hdr = block_header(bf16x2_max_bits(mine), f);
+    const uint32_t hdr = block_header_bf16(bf16x2_max_bits(mine), f);
     const uint32_t word = bf16_block_word<F>(hdr);
     const uint32_t sb = (hdr >> 8) & 0xFFu;
     const uint32_t sf2_mine = (sb == 0u ? 0x0040u : (sb << 7)) * 0x10001u;
@@ -969,7 +984,9 @@ __global__ void __launch_bounds__(kThreads) mx_quant_pack_flat_kernel(const void
     uint32_t mine = amax[0];
 #pragma unroll
     for (int j = 1; j < U; ++j) mine = (sub == j) ? amax[j] : mine;
-    const uint32_t hdr = block_header(BF16 ? bf16x2_max_bits(mine) : mine, f);
+    uint32_t hdr;
+    if constexpr (BF16) hdr = block_header_bf16(bf16x2_max_bits(mine), f);
+    else hdr = block_header(mine, f);
     constexpr bool F32 = KIn::size == 4;
     // the second per-block word: bf16 -- see bf16_block_word; fp32 -- the bound of the short form
     const uint32_t word = BF16 ? bf16_block_word<F>(hdr) : (F32 ? short_form_limit_bits<F>(hdr) : 0u);
