@@ -35,7 +35,7 @@ def build(force: bool = False) -> Path:
     r = subprocess.run([nvcc, *lib_build.NVCC_FLAGS, *FLAGS, "-c", str(csrc / "mxq_gemm.cu"), "-o", str(obj)], capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"nvcc failed on the wait-limit variant:\n{r.stdout}\n{r.stderr}")
-    others = [str(csrc / f"{name}.o") for name in ("mxq_api", "mxq_elementwise")]
+    others = [str(csrc / f"{name}.o") for name in ("mxq_api", "mxq_elementwise", "mxq_bitpack")]
     r = subprocess.run([nvcc, "-shared", "-o", str(LIB), str(obj), *others], capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
