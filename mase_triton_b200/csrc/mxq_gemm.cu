@@ -55,6 +55,8 @@ template <int MH> struct Cfg {
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;   // + slack to align the ring
     static constexpr int SMEM_BYTES_TMA = SMEM_BYTES + EPI_TMA_WARPS * EPI_SLOT_BYTES;   // + staging of the asynchronous epilogue
 };
+constexpr int FWD_BUF_BYTES = 3584;              // one box of the forwarding warp: a few rows of a tile (8 x 224 16-bit values)
+constexpr int FWD_BUFS = 2;
 
 // Destinations of the gather-fused kernel: the [M, N] result goes, at column offset col0 of a
 // row-major matrix with leading dimension ld, to every pointer in ptr[0..n): ptr[self] is this GPU's
@@ -68,6 +70,15 @@ struct OutSpec {
 constexpr int FWD_WARPS = 4;                     // copy-out warps of the gather-fused kernel
 constexpr int FWD_UNROLL = 4;                    // 16-byte units each copy-out lane keeps in flight
 constexpr int STORED_BAR_OFF = 128, ACK_BAR_OFF = 144;   // two barriers each (one per accumulator), inside the BAR_BYTES region past the pipeline barriers
+constexpr int FWD_BAR_OFF = 160;                 // one barrier per forwarding buffer
+
+// Tensor maps of the gather-fused kernel whose forwarding is done by the copy engine: `src` reads this GPU's own
+// output region back (boxes of box_rows rows x the tile width), dst[d] writes the same box into destination d.
+struct FwdMaps {
+    CUtensorMap src;
+    CUtensorMap dst[MAX_DEST];
+    int n, self, box_rows, box_bytes;
+};
 
 
 // Copy-out of the gather-fused kernel: one tile of this GPU's output (just written by the epilogue
@@ -108,25 +119,34 @@ __device__ __forceinline__ void forward_tile(const OutSpec& outs, int fw, int la
 //      store with TMA (asynchronous: tensor memory is handed back without waiting for global memory),
 //      EPI_GATHER = EPI_REGS plus the copy-out warps of the gather-fused kernel;
 // bn: columns of the CTA tile (multiple of 16, <= BN_MAX) = rows per scale-factor tile of the right operand
-enum : int { EPI_REGS = 0, EPI_TMA = 1, EPI_GATHER = 2 };
-template <int EPI> constexpr int kernel_threads() { return EPI == EPI_TMA ? THREADS_TMA : THREADS + (EPI == EPI_GATHER ? FWD_WARPS * 32 : 0); }
+//      EPI_GATHER_TMA = EPI_TMA plus one forwarding warp: a single thread reads each finished half tile of the local
+//      output back into small shared-memory boxes with TMA loads and stores every box to all peers with TMA stores
+enum : int { EPI_REGS = 0, EPI_TMA = 1, EPI_GATHER = 2, EPI_GATHER_TMA = 3 };
+template <int EPI> constexpr int kernel_threads() {
+    return EPI == EPI_TMA ? THREADS_TMA : EPI == EPI_GATHER_TMA ? THREADS_TMA + 32 : THREADS + (EPI == EPI_GATHER ? FWD_WARPS * 32 : 0);
+}
+template <int EPI, int MH> constexpr int kernel_smem() {
+    return EPI == EPI_TMA ? Cfg<MH>::SMEM_BYTES_TMA : EPI == EPI_GATHER_TMA ? Cfg<MH>::SMEM_BYTES_TMA + FWD_BUFS * FWD_BUF_BYTES : Cfg<MH>::SMEM_BYTES;
+}
 
 template <int OUT_DT, int MH, int EPI>
 __global__ void __launch_bounds__(kernel_threads<EPI>(), 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, void* __restrict__ out,
                const void* __restrict__ bias, int M, int N, int K, int bn, uint32_t idesc_base, int* status,
-               const __grid_constant__ OutSpec outs, const __grid_constant__ OutMaps omaps) {
+               const __grid_constant__ OutSpec outs, const __grid_constant__ OutMaps omaps, const __grid_constant__ FwdMaps fmaps) {
     using C = Cfg<MH>;
     constexpr int STAGES = C::STAGES;
     constexpr bool MULTI = EPI == EPI_GATHER;
-    constexpr int EPI_WARPS = EPI == EPI_TMA ? EPI_TMA_WARPS : 4;
+    constexpr bool TMA_EPI = EPI == EPI_TMA || EPI == EPI_GATHER_TMA;
+    constexpr int EPI_WARPS = TMA_EPI ? EPI_TMA_WARPS : 4;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t ring = (raw + 1023u) & ~1023u;                    // 1024-aligned operand ring
     uint8_t* ring_ptr = smem_raw + (ring - raw);
-    // ring | staging slots of the asynchronous epilogue (EPI_TMA only) | barriers
-    constexpr uint32_t STAGING = EPI == EPI_TMA ? EPI_TMA_WARPS * EPI_SLOT_BYTES : 0;
+    // ring | staging slots of the asynchronous epilogue | boxes of the forwarding warp (EPI_GATHER_TMA) | barriers
+    constexpr uint32_t SLOTS = TMA_EPI ? EPI_TMA_WARPS * EPI_SLOT_BYTES : 0;
+    constexpr uint32_t STAGING = SLOTS + (EPI == EPI_GATHER_TMA ? FWD_BUFS * FWD_BUF_BYTES : 0);
     const uint32_t bars = ring + STAGES * C::STAGE_BYTES + STAGING;  // full[S], empty[S], accum_full, tmem_empty[2], drain, tmem slot
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ring_ptr + STAGES * C::STAGE_BYTES + STAGING + 8 * (2 * STAGES + 4));
     auto full_bar = [&](int s) { return bars + 8u * s; };
@@ -136,6 +156,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t drain_bar = bars + 8u * (2 * STAGES + 3);                         // used only when the MMA warp unwinds
     auto stored_bar = [&](int h) { return bars + STORED_BAR_OFF + 8u * h; };
     auto ack_bar = [&](int h) { return bars + ACK_BAR_OFF + 8u * h; };
+    auto fwd_bar = [&](int b) { return bars + FWD_BAR_OFF + 8u * b; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KT = (K + BK - 1) / BK;
@@ -157,6 +178,13 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 mbar_init(stored_bar(h), 4);                         // epilogue warps: "this accumulator's rows are in local memory"
                 mbar_init(ack_bar(h), FWD_WARPS);                    // copy-out warps: "seen it"
             }
+        }
+        if constexpr (EPI == EPI_GATHER_TMA) {
+            for (int h = 0; h < 2; ++h) {
+                mbar_init(stored_bar(h), EPI_WARPS);                 // epilogue warps: "my stores of this half tile have been written"
+                mbar_init(ack_bar(h), 1);                            // the forwarding thread: "seen it"
+            }
+            for (int b = 0; b < FWD_BUFS; ++b) mbar_init(fwd_bar(b), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -253,9 +281,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             __syncwarp();
             mbar_wait(drain_bar, 0, nullptr, 0);
         }
-    } else if (EPI == EPI_TMA && warp < 2 + EPI_WARPS) {
+    } else if (TMA_EPI && warp < 2 + EPI_WARPS) {
         // ---------------- epilogue: TMEM -> registers -> shared staging -> TMA store ----------------
-        if constexpr (EPI == EPI_TMA) {
+        if constexpr (TMA_EPI) {
             const int e = warp - 2, q = warp & 3;          // two warps per TMEM lane quadrant; each takes every other chunk
             const int grp = e >> 2;
             const int n_chunks = (bn + 31) >> 5;
@@ -276,11 +304,67 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     // the group that took the even chunks of accumulator 0 takes the odd ones of accumulator 1
                     drain_accumulator_tma<OUT_DT>(taddr, n_chunks, tail16, (grp ^ h) & 1, 2, bias, nt * bn, mt * C::BM + h * 128 + q * 32, M, N,
                                                   slots, turn, omaps, tmem_empty_bar(h), lane);
+                    if constexpr (EPI == EPI_GATHER_TMA) {
+                        // tell the forwarding thread that this warp's part of half tile h has been written to local
+                        // memory; it must have picked up the same half of the previous tile first (one tile of slack)
+                        if (lane == 0) bulk_wait_all();
+                        if (tcount > 0) ok = mbar_wait(ack_bar(h), (tcount - 1) & 1, status, ST_EPILOGUE_TIMEOUT);
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(stored_bar(h));
+                    }
                 }
             }
             if (lane == 0) bulk_wait_all();                // the stores issued by this warp have been written
         }
-    } else if (EPI != EPI_TMA && warp < 6) {
+    } else if (EPI == EPI_GATHER_TMA) {
+        // ---------------- gather-fused kernel, forwarding by the copy engine: local output -> peers ----------------
+        if constexpr (EPI == EPI_GATHER_TMA) {
+            if (lane == 0) {
+                const uint32_t bufs = ring + STAGES * C::STAGE_BYTES + SLOTS;
+                const int FR = fmaps.box_rows;
+                bool ok = true;
+                uint32_t tcount = 0, loaded = 0, sent = 0;          // boxes whose load has been started / whose stores have been issued
+                for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+                    int mt, nt;
+                    tile_coords(tile, MT, NT, mt, nt);
+                    for (int h = 0; h < MH && ok; ++h) {
+                        ok = mbar_wait(stored_bar(h), tcount & 1, status, ST_FORWARD_TIMEOUT);
+                        if (!ok) break;
+                        mbar_arrive(ack_bar(h));
+                        asm volatile("fence.proxy.async.global;" ::: "memory");      // the half tile was written through the async proxy by other threads
+                        const int row0 = mt * C::BM + h * 128;
+                        const int rows = min(128, M - row0);
+                        if (rows <= 0) continue;
+                        const int boxes = (rows + FR - 1) / FR;
+                        // two loads in flight: box i + 1 is requested before box i is waited for and sent on
+                        for (int i = -1; i < boxes && ok; ++i) {
+                            if (i + 1 < boxes) {
+                                const uint32_t b = loaded % FWD_BUFS;
+                                // the stores that read this buffer FWD_BUFS boxes ago must have finished reading it
+                                if (loaded >= FWD_BUFS) bulk_wait_read<0>();      // (its stores are the last ones issued: box i + 1 - FWD_BUFS)
+                                mbar_expect_tx(fwd_bar(b), (uint32_t)fmaps.box_bytes);
+                                tma_load_2d(bufs + b * FWD_BUF_BYTES, &fmaps.src, nt * bn, row0 + (i + 1) * FR, fwd_bar(b));
+                                ++loaded;
+                            }
+                            if (i >= 0) {
+                                const uint32_t b = sent % FWD_BUFS;
+                                ok = mbar_wait(fwd_bar(b), (sent / FWD_BUFS) & 1, status, ST_FORWARD_TIMEOUT);
+                                if (!ok) break;
+                                for (int d = 0; d < fmaps.n; ++d)
+                                    if (d != fmaps.self) tma_store_2d(&fmaps.dst[d], nt * bn, row0 + i * FR, bufs + b * FWD_BUF_BYTES);
+                                bulk_commit();
+                                ++sent;
+                            }
+                        }
+                    }
+                }
+                // after a wait that ran out: a load may still be in flight into this CTA's shared memory
+                for (; sent < loaded; ++sent) mbar_wait(fwd_bar(sent % FWD_BUFS), (sent / FWD_BUFS) & 1, status, ST_FORWARD_TIMEOUT);
+                bulk_wait_all();                               // every box has been written to every peer
+            }
+            __syncwarp();
+        }
+    } else if (!TMA_EPI && warp < 6) {
         // ---------------- epilogue: TMEM -> registers -> global ----------------
         const int q = warp & 3;                            // TMEM lane quadrant this warp may access
         const int full_chunks = bn >> 5;                   // 32-column chunks, then possibly one of 16 columns
@@ -482,9 +566,10 @@ static bool make_operand_map(CUtensorMap* map, const void* codes, int64_t rows, 
 template <int OUT_DT, int MH, int EPI>
 static int launch_gemm(const uint8_t* a_codes, const uint8_t* b_codes, const uint8_t* sfa, const uint8_t* sfb, void* out,
                        const void* bias, int M, int N, int K, int bn, uint32_t idesc, int* status, cudaStream_t st, const OutSpec* outs,
-                       const OutMaps& omaps) {
+                       const OutMaps& omaps, const FwdMaps& fmaps) {
     using C = Cfg<MH>;
-    constexpr int SMEM = EPI == EPI_TMA ? C::SMEM_BYTES_TMA : C::SMEM_BYTES;
+    constexpr int SMEM = kernel_smem<EPI, MH>();
+    static_assert(SMEM <= 232448, "more shared memory than a CTA can have");
     static bool attr_done[MAX_DEVICES] = {false};
     const cudaError_t attr_err = raise_smem_limit(mx_gemm_kernel<OUT_DT, MH, EPI>, SMEM, attr_done);
     if (attr_err != cudaSuccess) { set_last_cuda_error(attr_err); return MXQ_ELAUNCH; }
@@ -493,8 +578,24 @@ static int launch_gemm(const uint8_t* a_codes, const uint8_t* b_codes, const uin
     const int tiles = ((M + C::BM - 1) / C::BM) * ((N + bn - 1) / bn);
     const int grid = tiles < sm_count() ? tiles : sm_count();          // persistent: one CTA per SM
     mx_gemm_kernel<OUT_DT, MH, EPI><<<grid, kernel_threads<EPI>(), SMEM, st>>>(ma, mb, sfa, sfb, out, bias, M, N, K, bn, idesc, status,
-                                                                         EPI == EPI_GATHER ? *outs : OutSpec{}, omaps);
+                                                                         EPI == EPI_GATHER ? *outs : OutSpec{}, omaps, fmaps);
     return check_launch();
+}
+
+// Maps of the gather-fused kernel that forwards with the copy engine: the local epilogue's maps and one box map per
+// destination, all over columns [col0, col0 + N) of the [M, ld] matrices.  False when a matrix cannot be described.
+static bool make_gather_maps(const OutSpec& outs, int M, int N, int bn, int dt, OutMaps* omaps, FwdMaps* fmaps) {
+    const int esz = dt == MXQ_F32 ? 4 : 2;
+    int box_rows = 32;                                   // largest power of two whose box fits a forwarding buffer
+    while (box_rows > 1 && box_rows * bn * esz > FWD_BUF_BYTES) box_rows >>= 1;
+    if (box_rows * bn * esz > FWD_BUF_BYTES) return false;
+    auto region = [&](int d) { return static_cast<void*>(static_cast<uint8_t*>(outs.ptr[d]) + outs.col0 * esz); };
+    if (!make_out_maps(omaps, region(outs.self), M, N, outs.ld, dt)) return false;
+    if (!make_rows_map(&fmaps->src, region(outs.self), M, N, outs.ld, dt, bn, box_rows)) return false;
+    for (int d = 0; d < outs.n; ++d)
+        if (d != outs.self && !make_rows_map(&fmaps->dst[d], region(d), M, N, outs.ld, dt, bn, box_rows)) return false;
+    fmaps->n = outs.n; fmaps->self = outs.self; fmaps->box_rows = box_rows; fmaps->box_bytes = box_rows * bn * esz;
+    return true;
 }
 
 template <int OUT_DT>
@@ -502,17 +603,23 @@ static int launch_gemm_dt(const uint8_t* a_codes, const uint8_t* b_codes, const 
                           const void* bias, int M, int N, int K, int bn, uint32_t idesc, int* status, cudaStream_t st,
                           const OutSpec* outs = nullptr) {
     OutMaps omaps{};
+    FwdMaps fmaps{};
     if (outs != nullptr) {
-        if (M <= 128) return launch_gemm<OUT_DT, 1, EPI_GATHER>(a_codes, b_codes, sfa, sfb, nullptr, bias, M, N, K, bn, idesc, status, st, outs, omaps);
-        return launch_gemm<OUT_DT, 2, EPI_GATHER>(a_codes, b_codes, sfa, sfb, nullptr, bias, M, N, K, bn, idesc, status, st, outs, omaps);
+        // the copy engine forwards whole row segments of a tile; outputs it cannot describe take the copy-out warps
+        if (make_gather_maps(*outs, M, N, bn, OUT_DT, &omaps, &fmaps)) {
+            if (M <= 128) return launch_gemm<OUT_DT, 1, EPI_GATHER_TMA>(a_codes, b_codes, sfa, sfb, nullptr, bias, M, N, K, bn, idesc, status, st, outs, omaps, fmaps);
+            return launch_gemm<OUT_DT, 2, EPI_GATHER_TMA>(a_codes, b_codes, sfa, sfb, nullptr, bias, M, N, K, bn, idesc, status, st, outs, omaps, fmaps);
+        }
+        if (M <= 128) return launch_gemm<OUT_DT, 1, EPI_GATHER>(a_codes, b_codes, sfa, sfb, nullptr, bias, M, N, K, bn, idesc, status, st, outs, omaps, fmaps);
+        return launch_gemm<OUT_DT, 2, EPI_GATHER>(a_codes, b_codes, sfa, sfb, nullptr, bias, M, N, K, bn, idesc, status, st, outs, omaps, fmaps);
     }
     // the asynchronous epilogue needs an output TMA can describe (16-byte aligned base and row pitch)
     if (make_out_maps(&omaps, out, M, N, N, OUT_DT)) {
-        if (M <= 128) return launch_gemm<OUT_DT, 1, EPI_TMA>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, bn, idesc, status, st, nullptr, omaps);
-        return launch_gemm<OUT_DT, 2, EPI_TMA>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, bn, idesc, status, st, nullptr, omaps);
+        if (M <= 128) return launch_gemm<OUT_DT, 1, EPI_TMA>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, bn, idesc, status, st, nullptr, omaps, fmaps);
+        return launch_gemm<OUT_DT, 2, EPI_TMA>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, bn, idesc, status, st, nullptr, omaps, fmaps);
     }
-    if (M <= 128) return launch_gemm<OUT_DT, 1, EPI_REGS>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, bn, idesc, status, st, nullptr, omaps);
-    return launch_gemm<OUT_DT, 2, EPI_REGS>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, bn, idesc, status, st, nullptr, omaps);
+    if (M <= 128) return launch_gemm<OUT_DT, 1, EPI_REGS>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, bn, idesc, status, st, nullptr, omaps, fmaps);
+    return launch_gemm<OUT_DT, 2, EPI_REGS>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, bn, idesc, status, st, nullptr, omaps, fmaps);
 }
 
 // instruction descriptor: A/B formats, K-major operands, N >> 3, E8M0 scales, M >> 4

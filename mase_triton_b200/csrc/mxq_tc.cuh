@@ -337,6 +337,22 @@ static bool make_out_maps(OutMaps* maps, void* out, int64_t M, int64_t N, int64_
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Unswizzled map of a row-major [M, N] matrix (`ld` elements per row) with boxes of box_cols x box_rows elements: whole
+// row segments of a tile, for copies that only pass through shared memory.
+static bool make_rows_map(CUtensorMap* map, void* base, int64_t M, int64_t N, int64_t ld, int dt, int box_cols, int box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const int esz = dt == MXQ_F32 ? 4 : 2;
+    if (reinterpret_cast<uintptr_t>(base) % 16 != 0 || (ld * esz) % 16 != 0 || box_cols > 256 || (box_cols * esz) % 16 != 0) return false;
+    const CUtensorMapDataType type = dt == MXQ_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : (dt == MXQ_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+    const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)(ld * esz)};
+    const cuuint32_t estr[2] = {1, 1};
+    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+    return fn(map, type, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+              CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // Per-device facts and one-time set-up (a process may drive several GPUs): the SM count, and for every
 // kernel instantiation whether its dynamic shared-memory limit has been raised on that device.
 constexpr int MAX_DEVICES = 64;
