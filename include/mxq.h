@@ -270,11 +270,12 @@ int mxq_minifloat_weight_linear(const void* x, int dtype, const uint16_t* w_code
  * to columns [col_offset, col_offset + N) of EVERY row-major [>= M, ld_out] matrix in
  * outs[0 .. n_outs) (host array of device pointers, at most 8): outs[self_index] is this GPU's own
  * output, the others are the peers' outputs mapped into this process (CUDA IPC / virtual-memory
- * mappings).  The epilogue warps write the local output; four more warps of the same CTAs read each
- * finished tile back (from L2) and store it to the peers with plain 16-byte stores that cover whole
- * row segments, while the tensor cores work on the next tile.  Nothing in the kernel waits on
- * another GPU.  Ordering against the readers on the other ranks is the caller's business (a
- * collective or event after this call on the same stream).
+ * mappings).  The epilogue warps write the local output; one more warp of the same CTAs reads each
+ * finished half tile back (from L2) into small shared-memory boxes with TMA loads and sends every box
+ * to each peer with a TMA store (whole row segments of the tile; no multicast), while the tensor cores
+ * work on the next tile.  Outputs TMA cannot describe take four copy-out warps that store 16 bytes
+ * per lane instead.  Nothing in the kernel waits on another GPU.  Ordering against the readers on the
+ * other ranks is the caller's business (a collective or event after this call on the same stream).
  * N, ld_out and col_offset must be multiples of 8 elements (4 for MXQ_F32), else MXQ_ESIZE.
  */
 int mxq_mx_gemm_gather(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw_format, const uint8_t* b_codes,

@@ -57,7 +57,7 @@ def _fused_linear(x: Tensor, x_meta: MXFPMeta | None, w: Tensor | None, w_scales
     K = x.shape[-1]
     w_blocks_along_k = kind.w_quantised and len(w_shape) == 2 and w_tensor_meta.block_dim in (1, -1) and _gemm.supported(w_tensor_meta.meta)
     if kind.x_quantised and kind.w_quantised and block_scaled_ok(x, x_meta, w_tensor_meta):
-        wq = _gemm.packed_weight(w_scales, w_elements, w_shape, w_tensor_meta.meta)
+        wq = _gemm.packed_weight(w_scales, w_elements, w_shape, w_tensor_meta.meta, rows=x.numel() // K)
         return _gemm.mx_linear(x, x_meta, wq, bias)
     reason = tc_linear.why_not(x, K)
     if reason is not None:

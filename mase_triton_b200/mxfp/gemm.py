@@ -191,14 +191,65 @@ def minifloat_quantize_pack(x: Tensor, exp_bits: int, frac_bits: int, round_mode
     return PackedOperand(codes, sf, fmt.value, rows, K, OPERAND_A)
 
 
-def packed_weight(w_scales: Tensor, w_elements: Tensor, shape: tuple[int, int], meta: MXFPMeta) -> PackedOperand:
+_TUNED_TILE_ROWS: dict[tuple, int] = {}
+TILE_ROW_CANDIDATES = (224, 208, 192, 176, 160)
+
+
+def choose_tile_rows(w_scales: Tensor, w_elements: Tensor, shape: tuple[int, int], meta: MXFPMeta, rows: int | None) -> int:
+    """CTA tile width for a weight of ``shape`` multiplied with an activation of ``rows`` rows.
+
+    By default the width with the least padded work (``mxq_mx_best_tile_rows``).  With
+    ``KernelManager.enable_autotune()`` (the switch that turns Triton's autotuner on in the reference,
+    ``src/mase_triton/manager.py:7-32``) and a known ``rows``, the candidates whose padded work is within 8 % of the
+    least are each packed and timed on the GPU once per (device, rows rounded up to 256, shape) and the fastest is
+    kept; nothing is measured while a CUDA graph is being captured."""
+    from ..manager import KernelManager
+
+    n, k = shape
+    best = _lib.load().mxq_mx_best_tile_rows(n)
+    dev = w_elements.device
+    if not KernelManager.autotune_is_enabled() or not rows or torch.cuda.is_current_stream_capturing():
+        return best
+    m = min(-(-rows // 256) * 256, 16384)
+    key = (dev, m, n, k, meta)
+    if key in _TUNED_TILE_ROWS:
+        return _TUNED_TILE_ROWS[key]
+    padded = {t: -(-n // t) * t for t in TILE_ROW_CANDIDATES}
+    least = min(padded.values())
+    candidates = [t for t in TILE_ROW_CANDIDATES if padded[t] <= 1.08 * least]
+    if best not in candidates:
+        candidates.append(best)
+    a_codes = torch.randint(0, 0x78, (m, k), dtype=torch.uint8, device=dev)             # finite E4M3 codes, unit scales
+    a = pack_codes(None, a_codes, m, k, 4, 3, OPERAND_A)
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    timings = {}
+    for t in candidates:
+        b = pack_operand(w_scales, w_elements, n, k, meta, OPERAND_B, tile_rows=t)
+        for _ in range(2):
+            mx_gemm(a, b, torch.bfloat16, out=out)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            mx_gemm(a, b, torch.bfloat16, out=out)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        timings[t] = e0.elapsed_time(e1) / 5
+    choice = min(timings, key=timings.get)
+    _TUNED_TILE_ROWS[key] = choice
+    KernelManager.record_choice(("mx_gemm tile_rows", m, n, k), choice, timings)
+    return choice
+
+
+def packed_weight(w_scales: Tensor, w_elements: Tensor, shape: tuple[int, int], meta: MXFPMeta, rows: int | None = None) -> PackedOperand:
     """Packed form of a quantised weight.  The result is kept on the ``w_elements`` tensor object itself
     (so it dies with it and can never be confused with another tensor that re-uses the same address)
-    and is rebuilt when either code tensor was modified in place or replaced."""
-    tag = (w_elements._version, w_scales.data_ptr(), w_scales._version, tuple(shape), meta)
+    and is rebuilt when either code tensor was modified in place or replaced, or when the tile width chosen
+    for ``rows`` activation rows (:func:`choose_tile_rows`) differs from the one it was packed for."""
+    tile = choose_tile_rows(w_scales, w_elements, tuple(shape), meta, rows)
+    tag = (w_elements._version, w_scales.data_ptr(), w_scales._version, tuple(shape), meta, tile)
     cached = getattr(w_elements, "_mxq_packed", None)
     if cached is None or cached[0] != tag:
-        cached = (tag, pack_operand(w_scales, w_elements, shape[0], shape[1], meta, OPERAND_B))
+        cached = (tag, pack_operand(w_scales, w_elements, shape[0], shape[1], meta, OPERAND_B, tile_rows=tile))
         w_elements._mxq_packed = cached
     return cached[1]
 

@@ -87,17 +87,20 @@ class MXFPLinearPTQ(PTQLinearBase):
         elif bias is not None:
             self.bias = self._frozen(bias.to(dtype=dtype, device=device))
 
-    def tensor_core_weight(self):
+    def tensor_core_weight(self, rows: int | None = None):
         """The quantised weight re-encoded for the block-scaled GEMM, kept on the module: rebuilt only when the
-        code tensors were written (``load_state_dict``, in-place edits), moved - not rebuilt - by ``.to()``."""
+        code tensors were written (``load_state_dict``, in-place edits), moved - not rebuilt - by ``.to()``.
+        ``rows`` (the height of the activation it will be multiplied with) only matters while
+        ``KernelManager`` autotune is enabled: the tile width is then the one measured fastest for that height."""
         from . import gemm as _gemm
 
         versions = (self.w_elements._version, self.w_scales._version)
+        tile = _gemm.choose_tile_rows(self.w_scales.data, self.w_elements.data, tuple(self.w_tensor_meta.shape), self.w_tensor_meta.meta, rows)
         stale = (self._tc_codes is None or self._tc_info is None or self._tc_info[0] != versions
-                 or self._tc_codes.device != self.w_elements.device)
+                 or self._tc_codes.device != self.w_elements.device or self._tc_info[2] != tile)
         if stale:
             n, k = self.w_tensor_meta.shape
-            p = _gemm.pack_operand(self.w_scales.data, self.w_elements.data, n, k, self.w_tensor_meta.meta, _gemm.OPERAND_B)
+            p = _gemm.pack_operand(self.w_scales.data, self.w_elements.data, n, k, self.w_tensor_meta.meta, _gemm.OPERAND_B, tile_rows=tile)
             self._tc_codes, self._tc_sf = p.codes, p.sf
             self._tc_info = (versions, p.hw_format, p.tile_rows)
         n, k = self.w_tensor_meta.shape
@@ -125,7 +128,7 @@ class MXFPLinearPTQ(PTQLinearBase):
             # A layer with a quantised bias holds no plain one and then adds none (the reference's rule).
             from . import gemm as _gemm
 
-            return _gemm.mx_linear(input, self.x_mxfp_meta, self.tensor_core_weight(), self.bias)
+            return _gemm.mx_linear(input, self.x_mxfp_meta, self.tensor_core_weight(input.numel() // self.in_features), self.bias)
         return MXFP_F.mxfp_linear(
             x=input, x_meta=self.x_mxfp_meta,
             w=self.weight, w_scales=self.w_scales, w_elements=self.w_elements, w_tensor_meta=self.w_tensor_meta,
@@ -151,7 +154,7 @@ class MXFPLinearPTQ(PTQLinearBase):
         from . import gemm as _gemm
 
         assert packed.K == self.in_features and self.w_scales is not None
-        wq = self.tensor_core_weight()
+        wq = self.tensor_core_weight(packed.rows)
         # a layer with a quantised bias holds no plain one, and forward() then adds none (the reference's rule)
         y = _gemm.mx_gemm(packed, wq, out_dtype, bias=self.bias)
         return y if lead_shape is None else y.reshape(*lead_shape, self.out_features)

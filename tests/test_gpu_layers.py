@@ -175,3 +175,31 @@ def test_host_pipeline_matches_device_result(lib, rows, chunk):
             want = direct(x.to(dev)).cpu()
             assert torch.equal(out.view(torch.int32), want.view(torch.int32))
         assert pipe.launches == 2 * ((rows + min(chunk, rows) - 1) // min(chunk, rows))
+
+
+def test_kernel_manager_autotune_picks_a_tile_width(lib):
+    """With KernelManager autotune on, a fused layer times the candidate tile widths at its first call for an
+    activation height, records the choice, and returns the same bytes as without tuning (the tile width does not
+    change the order in which an output element is accumulated)."""
+    from mase_triton_b200.manager import KernelManager
+
+    torch.manual_seed(31)
+    fc = torch.nn.Linear(256, 1000, bias=True, device=DEV, dtype=torch.bfloat16)
+    x = torch.randn(300, 256, device=DEV, dtype=torch.bfloat16)
+    plain = MXFPLinearPTQ.from_linear(fc, MXFP8_E4M3_fn, OCP_MXFP6_E3M2, None, "XqWqB", "fused")
+    want = plain(x)
+    KernelManager.enable_autotune()
+    try:
+        tuned = MXFPLinearPTQ.from_linear(fc, MXFP8_E4M3_fn, OCP_MXFP6_E3M2, None, "XqWqB", "fused")
+        got = tuned(x)
+        got_functional = MX.mxfp_linear(x, MXFP8_E4M3_fn, None, tuned.w_scales, tuned.w_elements, tuned.w_tensor_meta, tuned.bias, None, None,
+                                        None, "XqWqB", "fused")
+        G.check_status(DEV)
+        choices = {k: v for k, v in KernelManager.tuned_choices().items() if k[0] == "mx_gemm tile_rows" and k[2:] == (1000, 256)}
+        assert len(choices) == 1
+        (rec,) = choices.values()
+        assert rec["choice"] in G.TILE_ROW_CANDIDATES and rec["choice"] == min(rec["ms"], key=rec["ms"].get) and len(rec["ms"]) >= 2
+        assert tuned.tensor_core_weight(300).tile_rows == rec["choice"]
+    finally:
+        KernelManager.disable_autotune()
+    assert torch.equal(got, want) and torch.equal(got_functional, want)
