@@ -56,7 +56,8 @@ template <int MH> struct Cfg {
     static constexpr int SMEM_BYTES_TMA = SMEM_BYTES + EPI_TMA_WARPS * EPI_SLOT_BYTES;   // + staging of the asynchronous epilogue
 };
 constexpr int FWD_BUF_BYTES = 3584;              // one box of the forwarding warp: a few rows of a tile (8 x 224 16-bit values)
-constexpr int FWD_BUFS = 2;
+constexpr int FWD_BUFS = 2;                      // boxes with shared memory of their own; narrower tiles leave room for more:
+constexpr int FWD_BUFS_MAX = 6;                  // the unused end of each stage's B region (bn < BN_MAX) holds one box
 
 // Destinations of the gather-fused kernel: the [M, N] result goes, at column offset col0 of a
 // row-major matrix with leading dimension ld, to every pointer in ptr[0..n): ptr[self] is this GPU's
@@ -78,6 +79,7 @@ struct FwdMaps {
     CUtensorMap src;
     CUtensorMap dst[MAX_DEST];
     int n, self, box_rows, box_bytes;
+    int n_bufs;                                  // FWD_BUFS, or FWD_BUFS + the ring's stages when a box fits behind the B tile of a stage
 };
 
 
@@ -184,7 +186,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 mbar_init(stored_bar(h), EPI_WARPS);                 // epilogue warps: "my stores of this half tile have been written"
                 mbar_init(ack_bar(h), 1);                            // the forwarding thread: "seen it"
             }
-            for (int b = 0; b < FWD_BUFS; ++b) mbar_init(fwd_bar(b), 1);
+            for (int b = 0; b < FWD_BUFS_MAX; ++b) mbar_init(fwd_bar(b), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -320,7 +322,13 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ---------------- gather-fused kernel, forwarding by the copy engine: local output -> peers ----------------
         if constexpr (EPI == EPI_GATHER_TMA) {
             if (lane == 0) {
-                const uint32_t bufs = ring + STAGES * C::STAGE_BYTES + SLOTS;
+                const uint32_t own = ring + STAGES * C::STAGE_BYTES + SLOTS;
+                // box b: the first FWD_BUFS have memory of their own, the others sit behind the bn rows of a stage's B tile
+                auto buf = [&](uint32_t b) {
+                    return b < (uint32_t)FWD_BUFS ? own + b * FWD_BUF_BYTES : ring + (b - FWD_BUFS) * C::STAGE_BYTES + C::A_BYTES + (uint32_t)(bn * BK);
+                };
+                const uint32_t NB = (uint32_t)fmaps.n_bufs;
+                const int ahead = NB >= 3u ? (int)NB - 2 : 1;           // loads requested beyond the box being sent
                 const int FR = fmaps.box_rows;
                 bool ok = true;
                 uint32_t tcount = 0, loaded = 0, sent = 0;          // boxes whose load has been started / whose stores have been issued
@@ -336,30 +344,31 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         const int rows = min(128, M - row0);
                         if (rows <= 0) continue;
                         const int boxes = (rows + FR - 1) / FR;
-                        // two loads in flight: box i + 1 is requested before box i is waited for and sent on
-                        for (int i = -1; i < boxes && ok; ++i) {
-                            if (i + 1 < boxes) {
-                                const uint32_t b = loaded % FWD_BUFS;
-                                // the stores that read this buffer FWD_BUFS boxes ago must have finished reading it
-                                if (loaded >= FWD_BUFS) bulk_wait_read<0>();      // (its stores are the last ones issued: box i + 1 - FWD_BUFS)
+                        int issued = 0;                              // boxes of this half tile whose load has been requested
+                        for (int i = 0; i < boxes && ok; ++i) {
+                            while (issued < boxes && issued <= i + ahead) {
+                                const uint32_t b = loaded % NB;
+                                // The stores that read this box NB boxes ago must have finished reading it.  Groups retire in
+                                // order and at most `ahead` + 1 boxes separate this load from the last store issued, so
+                                // "all but the newest group" (all groups, with two boxes) covers it.
+                                if (loaded >= NB) { if (NB >= 3u) bulk_wait_read<1>(); else bulk_wait_read<0>(); }
                                 mbar_expect_tx(fwd_bar(b), (uint32_t)fmaps.box_bytes);
-                                tma_load_2d(bufs + b * FWD_BUF_BYTES, &fmaps.src, nt * bn, row0 + (i + 1) * FR, fwd_bar(b));
+                                tma_load_2d(buf(b), &fmaps.src, nt * bn, row0 + issued * FR, fwd_bar(b));
                                 ++loaded;
+                                ++issued;
                             }
-                            if (i >= 0) {
-                                const uint32_t b = sent % FWD_BUFS;
-                                ok = mbar_wait(fwd_bar(b), (sent / FWD_BUFS) & 1, status, ST_FORWARD_TIMEOUT);
-                                if (!ok) break;
-                                for (int d = 0; d < fmaps.n; ++d)
-                                    if (d != fmaps.self) tma_store_2d(&fmaps.dst[d], nt * bn, row0 + i * FR, bufs + b * FWD_BUF_BYTES);
-                                bulk_commit();
-                                ++sent;
-                            }
+                            const uint32_t b = sent % NB;
+                            ok = mbar_wait(fwd_bar(b), (sent / NB) & 1, status, ST_FORWARD_TIMEOUT);
+                            if (!ok) break;
+                            for (int d = 0; d < fmaps.n; ++d)
+                                if (d != fmaps.self) tma_store_2d(&fmaps.dst[d], nt * bn, row0 + i * FR, buf(b));
+                            bulk_commit();
+                            ++sent;
                         }
                     }
                 }
                 // after a wait that ran out: a load may still be in flight into this CTA's shared memory
-                for (; sent < loaded; ++sent) mbar_wait(fwd_bar(sent % FWD_BUFS), (sent / FWD_BUFS) & 1, status, ST_FORWARD_TIMEOUT);
+                for (; sent < loaded; ++sent) mbar_wait(fwd_bar(sent % NB), (sent / NB) & 1, status, ST_FORWARD_TIMEOUT);
                 bulk_wait_all();                               // every box has been written to every peer
             }
             __syncwarp();
@@ -595,6 +604,10 @@ static bool make_gather_maps(const OutSpec& outs, int M, int N, int bn, int dt, 
     for (int d = 0; d < outs.n; ++d)
         if (d != outs.self && !make_rows_map(&fmaps->dst[d], region(d), M, N, outs.ld, dt, bn, box_rows)) return false;
     fmaps->n = outs.n; fmaps->self = outs.self; fmaps->box_rows = box_rows; fmaps->box_bytes = box_rows * bn * esz;
+    // a tile narrower than the widest leaves (BN_MAX - bn) * BK bytes of every stage's B region unused: one more box each
+    const int stages = M <= 128 ? Cfg<1>::STAGES : Cfg<2>::STAGES;
+    const bool tails = (BN_MAX - bn) * BK >= fmaps->box_bytes;
+    fmaps->n_bufs = FWD_BUFS + (tails ? (stages < FWD_BUFS_MAX - FWD_BUFS ? stages : FWD_BUFS_MAX - FWD_BUFS) : 0);
     return true;
 }
 

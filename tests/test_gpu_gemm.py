@@ -143,15 +143,17 @@ def test_fused_matmul_matches_separate(lib, x_meta, w_meta, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
-@pytest.mark.parametrize("M,N,K", [(256, 224, 128), (300, 448 + 64, 256), (100, 72, 96), (1024, 1792, 512)])
-def test_gather_epilogue_writes_every_destination(lib, dtype, M, N, K):
+@pytest.mark.parametrize("M,N,K,tile", [(256, 224, 128, None), (300, 448 + 64, 256, None), (100, 72, 96, None), (1024, 1792, 512, None),
+                                        (2000, 1792, 256, 192), (128, 1000, 128, 160), (4096, 2048, 128, 192)])
+def test_gather_epilogue_writes_every_destination(lib, dtype, M, N, K, tile):
     """The gather-fused kernel gives, in each destination and at the column offset, the bytes of the
-    plain GEMM; columns outside the shard stay untouched."""
+    plain GEMM; columns outside the shard stay untouched.  Tiles narrower than the widest forward through more
+    boxes (the unused end of each stage's B region), many tiles per CTA wrap the boxes' barriers several times."""
     torch.manual_seed(M + N)
     x = torch.randn((M, K), device=DEV, dtype=torch.bfloat16)
     w = (torch.randn((N, K), device=DEV) * 0.05).to(torch.bfloat16)
     bias = torch.randn((N,), device=DEV).to(dtype)
-    a, b = G.quantize_pack(x, MXFP8_E4M3_fn), G.quantize_pack(w, OCP_MXFP6_E3M2, G.OPERAND_B)
+    a, b = G.quantize_pack(x, MXFP8_E4M3_fn), G.quantize_pack(w, OCP_MXFP6_E3M2, G.OPERAND_B, tile_rows=tile)
     want = G.mx_gemm(a, b, dtype, bias=bias)
     ld, off = N + 64, 40
     outs = [torch.full((M + 3, ld), 7.0, device=DEV, dtype=dtype) for _ in range(3)]
