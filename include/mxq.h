@@ -164,20 +164,24 @@ int mxq_mx_pack_operand(const uint8_t* scales, const uint8_t* elements, int64_t 
                         uint8_t* hw_sf, int* hw_format, void* stream);
 
 /*
- * The RIGHT operand in the tensor cores' own 6- and 4-bit formats, for MXFP6 / MXFP4 weights (element
- * formats E2M3, E3M2, E2M1; the reference's code bytes are already the hardware's codes):
+ * An operand in the tensor cores' own 6- and 4-bit formats, for MXFP6 / MXFP4 tensors (element formats E2M3,
+ * E3M2, E2M1; the reference's code bytes are already the hardware's codes):
  *   hw_codes           : rows * K codes as a dense little-endian bit stream of 6 (4) bits per code,
  *                        rows * K * 6 / 8 (rows * K / 2) bytes, 32-byte aligned - three quarters (half) of the
- *                        bytes the GEMM reads per weight with mxq_mx_pack_operand
- *   hw_sf              : as mxq_mx_pack_operand(..., MXQ_OPERAND_B, tile_rows, ...)
- *   *hw_format (host)  : 3 = E2M3, 4 = E3M2, 5 = E2M1; pass it to the GEMM entry points as b_hw_format
- * The copy engine spreads every 16 codes to 16 bytes of shared memory; the products are the same as with
- * the one-byte-per-code form.  K must be a multiple of 128 (else MXQ_ESIZE: use mxq_mx_pack_operand);
- * MXQ_ESIZE also for the 8-bit element formats.  `scales` may be NULL (unit scales).
+ *                        bytes the GEMM reads per element with mxq_mx_pack_operand
+ *   hw_sf              : as mxq_mx_pack_operand(..., operand, tile_rows, ...)
+ *   *hw_format (host)  : 3 = E2M3, 4 = E3M2, 5 = E2M1; pass it to the GEMM entry points as a/b_hw_format
+ * MXQ_OPERAND_B, any of the three formats: against an 8-bit left operand the copy engine spreads every 16 codes
+ * to 16 bytes of shared memory; the products are the same as with the one-byte-per-code form.
+ * MXQ_OPERAND_A, E2M1 only: for the 4-bit x 4-bit GEMM (mxq_mx_gemm with a_hw_format = b_hw_format = 5), in
+ * which both operands stay packed two codes per byte in shared memory and every tensor-core instruction covers 64
+ * elements of K (tcgen05.mma.kind::mxf4): twice the arithmetic rate of the 8-bit kinds; K % 256 == 0 there.
+ * K must be a multiple of 128 (else MXQ_ESIZE: use mxq_mx_pack_operand); MXQ_ESIZE also for the 8-bit element
+ * formats.  `scales` may be NULL (unit scales).  No counterpart in the reference.
  */
 int mxq_mx_pack_operand_native(const uint8_t* scales, const uint8_t* elements, int64_t rows, int64_t K,
-                               int exp_bits, int frac_bits, int tile_rows, uint8_t* hw_codes, uint8_t* hw_sf,
-                               int* hw_format, void* stream);
+                               int exp_bits, int frac_bits, int operand, int tile_rows, uint8_t* hw_codes,
+                               uint8_t* hw_sf, int* hw_format, void* stream);
 
 /*
  * One-pass alternative to mxq_mxfp_extract + mxq_mx_pack_operand for the LEFT operand: quantise
@@ -201,7 +205,9 @@ int mxq_minifloat_quantize_pack(const void* x, int x_dtype, int64_t M, int64_t K
 /*
  * out[M,N] = A[M,K] * B[N,K]^T (+ bias[N]) on operands packed as MXQ_OPERAND_A / MXQ_OPERAND_B,
  * fp32 accumulation in tensor memory.  `b_tile_rows` is the value B was packed with.
- * a_hw_format: 0 / 1; b_hw_format: 0 / 1, or 3 / 4 / 5 for codes packed by mxq_mx_pack_operand_native.
+ * a_hw_format: 0 / 1; b_hw_format: 0 / 1, or 3 / 4 / 5 for codes packed by mxq_mx_pack_operand_native;
+ * a_hw_format = b_hw_format = 5 (both packed by mxq_mx_pack_operand_native): the 4-bit x 4-bit kernel
+ * (K % 256 == 0 and an output whose base and row pitch are multiples of 16 bytes, else MXQ_ESIZE).
  * out_dtype / bias dtype: MXQ_F32, MXQ_BF16 or MXQ_F16 (bias may be NULL). K % 32 == 0.
  * `status` (an int32 the GPU can write: device memory, or pinned host memory mapped into the device so
  * that the host can poll it without synchronising; may be NULL; must be zero on entry) receives a

@@ -29,7 +29,7 @@ SIGNATURES = {
     "mxq_mxfp_compose_strided": [_p, _p, _p, _i, _i64, _i64, _i64, _i, _i, _i, _i, _p],
     "mxq_mxfp_qdq_strided": [_p, _i, _p, _i, _i64, _i64, _i64, _i, _i, _i, _i, _i, _p],
     "mxq_mx_pack_operand": [_p, _p, _i64, _i64, _i, _i, _i, _i, _p, _p, _p, _p],
-    "mxq_mx_pack_operand_native": [_p, _p, _i64, _i64, _i, _i, _i, _p, _p, _p, _p],
+    "mxq_mx_pack_operand_native": [_p, _p, _i64, _i64, _i, _i, _i, _i, _p, _p, _p, _p],
     "mxq_mx_best_tile_rows": [_i64],
     "mxq_mx_quantize_pack": [_p, _i, _i64, _i64, _i, _i, _p, _p, _p, _p],
     "mxq_minifloat_quantize_pack": [_p, _i, _i64, _i64, _i, _i, _i, _p, _p, _p, _p],

@@ -38,20 +38,25 @@ using namespace tc;
 constexpr int BN_MAX = 224, BK = 128;            // widest right-operand tile (columns of the CTA tile)
 constexpr int A_TILE_ROWS = 256;                 // rows per scale-factor tile of the A operand
 constexpr int B_BYTES = BN_MAX * BK;             // 28 KiB reserved per stage, bn * 128 bytes of it used
-constexpr int SF_REGION = 2048;                  // A chunks (<= 1024) + B chunks (1024)
+constexpr int SF_REGION = 2048;                  // A chunks (<= 1024) + B chunks (1024) of one 128-element K step
 constexpr int BAR_BYTES = 256;
 constexpr int TMEM_COLS = 512;
 constexpr int SFA_COL = 448, SFB_COL = 456;      // accumulators occupy columns [0, 448)
+constexpr int SFA4_COL = 448, SFB4_COL = 464;    // 4-bit x 4-bit kernel: a stage holds two 128-element K steps of scales (8 columns each per operand)
 constexpr int THREADS = 192;                     // TMA producer, MMA issuer, four epilogue warps (epilogue that stores from registers)
 constexpr int EPI_TMA_WARPS = 8;                 // epilogue warps of the asynchronous (TMA-store) epilogue: two per TMEM lane quadrant
 constexpr int THREADS_TMA = 64 + EPI_TMA_WARPS * 32;
 
-template <int MH> struct Cfg {
+// MXF4: both operands are packed E2M1 nibbles (kind::mxf4): a stage's 128 bytes per row are 256 elements of K, so it
+// carries the scales of two 128-element K steps
+template <int MH, bool MXF4 = false> struct Cfg {
     static constexpr int BM = 128 * MH;
     static constexpr int A_BYTES = BM * BK;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SF_REGION;       // multiple of 1024
+    static constexpr int K_PER_STAGE = MXF4 ? 2 * BK : BK;          // elements of K per stage
+    static constexpr int SF_STEPS = MXF4 ? 2 : 1;                   // 128-element K steps of scales per stage
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SF_STEPS * SF_REGION;       // multiple of 1024
     static constexpr int STAGES = MH == 2 ? 3 : 4;
-    static constexpr int TX_FIXED = A_BYTES + MH * 512 + 1024;       // + the bytes of bn * BK codes of the right operand
+    static constexpr int TX_FIXED = A_BYTES + SF_STEPS * (MH * 512 + 1024);       // + the bytes of bn * BK codes of the right operand
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;   // + slack to align the ring
     static constexpr int SMEM_BYTES_TMA = SMEM_BYTES + EPI_TMA_WARPS * EPI_SLOT_BYTES;   // + staging of the asynchronous epilogue
 };
@@ -127,17 +132,18 @@ enum : int { EPI_REGS = 0, EPI_TMA = 1, EPI_GATHER = 2, EPI_GATHER_TMA = 3 };
 template <int EPI> constexpr int kernel_threads() {
     return EPI == EPI_TMA ? THREADS_TMA : EPI == EPI_GATHER_TMA ? THREADS_TMA + 32 : THREADS + (EPI == EPI_GATHER ? FWD_WARPS * 32 : 0);
 }
-template <int EPI, int MH> constexpr int kernel_smem() {
-    return EPI == EPI_TMA ? Cfg<MH>::SMEM_BYTES_TMA : EPI == EPI_GATHER_TMA ? Cfg<MH>::SMEM_BYTES_TMA + FWD_BUFS * FWD_BUF_BYTES : Cfg<MH>::SMEM_BYTES;
+template <int EPI, int MH, bool MXF4 = false> constexpr int kernel_smem() {
+    using C = Cfg<MH, MXF4>;
+    return EPI == EPI_TMA ? C::SMEM_BYTES_TMA : EPI == EPI_GATHER_TMA ? C::SMEM_BYTES_TMA + FWD_BUFS * FWD_BUF_BYTES : C::SMEM_BYTES;
 }
 
-template <int OUT_DT, int MH, int EPI>
+template <int OUT_DT, int MH, int EPI, bool MXF4 = false>
 __global__ void __launch_bounds__(kernel_threads<EPI>(), 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, void* __restrict__ out,
                const void* __restrict__ bias, int M, int N, int K, int bn, uint32_t idesc_base, int* status,
                const __grid_constant__ OutSpec outs, const __grid_constant__ OutMaps omaps, const __grid_constant__ FwdMaps fmaps) {
-    using C = Cfg<MH>;
+    using C = Cfg<MH, MXF4>;
     constexpr int STAGES = C::STAGES;
     constexpr bool MULTI = EPI == EPI_GATHER;
     constexpr bool TMA_EPI = EPI == EPI_TMA || EPI == EPI_GATHER_TMA;
@@ -161,13 +167,15 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     auto fwd_bar = [&](int b) { return bars + FWD_BAR_OFF + 8u * b; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int KT = (K + BK - 1) / BK;
+    const int KT = (K + C::K_PER_STAGE - 1) / C::K_PER_STAGE;       // stages per tile
+    const int KT128 = (K + BK - 1) / BK;                            // scale chunks per row tile
     const int MT = (M + C::BM - 1) / C::BM, NT = (N + bn - 1) / bn;
     const int num_tiles = MT * NT;
     // the right operand's copy counts the bytes it reads: dense 6-bit (formats 3, 4) and 4-bit (5) codes are narrower
     const uint32_t b_fmt = (idesc_base >> 10) & 7u;
     const uint32_t b_bits = b_fmt <= 1u ? 8u : (b_fmt == 5u ? 4u : 6u);
-    const uint32_t tx_bytes = (uint32_t)C::TX_FIXED + (uint32_t)(bn * BK) * b_bits / 8u;
+    // (packed nibbles of the 4-bit x 4-bit kernel fill the 128 bytes per row: 256 codes)
+    const uint32_t tx_bytes = (uint32_t)C::TX_FIXED + (MXF4 ? (uint32_t)(bn * BK) : (uint32_t)(bn * BK) * b_bits / 8u);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -208,8 +216,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             int mt, nt;
             tile_coords(tile, MT, NT, mt, nt);
             // A scale tiles are 256 rows (2 chunks); a 128-row CTA tile uses one of the two chunks
-            const uint8_t* sfa_tile = (MH == 2) ? sfa + (size_t)mt * KT * 1024 : sfa + (size_t)(mt >> 1) * KT * 1024 + (mt & 1) * 512;
-            const uint8_t* sfb_tile = sfb + (size_t)nt * KT * 1024;
+            const uint8_t* sfa_tile = (MH == 2) ? sfa + (size_t)mt * KT128 * 1024 : sfa + (size_t)(mt >> 1) * KT128 * 1024 + (mt & 1) * 512;
+            const uint8_t* sfb_tile = sfb + (size_t)nt * KT128 * 1024;
             for (int kt = 0; kt < KT && ok; ++kt, ++it) {
                 const int s = it % STAGES;
                 if (it >= STAGES) ok = mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, status, ST_PRODUCER_TIMEOUT);
@@ -217,10 +225,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (lane == 0) {
                     const uint32_t st = ring + s * C::STAGE_BYTES;
                     mbar_expect_tx(full_bar(s), tx_bytes);
-                    tma_load_2d(st, &map_a, kt * BK, mt * C::BM, full_bar(s));
-                    tma_load_2d(st + C::A_BYTES, &map_b, kt * BK, nt * bn, full_bar(s));
-                    bulk_load(st + C::A_BYTES + B_BYTES, sfa_tile + (size_t)kt * 1024, MH * 512, full_bar(s));
-                    bulk_load(st + C::A_BYTES + B_BYTES + 1024, sfb_tile + (size_t)kt * 1024, 1024, full_bar(s));
+                    tma_load_2d(st, &map_a, kt * C::K_PER_STAGE, mt * C::BM, full_bar(s));
+                    tma_load_2d(st + C::A_BYTES, &map_b, kt * C::K_PER_STAGE, nt * bn, full_bar(s));
+#pragma unroll
+                    for (int c = 0; c < C::SF_STEPS; ++c) {
+                        const size_t chunk = (size_t)(kt * C::SF_STEPS + c) * 1024;
+                        bulk_load(st + C::A_BYTES + B_BYTES + c * SF_REGION, sfa_tile + chunk, MH * 512, full_bar(s));
+                        bulk_load(st + C::A_BYTES + B_BYTES + c * SF_REGION + 1024, sfb_tile + chunk, 1024, full_bar(s));
+                    }
                 }
                 __syncwarp();
             }
@@ -249,20 +261,33 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (kt == 0 && tcount > 0 && ok) ok = mbar_wait(tmem_empty_bar(h), (tcount - 1) & 1, status, ST_MMA_TIMEOUT);
                     tc_fence_after();
                     if (ok && lane == 0) {
+                        constexpr int SA = MXF4 ? SFA4_COL : SFA_COL, SB = MXF4 ? SFB4_COL : SFB_COL;
                         if (h == 0) {
 #pragma unroll
-                            for (int hh = 0; hh < MH; ++hh) tmem_cp_32x128b(tmem_base + SFA_COL + 4 * hh, smem_desc(sf + 512 * hh, 0, 128, LAYOUT_NONE));
-                            tmem_cp_32x128b(tmem_base + SFB_COL, smem_desc(sf + 1024, 0, 128, LAYOUT_NONE));
-                            tmem_cp_32x128b(tmem_base + SFB_COL + 4, smem_desc(sf + 1536, 0, 128, LAYOUT_NONE));
+                            for (int c = 0; c < C::SF_STEPS; ++c) {             // 8 columns per operand and 128-element K step
+#pragma unroll
+                                for (int hh = 0; hh < MH; ++hh)
+                                    tmem_cp_32x128b(tmem_base + SA + 8 * c + 4 * hh, smem_desc(sf + c * SF_REGION + 512 * hh, 0, 128, LAYOUT_NONE));
+                                tmem_cp_32x128b(tmem_base + SB + 8 * c, smem_desc(sf + c * SF_REGION + 1024, 0, 128, LAYOUT_NONE));
+                                tmem_cp_32x128b(tmem_base + SB + 8 * c + 4, smem_desc(sf + c * SF_REGION + 1536, 0, 128, LAYOUT_NONE));
+                            }
                         }
                         const uint64_t a_desc = smem_desc(st + h * 16384, 16, 1024, LAYOUT_SW128);
 #pragma unroll
                         for (uint32_t k = 0; k < BK / 32; ++k) {
-                            // +32 bytes along K inside the 128-byte swizzle span = +2 in the address field;
-                            // scale-factor byte k of each 32-bit TMEM column
-                            const uint32_t idesc = idesc_base | (k << 29) | (k << 4);
-                            mma_mxf8f6f4(tmem_base + h * BN_MAX, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_base + SFA_COL + 4 * h,
-                                         tmem_base + SFB_COL, (kt > 0 || k > 0) ? 1u : 0u);
+                            // +32 bytes along K inside the 128-byte swizzle span = +2 in the address field
+                            if constexpr (MXF4) {
+                                // 64 elements per instruction: scale bytes (0, 1) or (2, 3) of the column set of K step k / 2
+                                const uint32_t id = (k & 1u) * 2u;
+                                const uint32_t idesc = idesc_base | (id << 29) | (id << 4);
+                                mma_mxf4(tmem_base + h * BN_MAX, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_base + SA + 8 * (k >> 1) + 4 * h,
+                                         tmem_base + SB + 8 * (k >> 1), (kt > 0 || k > 0) ? 1u : 0u);
+                            } else {
+                                // scale-factor byte k of each 32-bit TMEM column
+                                const uint32_t idesc = idesc_base | (k << 29) | (k << 4);
+                                mma_mxf8f6f4(tmem_base + h * BN_MAX, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_base + SA + 4 * h,
+                                             tmem_base + SB, (kt > 0 || k > 0) ? 1u : 0u);
+                            }
                         }
                         if (h == MH - 1) mma_commit(empty_bar(s));     // frees the stage once these MMAs have read it
                     }
@@ -557,38 +582,58 @@ static int hw_code_bits(int hw_format) {
     }
 }
 
-static bool make_operand_map(CUtensorMap* map, const void* codes, int64_t rows, int64_t K, int box_rows, int hw_format = HW_E4M3) {
+// nibbles: the 4-bit x 4-bit kernel keeps two codes per byte in shared memory too (256 codes per 128-byte row)
+static bool make_operand_map(CUtensorMap* map, const void* codes, int64_t rows, int64_t K, int box_rows, int hw_format = HW_E4M3,
+                             bool nibbles = false) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
     const int bits = hw_code_bits(hw_format);
-    const CUtensorMapDataType dt = bits == 8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+    const CUtensorMapDataType dt = nibbles ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN8B : bits == 8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                  : bits == 6 ? CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B;
     const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};                  // in codes, whatever their width
     const cuuint64_t strides[1] = {(cuuint64_t)(K * bits / 8)};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t box[2] = {(cuuint32_t)(nibbles ? 2 * BK : BK), (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     return fn(map, dt, 2, const_cast<void*>(codes), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // outs == nullptr: plain epilogue into `out`; otherwise the gather-fused epilogue into outs->ptr[]
-template <int OUT_DT, int MH, int EPI>
+template <int OUT_DT, int MH, int EPI, bool MXF4 = false>
 static int launch_gemm(const uint8_t* a_codes, const uint8_t* b_codes, const uint8_t* sfa, const uint8_t* sfb, void* out,
                        const void* bias, int M, int N, int K, int bn, uint32_t idesc, int* status, cudaStream_t st, const OutSpec* outs,
                        const OutMaps& omaps, const FwdMaps& fmaps) {
-    using C = Cfg<MH>;
-    constexpr int SMEM = kernel_smem<EPI, MH>();
+    using C = Cfg<MH, MXF4>;
+    constexpr int SMEM = kernel_smem<EPI, MH, MXF4>();
     static_assert(SMEM <= 232448, "more shared memory than a CTA can have");
     static bool attr_done[MAX_DEVICES] = {false};
-    const cudaError_t attr_err = raise_smem_limit(mx_gemm_kernel<OUT_DT, MH, EPI>, SMEM, attr_done);
+    const cudaError_t attr_err = raise_smem_limit(mx_gemm_kernel<OUT_DT, MH, EPI, MXF4>, SMEM, attr_done);
     if (attr_err != cudaSuccess) { set_last_cuda_error(attr_err); return MXQ_ELAUNCH; }
     CUtensorMap ma, mb;
-    if (!make_operand_map(&ma, a_codes, M, K, C::BM) || !make_operand_map(&mb, b_codes, N, K, bn, (int)((idesc >> 10) & 7u))) return MXQ_ELAUNCH;
+    if constexpr (MXF4) {
+        if (!make_operand_map(&ma, a_codes, M, K, C::BM, HW_E2M1, true) || !make_operand_map(&mb, b_codes, N, K, bn, HW_E2M1, true)) return MXQ_ELAUNCH;
+    } else {
+        if (!make_operand_map(&ma, a_codes, M, K, C::BM) || !make_operand_map(&mb, b_codes, N, K, bn, (int)((idesc >> 10) & 7u))) return MXQ_ELAUNCH;
+    }
     const int tiles = ((M + C::BM - 1) / C::BM) * ((N + bn - 1) / bn);
     const int grid = tiles < sm_count() ? tiles : sm_count();          // persistent: one CTA per SM
-    mx_gemm_kernel<OUT_DT, MH, EPI><<<grid, kernel_threads<EPI>(), SMEM, st>>>(ma, mb, sfa, sfb, out, bias, M, N, K, bn, idesc, status,
-                                                                         EPI == EPI_GATHER ? *outs : OutSpec{}, omaps, fmaps);
+    mx_gemm_kernel<OUT_DT, MH, EPI, MXF4><<<grid, kernel_threads<EPI>(), SMEM, st>>>(ma, mb, sfa, sfb, out, bias, M, N, K, bn, idesc, status,
+                                                                               EPI == EPI_GATHER ? *outs : OutSpec{}, omaps, fmaps);
     return check_launch();
+}
+
+// Both operands as packed E2M1 nibbles: tcgen05.mma.kind::mxf4 (twice the arithmetic per instruction).  Only with an
+// output the asynchronous epilogue can describe.
+template <int OUT_DT>
+static int launch_gemm_mxf4(const uint8_t* a_codes, const uint8_t* b_codes, const uint8_t* sfa, const uint8_t* sfb, void* out,
+                            const void* bias, int M, int N, int K, int bn, int* status, cudaStream_t st) {
+    OutMaps omaps{};
+    FwdMaps fmaps{};
+    if (!make_out_maps(&omaps, out, M, N, N, OUT_DT)) return MXQ_ESIZE;
+    // formats: E2M1 is 1 in this kind's encoding; K-major operands, N >> 3, E8M0 scales, M >> 4; 64 elements of K per instruction
+    const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | (1u << 23) | ((uint32_t)(128 >> 4) << 24);
+    if (M <= 128) return launch_gemm<OUT_DT, 1, EPI_TMA, true>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, bn, idesc, status, st, nullptr, omaps, fmaps);
+    return launch_gemm<OUT_DT, 2, EPI_TMA, true>(a_codes, b_codes, sfa, sfb, out, bias, M, N, K, bn, idesc, status, st, nullptr, omaps, fmaps);
 }
 
 // Maps of the gather-fused kernel that forwards with the copy engine: the local epilogue's maps and one box map per
@@ -658,6 +703,8 @@ static int sf_tile_rows(int operand, int tile_rows) { return operand == MXQ_OPER
 // the left operand is one byte per code; the right one may also be a dense 6- or 4-bit stream (whole 128-code K steps,
 // 32-byte aligned rows: what the packed tensor-map types ask for)
 static bool operand_formats_ok(int a_hw_format, int b_hw_format, const uint8_t* b_codes, int64_t K) {
+    if (a_hw_format == gemm::HW_E2M1)           // packed nibbles on the left: only against packed nibbles on the right (mxq_mx_gemm)
+        return false;
     if (a_hw_format != gemm::HW_E4M3 && a_hw_format != gemm::HW_E5M2) return false;
     const int bits = gemm::hw_code_bits(b_hw_format);
     if (bits == 0) return false;
@@ -698,15 +745,16 @@ extern "C" int mxq_mx_pack_operand(const uint8_t* scales, const uint8_t* element
 }
 
 extern "C" int mxq_mx_pack_operand_native(const uint8_t* scales, const uint8_t* elements, int64_t rows, int64_t K, int eb, int fb,
-                                          int tile_rows, uint8_t* hw_codes, uint8_t* hw_sf, int* hw_format, void* stream) {
-    if (rows <= 0 || K <= 0 || !elements || !hw_codes || !hw_sf || !hw_format) return MXQ_EINVAL;
+                                          int operand, int tile_rows, uint8_t* hw_codes, uint8_t* hw_sf, int* hw_format, void* stream) {
+    if (rows <= 0 || K <= 0 || (operand & ~1) || !elements || !hw_codes || !hw_sf || !hw_format) return MXQ_EINVAL;
+    if (operand == MXQ_OPERAND_A && !(eb == 2 && fb == 1)) return MXQ_ESIZE;      // a left operand only as nibbles for the 4-bit x 4-bit GEMM
     int fmt;
     if (eb == 2 && fb == 3) fmt = gemm::HW_E2M3;
     else if (eb == 3 && fb == 2) fmt = gemm::HW_E3M2;
     else if (eb == 2 && fb == 1) fmt = gemm::HW_E2M1;
     else return MXQ_ESIZE;
     if (K % 128 != 0 || reinterpret_cast<uintptr_t>(hw_codes) % 32 != 0 || reinterpret_cast<uintptr_t>(elements) % 16 != 0) return MXQ_ESIZE;
-    const int tile = sf_tile_rows(MXQ_OPERAND_B, tile_rows);
+    const int tile = sf_tile_rows(operand, tile_rows);
     if (tile <= 0) return MXQ_EINVAL;
     // the reference's code bytes are the hardware's codes (sign, exponent, fraction in the low bits, the same subnormals,
     // no Inf / NaN): only the scale bytes move, and the codes are squeezed to their width
@@ -725,6 +773,19 @@ extern "C" int mxq_mx_gemm(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw
                            int64_t M, int64_t N, int64_t K, int* status, void* stream) {
     if (M <= 0 || N <= 0 || K <= 0 || K % 32 != 0 || M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return MXQ_EINVAL;
     if (!a_codes || !a_sf || !b_codes || !b_sf || !out) return MXQ_EINVAL;
+    if (a_hw_format == gemm::HW_E2M1 && b_hw_format == gemm::HW_E2M1) {
+        // 4-bit x 4-bit: both operands dense nibbles, whole stages of 256 codes
+        const int bn4 = gemm::resolve_b_tile(b_tile_rows);
+        if (bn4 <= 0) return MXQ_EINVAL;
+        if (K % 256 != 0) return MXQ_ESIZE;
+        if ((reinterpret_cast<uintptr_t>(a_codes) | reinterpret_cast<uintptr_t>(b_codes)) % 32 != 0 ||
+            (reinterpret_cast<uintptr_t>(a_sf) | reinterpret_cast<uintptr_t>(b_sf) | reinterpret_cast<uintptr_t>(out)) % 16 != 0) return MXQ_EINVAL;
+        cudaStream_t st4 = (cudaStream_t)stream;
+        if (out_dtype == MXQ_F32) return gemm::launch_gemm_mxf4<MXQ_F32>(a_codes, b_codes, a_sf, b_sf, out, bias, (int)M, (int)N, (int)K, bn4, status, st4);
+        if (out_dtype == MXQ_BF16) return gemm::launch_gemm_mxf4<MXQ_BF16>(a_codes, b_codes, a_sf, b_sf, out, bias, (int)M, (int)N, (int)K, bn4, status, st4);
+        if (out_dtype == MXQ_F16) return gemm::launch_gemm_mxf4<MXQ_F16>(a_codes, b_codes, a_sf, b_sf, out, bias, (int)M, (int)N, (int)K, bn4, status, st4);
+        return MXQ_EINVAL;
+    }
     if (!operand_formats_ok(a_hw_format, b_hw_format, b_codes, K)) return MXQ_EINVAL;
     const int bn = gemm::resolve_b_tile(b_tile_rows);
     if (bn <= 0) return MXQ_EINVAL;

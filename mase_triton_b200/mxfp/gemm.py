@@ -28,7 +28,7 @@ _STATUS_TEXT = {1: "TMA producer wait ran out", 2: "MMA issuer wait ran out", 3:
 class PackedOperand:
     codes: Tensor        # uint8 [rows, K] hardware element codes ([rows, K * bits / 8] for the 6- / 4-bit formats)
     sf: Tensor           # uint8, hardware scale-factor chunks
-    hw_format: int       # 0 = E4M3, 1 = E5M2; right operand only: 3 = E2M3, 4 = E3M2, 5 = E2M1 as dense bit streams
+    hw_format: int       # 0 = E4M3, 1 = E5M2; dense bit streams: 3 = E2M3, 4 = E3M2 (right operand), 5 = E2M1 (either side)
     rows: int
     K: int
     operand: int         # 0: packed as the left operand (A), 1: as the right operand (B)
@@ -79,9 +79,12 @@ OPERAND_A, OPERAND_B = 0, 1
 
 
 def native_ok(exp_bits: int, frac_bits: int, K: int, operand: int) -> bool:
-    """Whether the tensor cores can read the codes in their own 6- / 4-bit width (right operand, FP6 / FP4 element
-    formats, whole 128-code K steps)."""
-    return operand == OPERAND_B and K % 128 == 0 and (exp_bits, frac_bits) in ((2, 3), (3, 2), (2, 1))
+    """Whether the tensor cores can read the codes in their own 6- / 4-bit width: a right operand in an FP6 / FP4
+    element format (whole 128-code K steps), or a left operand in E2M1 for the 4-bit x 4-bit GEMM (whole 256-code
+    stages; the right operand must then be native E2M1 too)."""
+    if operand == OPERAND_B:
+        return K % 128 == 0 and (exp_bits, frac_bits) in ((2, 3), (3, 2), (2, 1))
+    return K % 256 == 0 and (exp_bits, frac_bits) == (2, 1)
 
 
 NATIVE_SUBBYTE_DEFAULT = False
@@ -116,7 +119,7 @@ def pack_codes(scales: Tensor | None, elements: Tensor, rows: int, K: int, exp_b
         codes = torch.empty((rows, K * bits // 8), dtype=torch.uint8, device=dev)
         with torch.cuda.device(dev):
             rc = L.mxq_mx_pack_operand_native(None if scales is None else scales.data_ptr(), elements.data_ptr(), rows, K, exp_bits,
-                                              frac_bits, tile_rows, codes.data_ptr(), sf.data_ptr(), ctypes.addressof(fmt),
+                                              frac_bits, operand, tile_rows, codes.data_ptr(), sf.data_ptr(), ctypes.addressof(fmt),
                                               _lib.stream_ptr(dev))
         _lib.check(rc, "mxq_mx_pack_operand_native")
         return PackedOperand(codes, sf, fmt.value, rows, K, operand, tile_rows)
@@ -136,12 +139,13 @@ def pack_operand(scales: Tensor, elements: Tensor, rows: int, K: int, meta: MXFP
     return pack_codes(scales, elements, rows, K, meta.element_exp_bits, meta.element_frac_bits, operand, tile_rows, native)
 
 
-def quantize_pack(x: Tensor, meta: MXFPMeta, operand: int = OPERAND_A, tile_rows: int | None = None) -> PackedOperand:
+def quantize_pack(x: Tensor, meta: MXFPMeta, operand: int = OPERAND_A, tile_rows: int | None = None,
+                  native: bool | None = None) -> PackedOperand:
     """Quantise a ``[..., K]`` tensor along its last dim and pack it."""
     K = x.shape[-1]
     rows = x.numel() // K
     scales, elements = kernels.extract_mxfp_components(x.reshape(-1), meta)
-    return pack_operand(scales, elements, rows, K, meta, operand, tile_rows)
+    return pack_operand(scales, elements, rows, K, meta, operand, tile_rows, native)
 
 
 def quantize_pack_fused(x: Tensor, meta: MXFPMeta) -> PackedOperand:
@@ -258,6 +262,7 @@ def mx_gemm(a: PackedOperand, b: PackedOperand, out_dtype: torch.dtype, bias: Te
             out: Tensor | None = None) -> Tensor:
     """``a [M,K] @ b[N,K]^T (+ bias)`` on the tensor cores; returns ``[M, N]`` of ``out_dtype``."""
     assert a.K == b.K and out_dtype in _lib.DTYPE_ID and a.operand == OPERAND_A and b.operand == OPERAND_B
+    assert a.hw_format <= 1 or (a.hw_format == 5 and b.hw_format == 5), "a packed 4-bit left operand needs a packed 4-bit right one"
     dev = a.codes.device
     _raise_if_failed(dev)
     if out is None:

@@ -257,3 +257,29 @@ def test_native_subbyte_weight_equals_widened(lib, x_meta, w_meta, M, N, K):
         G.check_status(DEV)
         assert within_tolerance(y_dense, y32), f"max err {(y_dense.float() - y32).abs().max().item()}"
         assert torch.equal(y_dense, y_wide)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 448, 256), (300, 1000, 768), (128, 224, 512), (1000, 4096, 1024), (1, 16, 256)])
+def test_fp4_by_fp4_on_the_4bit_tensor_core_kind(lib, M, N, K):
+    """MXFP4 x MXFP4 with both operands kept as packed nibbles (tcgen05 kind::mxf4, 64 elements of K per instruction)
+    against an fp32 matmul of the dequantised operands, and against the same product computed with the codes widened
+    to E4M3 bytes (every product of two E2M1 values and two power-of-two scales is exact in both)."""
+    torch.manual_seed(M + N + K)
+    x = (torch.randn(M, K, device=DEV) * 2).to(torch.bfloat16)
+    w = (0.05 * torch.randn(N, K, device=DEV)).to(torch.bfloat16)
+    a4 = G.quantize_pack(x, OCP_MXFP4_E2M1, G.OPERAND_A, native=True)
+    b4 = G.quantize_pack(w, OCP_MXFP4_E2M1, G.OPERAND_B, native=True)
+    assert a4.hw_format == 5 and b4.hw_format == 5 and a4.codes.numel() == M * K // 2 and b4.codes.numel() == N * K // 2
+    a8, b8 = G.quantize_pack(x, OCP_MXFP4_E2M1), G.quantize_pack(w, OCP_MXFP4_E2M1, G.OPERAND_B)
+    y32 = dequant(x, OCP_MXFP4_E2M1) @ dequant(w, OCP_MXFP4_E2M1).t()
+    bias = torch.randn(N, device=DEV).to(torch.bfloat16)
+    for dt in (torch.float32, torch.bfloat16):
+        y4 = G.mx_gemm(a4, b4, dt)
+        y8 = G.mx_gemm(a8, b8, dt)
+        G.check_status(DEV)
+        assert within_tolerance(y4, y32), f"max err {(y4.float() - y32).abs().max().item()}"
+        # same exact products; only the order of the fp32 additions inside an instruction may differ
+        assert within_tolerance(y4, y8.float())
+    yb = G.mx_gemm(a4, b4, torch.bfloat16, bias)
+    G.check_status(DEV)
+    assert within_tolerance(yb, y32 + bias.float())
