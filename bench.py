@@ -363,6 +363,23 @@ def extras_single_gpu(dev, steps: int, warmup: int, peak: float) -> dict:
         "XWq_route": "512 rows: codes expanded in the GEMM's loader; 8192 rows: expanded once by the compose kernel, same GEMM on dense operands",
         "frac_of_measured_bf16_burst": {k: round(flops / v / 1e9 / bf16_peak, 3) for k, v in t.items()},
         "note": "fused = this library's tcgen05 kind::f16 GEMM (256x256 tiles); separate = dequantise kernels + torch.nn.functional.linear"}
+    # the same shape with MXFP4 activation and weight: both stay packed nibbles, tcgen05 kind::mxf4 (64 elements of K per instruction)
+    a4 = G.quantize_pack(xc, OCP_MXFP4_E2M1, G.OPERAND_A, native=True)
+    b4 = G.quantize_pack(wc, OCP_MXFP4_E2M1, G.OPERAND_B, native=True)
+    a48, b48 = G.quantize_pack(xc, OCP_MXFP4_E2M1), G.quantize_pack(wc, OCP_MXFP4_E2M1, G.OPERAND_B)
+    f4 = MXFPLinearPTQ.from_linear(fc, OCP_MXFP4_E2M1, OCP_MXFP4_E2M1, None, "XqWqB", "fused")
+    s4 = MXFPLinearPTQ.from_linear(fc, OCP_MXFP4_E2M1, OCP_MXFP4_E2M1, None, "XqWqB", "separate")
+    same4 = bool(torch.equal(G.mx_gemm(a4, b4, torch.bfloat16), G.mx_gemm(a48, b48, torch.bfloat16)))
+    t4 = {"gemm_packed_nibbles_kind_mxf4": graph_time(lambda: G.mx_gemm(a4, b4, torch.bfloat16, out=o), max(reps, 20), rounds=9),
+          "gemm_codes_widened_to_bytes_kind_mxf8f6f4": graph_time(lambda: G.mx_gemm(a48, b48, torch.bfloat16, out=o), max(reps, 20)),
+          "fused_linear": graph_time(lambda: f4(xc), reps), "separate_linear": graph_time(lambda: s4(xc), max(3, reps // 2))}
+    G.check_status(dev)
+    out["cfg4_shape_mxfp4_x_mxfp4"] = {
+        "TFLOPs": {k: round(flops / v / 1e9, 1) for k, v in t4.items()}, "ms": {k: round(v, 4) for k, v in t4.items()},
+        "gemm_frac_of_9000_nominal_fp4": round(flops / t4["gemm_packed_nibbles_kind_mxf4"] / 1e9 / 9000, 3),
+        "packed_nibble_gemm_equals_widened_gemm_bit_for_bit": same4,
+        "note": "fused linear = extract + nibble pack of the activation (three kernels) + the kind::mxf4 GEMM"}
+    del a4, b4, a48, b48, f4, s4
     del fc, fused, sep, wq_f, wq_s, xq_f, xq_s, a, b, o, xc, wc, x_short
     torch.cuda.empty_cache()
 

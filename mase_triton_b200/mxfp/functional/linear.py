@@ -45,7 +45,8 @@ def _fused_linear(x: Tensor, x_meta: MXFPMeta | None, w: Tensor | None, w_scales
     """``backend="fused"``: every layer type runs a hand-written tensor-core GEMM of this library.
 
     * ``XqWq`` with 32-element blocks and is_finite elements: both operands stay quantised, block-scaled
-      ``tcgen05.mma.kind::mxf8f6f4`` GEMM (fp32 / bf16 / fp16 activations);
+      ``tcgen05.mma.kind::mxf8f6f4`` GEMM (fp32 / bf16 / fp16 activations); MXFP4 activation x MXFP4 weight with
+      ``in_features`` a multiple of 256 stay packed nibbles and run on ``kind::mxf4`` at twice the rate;
     * every other combination on bf16 / fp16 activations: ``tcgen05.mma.kind::f16`` GEMM; an ``Xq``
       activation is fake-quantised by one bandwidth-bound kernel first, a ``Wq`` weight is expanded from
       its codes inside the GEMM's operand loader while the activation is short, and once by the compose
@@ -57,7 +58,8 @@ def _fused_linear(x: Tensor, x_meta: MXFPMeta | None, w: Tensor | None, w_scales
     K = x.shape[-1]
     w_blocks_along_k = kind.w_quantised and len(w_shape) == 2 and w_tensor_meta.block_dim in (1, -1) and _gemm.supported(w_tensor_meta.meta)
     if kind.x_quantised and kind.w_quantised and block_scaled_ok(x, x_meta, w_tensor_meta):
-        wq = _gemm.packed_weight(w_scales, w_elements, w_shape, w_tensor_meta.meta, rows=x.numel() // K)
+        wq = _gemm.packed_weight(w_scales, w_elements, w_shape, w_tensor_meta.meta, rows=x.numel() // K,
+                                 nibbles=_gemm.fp4_pair(x_meta, w_tensor_meta.meta, K))
         return _gemm.mx_linear(x, x_meta, wq, bias)
     reason = tc_linear.why_not(x, K)
     if reason is not None:

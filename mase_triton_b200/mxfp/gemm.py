@@ -90,6 +90,16 @@ def native_ok(exp_bits: int, frac_bits: int, K: int, operand: int) -> bool:
 NATIVE_SUBBYTE_DEFAULT = False
 
 
+def is_e2m1(meta: MXFPMeta | None) -> bool:
+    return meta is not None and (meta.element_exp_bits, meta.element_frac_bits) == (2, 1)
+
+
+def fp4_pair(x_meta: MXFPMeta | None, w_meta: MXFPMeta | None, K: int) -> bool:
+    """MXFP4 activation and MXFP4 weight with whole 256-element stages: both operands can stay packed nibbles and
+    the GEMM runs on the 4-bit x 4-bit tensor-core kind (twice the arithmetic rate of the 8-bit kinds)."""
+    return is_e2m1(x_meta) and is_e2m1(w_meta) and supported(x_meta) and supported(w_meta) and K % 256 == 0
+
+
 def pack_codes(scales: Tensor | None, elements: Tensor, rows: int, K: int, exp_bits: int, frac_bits: int, operand: int,
                tile_rows: int | None = None, native: bool | None = None) -> PackedOperand:
     """Element codes (one per byte, sign at bit ``exp_bits + frac_bits``) of a ``[rows, K]`` tensor and the
@@ -166,11 +176,14 @@ def quantize_pack_fused(x: Tensor, meta: MXFPMeta) -> PackedOperand:
     return PackedOperand(codes, sf, fmt.value, rows, K, OPERAND_A)
 
 
-def pack_activation(x: Tensor, meta: MXFPMeta) -> PackedOperand:
+def pack_activation(x: Tensor, meta: MXFPMeta, nibbles: bool = False) -> PackedOperand:
     """Quantise a ``[..., K]`` activation along its last dim, as ``meta`` says (element format and rounding
     mode), into the left operand of the GEMM: one kernel for MXFP8 / round to nearest, extract + pack
-    otherwise.  The result can be fed to several layers that share the activation (q / k / v, gate / up)
+    otherwise.  ``nibbles``: keep an MXFP4 activation as packed 4-bit codes for a weight packed the same way.
+    The result can be fed to several layers that share the activation (q / k / v, gate / up)
     through ``MXFPLinearPTQ.forward_packed`` so that it is quantised once."""
+    if nibbles:
+        return quantize_pack(x, meta, OPERAND_A, native=True)
     return quantize_pack_fused(x, meta) if one_pass_ok(meta) else quantize_pack(x, meta)
 
 
@@ -244,16 +257,17 @@ def choose_tile_rows(w_scales: Tensor, w_elements: Tensor, shape: tuple[int, int
     return choice
 
 
-def packed_weight(w_scales: Tensor, w_elements: Tensor, shape: tuple[int, int], meta: MXFPMeta, rows: int | None = None) -> PackedOperand:
+def packed_weight(w_scales: Tensor, w_elements: Tensor, shape: tuple[int, int], meta: MXFPMeta, rows: int | None = None,
+                  nibbles: bool = False) -> PackedOperand:
     """Packed form of a quantised weight.  The result is kept on the ``w_elements`` tensor object itself
     (so it dies with it and can never be confused with another tensor that re-uses the same address)
     and is rebuilt when either code tensor was modified in place or replaced, or when the tile width chosen
     for ``rows`` activation rows (:func:`choose_tile_rows`) differs from the one it was packed for."""
     tile = choose_tile_rows(w_scales, w_elements, tuple(shape), meta, rows)
-    tag = (w_elements._version, w_scales.data_ptr(), w_scales._version, tuple(shape), meta, tile)
+    tag = (w_elements._version, w_scales.data_ptr(), w_scales._version, tuple(shape), meta, tile, nibbles)
     cached = getattr(w_elements, "_mxq_packed", None)
     if cached is None or cached[0] != tag:
-        cached = (tag, pack_operand(w_scales, w_elements, shape[0], shape[1], meta, OPERAND_B, tile_rows=tile))
+        cached = (tag, pack_operand(w_scales, w_elements, shape[0], shape[1], meta, OPERAND_B, tile_rows=tile, native=nibbles))
         w_elements._mxq_packed = cached
     return cached[1]
 
@@ -321,13 +335,18 @@ def mx_linear(x: Tensor, x_meta: MXFPMeta, w: PackedOperand, bias: Tensor | None
     """``quantise(x) @ w^T (+ bias)``.  Round-to-nearest activations go through the single C entry point
     ``mxq_mx_linear`` (quantisation, packing and the tensor-core GEMM enqueued back to back on the
     current stream); the other rounding modes are quantised by the extract kernel, which implements
-    them, packed, and multiplied by the same GEMM."""
+    them, packed, and multiplied by the same GEMM.  An MXFP4 activation against a weight packed as 4-bit codes is
+    packed as 4-bit codes too and multiplied on the 4-bit x 4-bit tensor-core kind."""
     _lib.require_cuda(x, "mx_linear")
     assert supported(x_meta) and w.operand == OPERAND_B and x.shape[-1] == w.K
     if x.dtype not in _lib.DTYPE_ID:
         x = x.float()
     x2 = x.reshape(-1, w.K).contiguous()
     M, dev = x2.shape[0], x2.device
+    if w.hw_format == 5 and is_e2m1(x_meta) and w.K % 256 == 0:
+        # MXFP4 x MXFP4 with the weight kept as packed nibbles: the activation is packed the same way (kind::mxf4)
+        y = mx_gemm(pack_activation(x2, x_meta, nibbles=True), w, x2.dtype, bias=bias, out=out)
+        return y.reshape(*x.shape[:-1], w.rows)
     if x_meta.round_mode != "rn":
         y = mx_gemm(quantize_pack(x2, x_meta), w, x2.dtype, bias=bias, out=out)
         return y.reshape(*x.shape[:-1], w.rows)

@@ -100,7 +100,10 @@ class MXFPLinearPTQ(PTQLinearBase):
                  or self._tc_codes.device != self.w_elements.device or self._tc_info[2] != tile)
         if stale:
             n, k = self.w_tensor_meta.shape
-            p = _gemm.pack_operand(self.w_scales.data, self.w_elements.data, n, k, self.w_tensor_meta.meta, _gemm.OPERAND_B, tile_rows=tile)
+            # an MXFP4 layer (activation and weight) keeps its weight as packed 4-bit codes for the 4-bit x 4-bit GEMM
+            nibbles = _gemm.fp4_pair(self.x_mxfp_meta, self.w_tensor_meta.meta, k)
+            p = _gemm.pack_operand(self.w_scales.data, self.w_elements.data, n, k, self.w_tensor_meta.meta, _gemm.OPERAND_B, tile_rows=tile,
+                                   native=nibbles)
             self._tc_codes, self._tc_sf = p.codes, p.sf
             self._tc_info = (versions, p.hw_format, p.tile_rows)
         n, k = self.w_tensor_meta.shape
@@ -144,7 +147,8 @@ class MXFPLinearPTQ(PTQLinearBase):
 
         assert "Xq" in self.layer_type and "Wq" in self.layer_type and _gemm.supported(self.x_mxfp_meta), \
             "pack_input needs a layer with quantised activation and weight (32-element blocks)"
-        return _gemm.pack_activation(input.reshape(-1, self.in_features), self.x_mxfp_meta)
+        return _gemm.pack_activation(input.reshape(-1, self.in_features), self.x_mxfp_meta,
+                                     nibbles=_gemm.fp4_pair(self.x_mxfp_meta, self.w_tensor_meta.meta, self.in_features))
 
     @torch.no_grad()
     def forward_packed(self, packed, out_dtype: torch.dtype = torch.bfloat16, lead_shape: tuple[int, ...] | None = None) -> Tensor:

@@ -203,3 +203,31 @@ def test_kernel_manager_autotune_picks_a_tile_width(lib):
     finally:
         KernelManager.disable_autotune()
     assert torch.equal(got, want) and torch.equal(got_functional, want)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_mxfp4_layer_runs_on_packed_nibbles(lib, dtype):
+    """An MXFP4 x MXFP4 fused layer keeps weight and activation as packed 4-bit codes (the 4-bit x 4-bit tensor-core
+    kind) when in_features is a multiple of 256, and the widened 8-bit form otherwise; both match the fp32 linear of
+    the oracle-dequantised operands, and the functional entry gives the layer's bytes."""
+    torch.manual_seed(41)
+    for K, packed in ((512, True), (384, False)):
+        fc = torch.nn.Linear(K, 1000, bias=True, device=DEV, dtype=dtype)
+        layer = MXFPLinearPTQ.from_linear(fc, OCP_MXFP4_E2M1, OCP_MXFP4_E2M1, None, "XqWqB", backend="fused")
+        x = (torch.randn(3, 100, K, device=DEV) * 2).to(dtype)
+        y = layer(x)
+        G.check_status(DEV)
+        wq = layer.tensor_core_weight()
+        assert (wq.hw_format == 5) == packed and wq.codes.numel() == (1000 * K // 2 if packed else 1000 * K)
+        def oracle_dq(t):
+            flat = t.detach().cpu().reshape(-1)
+            return oracle.compose_mxfp_tensor(*oracle.extract_mxfp_components(flat, OCP_MXFP4_E2M1), OCP_MXFP4_E2M1, torch.float32).reshape(-1, K)
+
+        y32 = torch.nn.functional.linear(oracle_dq(x), oracle_dq(fc.weight), fc.bias.detach().float().cpu()).reshape(3, 100, 1000)
+        tol = 2.0**-7 * y32.abs() + 2.0**-7 * y32.pow(2).mean().sqrt()
+        assert y.shape == (3, 100, 1000) and y.dtype == dtype and bool(((y.float().cpu() - y32).abs() <= tol).all())
+        y_fn = MX.mxfp_linear(x, OCP_MXFP4_E2M1, None, layer.w_scales, layer.w_elements, layer.w_tensor_meta, layer.bias, None, None, None,
+                              "XqWqB", "fused")
+        shared = layer.forward_packed(layer.pack_input(x), dtype, lead_shape=(3, 100))
+        G.check_status(DEV)
+        assert torch.equal(y_fn, y) and torch.equal(shared, y)
