@@ -378,7 +378,7 @@ def extras_single_gpu(dev, steps: int, warmup: int, peak: float) -> dict:
         "TFLOPs": {k: round(flops / v / 1e9, 1) for k, v in t4.items()}, "ms": {k: round(v, 4) for k, v in t4.items()},
         "gemm_frac_of_9000_nominal_fp4": round(flops / t4["gemm_packed_nibbles_kind_mxf4"] / 1e9 / 9000, 3),
         "packed_nibble_gemm_equals_widened_gemm_bit_for_bit": same4,
-        "note": "fused linear = extract + nibble pack of the activation (three kernels) + the kind::mxf4 GEMM"}
+        "note": "fused linear = one-pass quantise + nibble pack of the activation, then the kind::mxf4 GEMM"}
     del a4, b4, a48, b48, f4, s4
     del fc, fused, sep, wq_f, wq_s, xq_f, xq_s, a, b, o, xc, wc, x_short
     torch.cuda.empty_cache()

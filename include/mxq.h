@@ -187,6 +187,8 @@ int mxq_mx_pack_operand_native(const uint8_t* scales, const uint8_t* elements, i
  * One-pass alternative to mxq_mxfp_extract + mxq_mx_pack_operand for the LEFT operand: quantise
  * x [M,K] to MXFP8 (E4M3 or E5M2 elements, 32-element blocks along K, round to nearest) directly
  * into hardware codes and MXQ_OPERAND_A scale chunks. Same bytes as the two-step route.
+ * E2M1 elements (MXFP4) are written as packed nibbles, M * K / 2 bytes, *hw_format = 5: the left operand
+ * of the 4-bit x 4-bit GEMM, the bytes of mxq_mxfp_extract + mxq_mx_pack_operand_native(MXQ_OPERAND_A).
  * Returns MXQ_ESIZE for other element formats or unaligned buffers (use the two-step route).
  */
 int mxq_mx_quantize_pack(const void* x, int x_dtype, int64_t M, int64_t K, int exp_bits, int frac_bits,

@@ -958,6 +958,8 @@ __global__ void __launch_bounds__(kThreads) mx_quant_pack_flat_kernel(const void
     const int64_t first = (int64_t)blockIdx.x * (kThreads * U) + threadIdx.x;
     const F f{};
     constexpr uint32_t probe = (F{}.eb() == 4) ? 0x01010101u : 0x04040404u;    // carry out of the magnitude byte: a code the hardware reads as NaN / Inf
+    // E2M1: the codes are stored two per byte (the 4-bit x 4-bit GEMM's operand); every E2M1 code is one the hardware has
+    constexpr bool NIB = (F{}.eb() == 2 && F{}.fb() == 1);
     constexpr bool BF16 = std::is_same<KIn, KBF16>::value;
     Pack<16> p[U];
     uint32_t amax[U], amin[U];             // bf16: packed pairs (see bf16_abs_range); else fp32 bits of the maximum
@@ -1007,7 +1009,7 @@ __global__ void __launch_bounds__(kThreads) mx_quant_pack_flat_kernel(const void
             } else {
                 const float inv = __uint_as_float(h & 0x7F800000u);
                 bool short_form = false;
-                if constexpr (F32) short_form = !__any_sync(__activemask(), f32x4_absmin(p[j]) < __uint_as_float(w2));
+                if constexpr (F32 && PkFmt<F>::RARE_SUBRANGE) short_form = !__any_sync(__activemask(), f32x4_absmin(p[j]) < __uint_as_float(w2));
                 if (short_form) {
                     o.w[0] = f32_codes4_normal(p[j].w, inv, f);
                 } else {
@@ -1021,8 +1023,10 @@ __global__ void __launch_bounds__(kThreads) mx_quant_pack_flat_kernel(const void
                     for (int i = 0; i < V; i += 4) o.w[i >> 2] = pack4_codes(&mag[i], &qb[i], f);
                 }
             }
+            if constexpr (!NIB) {
 #pragma unroll
-            for (int i = 0; i < V / 4; ++i) bad |= ((o.w[i] & 0x7F7F7F7Fu) + probe) & 0x80808080u;
+                for (int i = 0; i < V / 4; ++i) bad |= ((o.w[i] & 0x7F7F7F7Fu) + probe) & 0x80808080u;
+            }
         } else {
             // Inf/NaN block: scale byte 255 is NaN for the tensor cores too; the codes do not matter
 #pragma unroll
@@ -1031,14 +1035,29 @@ __global__ void __launch_bounds__(kThreads) mx_quant_pack_flat_kernel(const void
         }
         // the lanes of a block agree with xor-shuffles that every lane of the warp executes (a vote with a mask per
         // group compiles to a loop over the groups); lanes of Inf/NaN blocks contribute nothing
+        if constexpr (!NIB) {
 #pragma unroll
-        for (int w = 1; w < G; w <<= 1) bad |= __shfl_xor_sync(0xFFFFFFFFu, bad, w);
-        if (bad != 0u) {
+            for (int w = 1; w < G; w <<= 1) bad |= __shfl_xor_sync(0xFFFFFFFFu, bad, w);
+            if (bad != 0u) {
 #pragma unroll
-            for (int i = 0; i < V / 4; ++i) o.w[i] = halve_codes4<F{}.fb()>(o.w[i]);
-            if (sbyte < 255u) sbyte += 1u;
+                for (int i = 0; i < V / 4; ++i) o.w[i] = halve_codes4<F{}.fb()>(o.w[i]);
+                if (sbyte < 255u) sbyte += 1u;
+            }
+            if (vec < n_vec) store_pack<V>(hw_codes + vec * V, o);
+        } else {
+            // four code bytes -> two bytes of nibbles (element 2i in the low nibble of byte i)
+            uint32_t nib = 0u;
+#pragma unroll
+            for (int i = 0; i < V / 4; ++i) {
+                uint32_t t = o.w[i] & 0x0F0F0F0Fu;
+                t |= t >> 4;
+                nib |= ((t & 0xFFu) | ((t >> 8) & 0xFF00u)) << (16 * i);
+            }
+            if (vec < n_vec) {
+                if constexpr (V == 8) *reinterpret_cast<uint32_t*>(hw_codes + vec * 4) = nib;
+                else *reinterpret_cast<uint16_t*>(hw_codes + vec * 2) = (uint16_t)nib;
+            }
         }
-        if (vec < n_vec) store_pack<V>(hw_codes + vec * V, o);
         sb_of[j] = sbyte;
     }
     // lane `sub` of each group stores the scale byte of access `sub`, so that the position in the chunked array is
@@ -1067,10 +1086,10 @@ __global__ void __launch_bounds__(kThreads) mx_quant_pack_flat_kernel(const void
 namespace mxq {
 int quantize_pack_left_operand(const void* x, int x_dtype, int64_t M, int64_t K, int eb, int fb, uint8_t* hw_codes,
                                uint8_t* hw_sf, int64_t sf_bytes, int* hw_format, cudaStream_t st) {
-    const bool e4m3 = (eb == 4 && fb == 3), e5m2 = (eb == 5 && fb == 2);
-    if (!(e4m3 || e5m2) || K % 32 != 0 || M * K / 32 >= (1ll << 31)) return MXQ_ESIZE;
+    const bool e4m3 = (eb == 4 && fb == 3), e5m2 = (eb == 5 && fb == 2), e2m1 = (eb == 2 && fb == 1);
+    if (!(e4m3 || e5m2 || e2m1) || K % 32 != 0 || M * K / 32 >= (1ll << 31)) return MXQ_ESIZE;
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(hw_codes) | reinterpret_cast<uintptr_t>(hw_sf)) % 16 != 0) return MXQ_ESIZE;
-    *hw_format = e5m2 ? 1 : 0;
+    *hw_format = e2m1 ? 5 : (e5m2 ? 1 : 0);          // E2M1: packed nibbles, the left operand of the 4-bit x 4-bit GEMM
     // padding rows / K blocks of the chunked scale array must read as 2^0; none exist for whole tiles
     if ((M % 256 != 0 || K % 128 != 0) && cudaMemsetAsync(hw_sf, 127, (size_t)sf_bytes, st) != cudaSuccess) return check_launch();
     PackGeom g;
@@ -1091,7 +1110,7 @@ int quantize_pack_left_operand(const void* x, int x_dtype, int64_t M, int64_t K,
             if (words) mx_quant_pack_flat_kernel<KIn, F, true><<<grid, kThreads, 0, st>>>(x, hw_codes, hw_sf, n_vec, g);
             else mx_quant_pack_flat_kernel<KIn, F, false><<<grid, kThreads, 0, st>>>(x, hw_codes, hw_sf, n_vec, g);
         };
-        if (e4m3) go(FmtCT<4, 3, true, RM_RN>{}); else go(FmtCT<5, 2, true, RM_RN>{});
+        if (e4m3) go(FmtCT<4, 3, true, RM_RN>{}); else if (e5m2) go(FmtCT<5, 2, true, RM_RN>{}); else go(FmtCT<2, 1, true, RM_RN>{});
         rc = check_launch();
     });
     return rc;

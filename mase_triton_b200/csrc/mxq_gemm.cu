@@ -841,9 +841,13 @@ static int linear_with_scratch(const void* x, int x_dtype, int64_t M, int64_t K,
     uint8_t* ref_scales = codes + M * K;
     uint8_t* sf = ref_scales + ((M * K / 32 + 255) / 256) * 256;
     int x_fmt = 0;
-    // MXFP8 activations: one pass straight into the operand layout; other formats take extract + pack
-    int rc = quantize_pack_left_operand(x, x_dtype, M, K, x_eb, x_fb, codes, sf, mxq_mx_sf_bytes(M, K, MXQ_OPERAND_A, 0), &x_fmt,
-                                        (cudaStream_t)stream);
+    // MXFP8 activations: one pass straight into the operand layout; other formats take extract + pack.  An MXFP4
+    // activation is packed as nibbles (one pass too) only against a weight packed as nibbles: the 4-bit x 4-bit GEMM.
+    const bool x_e2m1 = x_eb == 2 && x_fb == 1;
+    const bool nibble_pair = x_e2m1 && w_hw_format == gemm::HW_E2M1 && K % 256 == 0;
+    int rc = (x_e2m1 && !nibble_pair) ? MXQ_ESIZE
+                                      : quantize_pack_left_operand(x, x_dtype, M, K, x_eb, x_fb, codes, sf, mxq_mx_sf_bytes(M, K, MXQ_OPERAND_A, 0),
+                                                                   &x_fmt, (cudaStream_t)stream);
     if (rc == MXQ_OK) return mxq_mx_gemm(codes, sf, x_fmt, w_codes, w_sf, w_hw_format, w_tile_rows, out, out_dtype, bias, M, N, K, status, stream);
     if (rc != MXQ_ESIZE) return rc;
     rc = mxq_mxfp_extract(x, x_dtype, ref_scales, codes, M * K, 32, x_eb, x_fb, 1, MXQ_RN, stream);

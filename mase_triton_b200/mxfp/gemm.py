@@ -159,14 +159,16 @@ def quantize_pack(x: Tensor, meta: MXFPMeta, operand: int = OPERAND_A, tile_rows
 
 
 def quantize_pack_fused(x: Tensor, meta: MXFPMeta) -> PackedOperand:
-    """One-kernel version of :func:`quantize_pack` for a left operand with MXFP8 elements (round to nearest)."""
+    """One-kernel version of :func:`quantize_pack` for a left operand with MXFP8 elements (round to nearest), or with
+    MXFP4 elements as packed nibbles (the left operand of the 4-bit x 4-bit GEMM)."""
     _lib.require_cuda(x, "quantize_pack_fused")
-    assert one_pass_ok(meta), "one-pass quantise + pack covers MXFP8 elements with round_mode 'rn' only"
+    nibbles = is_e2m1(meta) and supported(meta) and meta.round_mode == "rn"
+    assert one_pass_ok(meta) or nibbles, "one-pass quantise + pack covers MXFP8 and MXFP4 elements with round_mode 'rn' only"
     K = x.shape[-1]
     rows = x.numel() // K
     x2 = x.reshape(rows, K).contiguous()
     L = _lib.load()
-    codes = torch.empty((rows, K), dtype=torch.uint8, device=x.device)
+    codes = torch.empty((rows, K // 2 if nibbles else K), dtype=torch.uint8, device=x.device)
     sf = torch.empty((L.mxq_mx_sf_bytes(rows, K, OPERAND_A, 0),), dtype=torch.uint8, device=x.device)
     fmt = ctypes.c_int(0)
     with torch.cuda.device(x.device):
@@ -183,7 +185,7 @@ def pack_activation(x: Tensor, meta: MXFPMeta, nibbles: bool = False) -> PackedO
     The result can be fed to several layers that share the activation (q / k / v, gate / up)
     through ``MXFPLinearPTQ.forward_packed`` so that it is quantised once."""
     if nibbles:
-        return quantize_pack(x, meta, OPERAND_A, native=True)
+        return quantize_pack_fused(x, meta) if meta.round_mode == "rn" and x.dtype in _lib.DTYPE_ID else quantize_pack(x, meta, OPERAND_A, native=True)
     return quantize_pack_fused(x, meta) if one_pass_ok(meta) else quantize_pack(x, meta)
 
 
@@ -343,8 +345,9 @@ def mx_linear(x: Tensor, x_meta: MXFPMeta, w: PackedOperand, bias: Tensor | None
         x = x.float()
     x2 = x.reshape(-1, w.K).contiguous()
     M, dev = x2.shape[0], x2.device
-    if w.hw_format == 5 and is_e2m1(x_meta) and w.K % 256 == 0:
-        # MXFP4 x MXFP4 with the weight kept as packed nibbles: the activation is packed the same way (kind::mxf4)
+    if w.hw_format == 5 and is_e2m1(x_meta) and w.K % 256 == 0 and x_meta.round_mode != "rn":
+        # MXFP4 x MXFP4 with the weight kept as packed nibbles: the activation is packed the same way (kind::mxf4);
+        # round to nearest goes through the single C entry point below, which does the same
         y = mx_gemm(pack_activation(x2, x_meta, nibbles=True), w, x2.dtype, bias=bias, out=out)
         return y.reshape(*x.shape[:-1], w.rows)
     if x_meta.round_mode != "rn":

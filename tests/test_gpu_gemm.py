@@ -283,3 +283,23 @@ def test_fp4_by_fp4_on_the_4bit_tensor_core_kind(lib, M, N, K):
     yb = G.mx_gemm(a4, b4, torch.bfloat16, bias)
     G.check_status(DEV)
     assert within_tolerance(yb, y32 + bias.float())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("rows,K", [(512, 1024), (300, 256), (1, 512), (2050, 4096)])
+def test_one_pass_nibble_pack_equals_two_step(lib, dtype, rows, K):
+    """The one-kernel MXFP4 activation pack (packed nibbles + scale chunks) writes the bytes of extract followed by
+    the native pack."""
+    torch.manual_seed(rows + K)
+    for scale in (1.0, 300.0):
+        x = (torch.randn(rows, K, device=DEV) * scale).to(dtype)
+        x[0, :32] = 0
+        if rows > 2:
+            x[1, 5] = float("inf")
+            x[2, 40] = float("nan")
+        one = G.quantize_pack_fused(x, OCP_MXFP4_E2M1)
+        two = G.quantize_pack(x, OCP_MXFP4_E2M1, G.OPERAND_A, native=True)
+        assert one.hw_format == 5 and two.hw_format == 5
+        finite_rows = torch.isfinite(x.float()).reshape(rows, K // 32, 32).all(dim=2).repeat_interleave(16, dim=1)
+        assert torch.equal(one.codes[finite_rows], two.codes[finite_rows]), "codes differ"
+        assert torch.equal(one.sf, two.sf), "scale chunks differ"
