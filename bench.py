@@ -652,6 +652,10 @@ def small_cases():
             a, b = G.quantize_pack(x, MXFP8_E4M3_fn), G.quantize_pack(w, MXFP8_E4M3_fn, G.OPERAND_B)
             out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
             return (lambda: G.mx_gemm(a, b, torch.bfloat16, out=out)), flops
+        if which == "gemm4":           # MXFP4 x MXFP4, both operands packed nibbles: the kind::mxf4 form of the kernel
+            a, b = G.quantize_pack(x, OCP_MXFP4_E2M1, G.OPERAND_A, native=True), G.quantize_pack(w, OCP_MXFP4_E2M1, G.OPERAND_B, native=True)
+            out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+            return (lambda: G.mx_gemm(a, b, torch.bfloat16, out=out)), flops
         if which == "gather_local":     # the gather-fused kernel with two destinations on this GPU (no NVLink involved)
             a, b = G.quantize_pack(x, MXFP8_E4M3_fn), G.quantize_pack(w, MXFP8_E4M3_fn, G.OPERAND_B)
             outs = [torch.empty((M, N), dtype=torch.bfloat16, device=dev) for _ in range(2)]
@@ -713,7 +717,7 @@ def small_cases():
             cases[f"mxfp8_{which}_dim0_{route}_f32"] = (lambda w=which, r=route: strided_case(synthetic.cfg1_mxfp8_fp32, MXFP8_E4M3_fn, 4, w, r))
             cases[f"mxfp4_{which}_dim0_{route}_bf16"] = (lambda w=which, r=route: strided_case(synthetic.cfg3_mxfp4_bf16, OCP_MXFP4_E2M1, 2, w, r))
     cases["mx_gemm_gather_local_cfg4"] = (lambda: gemm_case(8192, 14336, 4096, "gather_local"))
-    for which in ("gemm", "linear", "separate", "xwq", "xwq_loader", "dense"):
+    for which in ("gemm", "gemm4", "linear", "separate", "xwq", "xwq_loader", "dense"):
         cases[f"mx_{which}_small"] = (lambda w=which: gemm_case(2048, 4096, 4096, w))
         cases[f"mx_{which}_cfg4"] = (lambda w=which: gemm_case(8192, 14336, 4096, w))
     for which in ("extract", "compose", "qdq"):

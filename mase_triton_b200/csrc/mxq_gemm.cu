@@ -8,7 +8,13 @@
 //     bulk copy and moved shared -> tensor memory with tcgen05.cp;
 //   * one elected thread issues tcgen05.mma.kind::mxf8f6f4.block_scale (M=128, N=bn, K=32); the
 //     fp32 accumulators (one or two 128-lane x bn-column blocks) live in tensor memory;
-//   * four epilogue warps read them back with tcgen05.ld, add the bias, convert and store.
+//   * epilogue warps read them back with tcgen05.ld, add the bias and convert; eight of them stage 32 x 32 chunks in
+//     shared memory and store with TMA (asynchronous: tensor memory goes back to the MMA warp before the stores land),
+//     or four store from registers when the output cannot be described by a tensor map.
+// Variants of the same kernel (template flags): the right operand as dense 6- / 4-bit codes that the copy engine
+// spreads to bytes in shared memory; both operands as packed E2M1 nibbles on tcgen05.mma.kind::mxf4 (K = 64 per
+// instruction, twice the arithmetic per byte staged); the all-gather of a column-parallel linear done by an extra
+// warp that forwards every finished half tile to the peers with TMA.
 // The CTA tile is 256 x bn (128 x bn when M <= 128) with bn = 224 by default: two accumulators fill
 // the 512 TMEM columns and raise the flops per byte pulled from L2, which is what bounds this kernel.
 // bn is a run-time value (a multiple of 16, at most 224) fixed when the right operand is packed, so a
@@ -16,7 +22,7 @@
 // persistent (one per SM, tiles dealt round-robin in an L2-friendly order): the TMA producer runs
 // ahead into the next tile while the epilogue drains tensor memory.
 // Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer (also owns the TMEM allocation),
-// warps 2..5 = epilogue.  Every wait on an mbarrier is bounded; a wait that runs out records a
+// warps 2.. = epilogue (then the forwarding / copy-out warps of the gather-fused forms).  Every wait on an mbarrier is bounded; a wait that runs out records a
 // code in the caller's status word and the CTA unwinds (TMEM is freed) instead of spinning.
 //
 // Operand layout in HBM (produced by the pack kernel in this file):
