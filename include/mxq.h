@@ -238,7 +238,7 @@ int mxq_unpack_codes(const uint8_t* packed, uint8_t* codes, int64_t n, int bits,
  * ---- Tensor-core GEMMs for the layer types whose operands are not both block-quantised ----
  * out[M,N] = x[M,K] * W[N,K]^T (+ bias[N]); x, out and bias are bf16 or fp16 (`dtype`: MXQ_BF16 /
  * MXQ_F16; MXQ_F32 returns MXQ_ESIZE), fp32 accumulation in tensor memory (tcgen05.mma.kind::f16,
- * 256 x 256 tiles, x by TMA).  `status` as for mxq_mx_gemm (code 5: a dequantiser wait ran out).
+ * 256 x 256 tiles - 256 x 128 or 256 x 64 for dense operands when that occupies more SMs -, x by TMA).  `status` as for mxq_mx_gemm (code 5: a dequantiser wait ran out).
  * They replace "compose the weight to a dense tensor, then torch.nn.functional.linear" in
  * mxfp_linear_XWq / _XqW / _XW (src/mase_triton/mxfp/functional/linear.py:10-33,67-116),
  * minifloat_linear_XWq / _XqW / _XW (src/mase_triton/minifloat/functional/linear.py:10-105) and the

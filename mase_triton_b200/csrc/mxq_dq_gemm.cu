@@ -190,7 +190,7 @@ template <> struct Staged<SRC_RAW> {};
 template <int DT, int MH, int SRC>
 __global__ void __launch_bounds__(THREADS, 1)
 dq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const WSource wsrc,
-               void* __restrict__ out, const void* __restrict__ bias, int M, int N, int K, uint32_t idesc, int* status,
+               void* __restrict__ out, const void* __restrict__ bias, int M, int N, int K, int bn, uint32_t idesc, int* status,
                const __grid_constant__ OutMaps omaps, int tma_out) {
     using C = Cfg<MH>;
     constexpr int STAGES = C::STAGES;
@@ -209,7 +209,8 @@ dq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KT = (K + BK - 1) / BK;
-    const int MT = (M + C::BM - 1) / C::BM, NT = (N + BN - 1) / BN;
+    // bn: columns of the CTA tile (64, 128 or 256; always 256 when the weight is expanded by the dequantiser warps)
+    const int MT = (M + C::BM - 1) / C::BM, NT = (N + bn - 1) / bn;
     const int num_tiles = MT * NT;
 
     if (threadIdx.x == 0) {
@@ -235,7 +236,7 @@ dq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ---------------- TMA producer ----------------
         bool ok = true;
         uint32_t it = 0;
-        constexpr uint32_t tx_bytes = C::A_BYTES + (SRC == SRC_RAW ? B_BYTES : 0);
+        const uint32_t tx_bytes = C::A_BYTES + (SRC == SRC_RAW ? (uint32_t)(bn * BK * 2) : 0u);
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             int mt, nt;
             tile_coords(tile, MT, NT, mt, nt);
@@ -247,7 +248,7 @@ dq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const uint32_t st = ring + s * C::STAGE_BYTES;
                     mbar_expect_tx(full_bar(s), tx_bytes);
                     tma_load_2d(st, &map_a, kt * BK, mt * C::BM, full_bar(s));
-                    if constexpr (SRC == SRC_RAW) tma_load_2d(st + C::A_BYTES, &map_b, kt * BK, nt * BN, full_bar(s));
+                    if constexpr (SRC == SRC_RAW) tma_load_2d(st + C::A_BYTES, &map_b, kt * BK, nt * bn, full_bar(s));
                 }
                 __syncwarp();
             }
@@ -306,22 +307,22 @@ dq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int h = 0; h < MH; ++h) {
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + h * BN;
                 if (tma_out) {
-                    drain_accumulator_tma<DT>(taddr, BN / 32, false, 0, 1, bias, nt * BN, mt * C::BM + h * 128 + q * 32, M, N, slots, turn, omaps,
+                    drain_accumulator_tma<DT>(taddr, bn / 32, false, 0, 1, bias, nt * bn, mt * C::BM + h * 128 + q * 32, M, N, slots, turn, omaps,
                                               tmem_empty_bar(h), lane);
                     continue;
                 }
                 const int row = mt * C::BM + h * 128 + q * 32 + lane;
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
+                for (int c = 0; c < bn / 32; ++c) {
                     uint32_t r[32];
                     tmem_ld_32x32b_x32(taddr + c * 32, r);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (c == BN / 32 - 1) {
+                    if (c == bn / 32 - 1) {
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(tmem_empty_bar(h));
                     }
-                    store_chunk<DT, 32>(out, bias, r, row, nt * BN + c * 32, M, N, N, 0);
+                    store_chunk<DT, 32>(out, bias, r, row, nt * bn + c * 32, M, N, N, 0);
                 }
             }
         }
@@ -460,18 +461,33 @@ static int launch(const void* x, const void* w_raw, const WSource& wsrc, void* o
     static bool attr_done[MAX_DEVICES] = {false};
     const cudaError_t e = raise_smem_limit(dq_gemm_kernel<DT, MH, SRC>, C::SMEM_BYTES, attr_done);
     if (e != cudaSuccess) { set_last_cuda_error(e); return MXQ_ELAUNCH; }
+    // Dense operands: the tile width that finishes first by a simple model -- waves of tiles over the SMs times the
+    // longer of a stage's MMAs (4 bn cycles for two 128-row halves, 2 bn for one) and its loads at the 69 bytes per clock
+    // an SM takes in, plus the epilogue.  256 columns whenever the problem has tiles enough; narrower tiles put more SMs
+    // to work on small problems (M = 256, N = 4096: 64 tiles of 64 columns instead of 16 of 256).
+    int bn = BN;
+    if (SRC == SRC_RAW) {
+        const int mt = (M + C::BM - 1) / C::BM, kt = (K + BK - 1) / BK, sms = sm_count();
+        double best = 1e300;
+        for (int cand = BN; cand >= 64; cand >>= 1) {
+            const int tiles = mt * ((N + cand - 1) / cand);
+            const double mma = 2.0 * MH * cand, load = (C::A_BYTES + cand * BK * 2) / 69.0;
+            const double cost = (double)((tiles + sms - 1) / sms) * (kt * (mma > load ? mma : load) + 24.0 * cand);
+            if (cost < 0.97 * best) { best = cost; bn = cand; }          // a narrower tile has to win by 3 %
+        }
+    }
     CUtensorMap ma, mb;
     if (!make_map_16bit(&ma, x, M, K, C::BM, DT)) return MXQ_ELAUNCH;
     // a quantised W is read with plain loads; the kernel still takes a map argument, so give it a valid one
-    if (!make_map_16bit(&mb, SRC == SRC_RAW ? w_raw : x, SRC == SRC_RAW ? N : M, K, SRC == SRC_RAW ? BN : C::BM, DT)) return MXQ_ELAUNCH;
+    if (!make_map_16bit(&mb, SRC == SRC_RAW ? w_raw : x, SRC == SRC_RAW ? N : M, K, SRC == SRC_RAW ? bn : C::BM, DT)) return MXQ_ELAUNCH;
     // instruction descriptor of kind::f16: fp32 accumulate, A/B format (0 fp16, 1 bf16), K-major operands, N >> 3, M >> 4
     const uint32_t fmt = DT == MXQ_BF16 ? 1u : 0u;
-    const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-    const int tiles = ((M + C::BM - 1) / C::BM) * ((N + BN - 1) / BN);
+    const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    const int tiles = ((M + C::BM - 1) / C::BM) * ((N + bn - 1) / bn);
     const int grid = tiles < sm_count() ? tiles : sm_count();
     OutMaps omaps{};
     const int tma_out = make_out_maps(&omaps, out, M, N, N, DT) ? 1 : 0;     // else: stores from registers
-    dq_gemm_kernel<DT, MH, SRC><<<grid, THREADS, C::SMEM_BYTES, st>>>(ma, mb, wsrc, out, bias, M, N, K, idesc, status, omaps, tma_out);
+    dq_gemm_kernel<DT, MH, SRC><<<grid, THREADS, C::SMEM_BYTES, st>>>(ma, mb, wsrc, out, bias, M, N, K, bn, idesc, status, omaps, tma_out);
     return check_launch();
 }
 
