@@ -5,7 +5,8 @@ dense linear.  ``layer_type`` names what is quantised (``Xq``/``X``, ``Wq``/``W`
 ``"separate"`` mirrors the reference's op sequence (dequantise, then a library linear).  ``"fused"`` (a stub
 in the reference) runs this library's tensor-core GEMMs: with both operands quantised to E4M3, E5M2 or one
 of the narrower OCP formats and ``in_features`` a multiple of 32, activation and weight stay 8-bit codes
-(the block-scaled GEMM with every block scale at 2^0); every other layer type on bf16 / fp16 activations
+(the block-scaled GEMM with every block scale at 2^0; FP4 x FP4 with ``in_features`` a multiple of 256 stays packed
+nibbles on the 4-bit tensor-core kind); every other layer type on bf16 / fp16 activations
 takes the ``kind::f16`` GEMM that expands weight codes in its operand loader; what neither takes raises
 ``NotImplementedError``.
 """
@@ -40,15 +41,21 @@ def _tensor_core_ok(x: Tensor, x_meta, w_element, w_tensor_meta) -> bool:
             and x.dtype in (torch.bfloat16, torch.float16, torch.float32))
 
 
-def _packed_weight(w_element: Tensor, w_tensor_meta: MinifloatTensorMeta):
+def _fp4_pair(x_meta: MinifloatMeta, w_meta: MinifloatMeta, k: int) -> bool:
+    """FP4 (E2M1) activation and weight with whole 256-element stages: both stay packed nibbles and the GEMM runs on
+    the 4-bit x 4-bit tensor-core kind (every block scale 2^0), at twice the rate of the 8-bit kinds."""
+    return (x_meta.exp_bits, x_meta.frac_bits) == (2, 1) and (w_meta.exp_bits, w_meta.frac_bits) == (2, 1) and k % 256 == 0
+
+
+def _packed_weight(w_element: Tensor, w_tensor_meta: MinifloatTensorMeta, nibbles: bool = False):
     """Tensor-core form of the weight codes, kept on the code tensor itself and rebuilt when it changes."""
     from ...mxfp import gemm as _gemm
-    tag = (w_element._version, tuple(w_tensor_meta.shape), w_tensor_meta.meta)
+    tag = (w_element._version, tuple(w_tensor_meta.shape), w_tensor_meta.meta, nibbles)
     cached = getattr(w_element, "_mxq_packed", None)
     if cached is None or cached[0] != tag:
         n, k = w_tensor_meta.shape
         cached = (tag, _gemm.pack_codes(None, w_element.reshape(n, k).to(torch.uint8), n, k, w_tensor_meta.meta.exp_bits,
-                                        w_tensor_meta.meta.frac_bits, _gemm.OPERAND_B))
+                                        w_tensor_meta.meta.frac_bits, _gemm.OPERAND_B, native=nibbles))
         w_element._mxq_packed = cached
     return cached[1]
 
@@ -57,11 +64,12 @@ def _fused_linear(x: Tensor, x_meta: MinifloatMeta, w_element: Tensor, w_tensor_
     from ...mxfp import gemm as _gemm
     k = x.shape[-1]
     x2 = x.reshape(-1, k)
-    a = _gemm.minifloat_quantize_pack(x2, x_meta.exp_bits, x_meta.frac_bits, x_meta.round_mode)    # FP8: one kernel
+    nibbles = _fp4_pair(x_meta, w_tensor_meta.meta, k)
+    a = None if nibbles else _gemm.minifloat_quantize_pack(x2, x_meta.exp_bits, x_meta.frac_bits, x_meta.round_mode)    # FP8: one kernel
     if a is None:
         codes = kernels.extract_minifloat_component(x2, x_meta).to(torch.uint8)      # the sign sits below bit 8
-        a = _gemm.pack_codes(None, codes, x2.shape[0], k, x_meta.exp_bits, x_meta.frac_bits, _gemm.OPERAND_A)
-    out = _gemm.mx_gemm(a, _packed_weight(w_element, w_tensor_meta), x.dtype, bias=bias)
+        a = _gemm.pack_codes(None, codes, x2.shape[0], k, x_meta.exp_bits, x_meta.frac_bits, _gemm.OPERAND_A, native=nibbles)
+    out = _gemm.mx_gemm(a, _packed_weight(w_element, w_tensor_meta, nibbles), x.dtype, bias=bias)
     return out.reshape(*x.shape[:-1], out.shape[-1])
 
 

@@ -231,3 +231,31 @@ def test_mxfp4_layer_runs_on_packed_nibbles(lib, dtype):
         shared = layer.forward_packed(layer.pack_input(x), dtype, lead_shape=(3, 100))
         G.check_status(DEV)
         assert torch.equal(y_fn, y) and torch.equal(shared, y)
+
+
+def test_minifloat_fp4_layer_runs_on_packed_nibbles(lib):
+    """A per-tensor FP4 x FP4 fused layer takes the 4-bit tensor-core kind (unit block scales) when in_features is a
+    multiple of 256 and gives the bytes of the widened 8-bit form it takes otherwise."""
+    from mase_triton_b200.minifloat.functional import linear as ML
+
+    torch.manual_seed(43)
+    fc = torch.nn.Linear(512, 600, bias=True, device=DEV, dtype=torch.bfloat16)
+    with torch.no_grad():
+        fc.weight.mul_(20.0)                              # spread the weights over the FP4 range
+    layer = MinifloatLinearPTQ.from_linear(fc, FP4_E2M1_fn, FP4_E2M1_fn, None, "XqWqB", backend="fused")
+    x = (torch.randn(200, 512, device=DEV) * 2).to(torch.bfloat16)
+    y = layer(x)
+    G.check_status(DEV)
+    packed = ML._packed_weight(layer.w_element, layer.w_tensor_meta, True)
+    assert packed.hw_format == 5 and packed.codes.numel() == 600 * 512 // 2
+    x_dq = MF.quantize_dequantize(x, FP4_E2M1_fn, torch.float32).cpu()
+    w_dq = MF.quantize_dequantize(fc.weight.detach(), FP4_E2M1_fn, torch.float32).cpu()
+    y32 = torch.nn.functional.linear(x_dq, w_dq, fc.bias.detach().float().cpu())
+    tol = 2.0**-7 * y32.abs() + 2.0**-7 * y32.pow(2).mean().sqrt()
+    assert bool(((y.float().cpu() - y32).abs() <= tol).all())
+    # the same layer computed with the codes widened to bytes
+    codes = layer.w_element.reshape(600, 512).to(torch.uint8)
+    wide_w = G.pack_codes(None, codes, 600, 512, 2, 1, G.OPERAND_B)
+    from mase_triton_b200.minifloat import kernels as mfk
+    a_wide = G.pack_codes(None, mfk.extract_minifloat_component(x, FP4_E2M1_fn).to(torch.uint8), 200, 512, 2, 1, G.OPERAND_A)
+    assert torch.equal(G.mx_gemm(a_wide, wide_w, torch.bfloat16, bias=layer.bias), y)
