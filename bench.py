@@ -249,6 +249,44 @@ def graph_time(fn, reps: int, rounds: int = 5) -> float:
         return statistics.median(time_steps(fn, reps))
 
 
+def graph_time_interleaved(fns: dict, reps: int, rounds: int = 7) -> dict:
+    """`graph_time` for several callables at once: one CUDA graph of `reps` calls each, replayed in turn for `rounds`
+    rounds, median per callable.  What ran just before (clocks under the power cap, what is left in L2) then weighs on
+    all of them alike instead of on whichever is measured last."""
+    graphs = {}
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for fn in fns.values():
+            for _ in range(3):
+                fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    try:
+        for name, fn in fns.items():
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for _ in range(reps):
+                    fn()
+            g.replay()
+            graphs[name] = g
+        torch.cuda.synchronize()
+        ts = {name: [] for name in fns}
+        for _ in range(rounds):
+            for name, g in graphs.items():
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                g.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                ts[name].append(e0.elapsed_time(e1) / reps)
+        return {name: statistics.median(v) for name, v in ts.items()}
+    except Exception as exc:      # noqa: BLE001
+        GRAPH_FALLBACKS.append(f"{type(exc).__name__}: {exc}"[:200])
+        torch.cuda.synchronize()
+        return {name: statistics.median(time_steps(fn, reps)) for name, fn in fns.items()}
+
+
 def extras_single_gpu(dev, steps: int, warmup: int, peak: float) -> dict:
     """MXFP extract / compose on configurations 1 and 3, and the MX GEMM / linear on configurations
     4 and 5 (device-resident; CUDA-graph replays so that host launch gaps are not part of the time)."""
@@ -315,12 +353,12 @@ def extras_single_gpu(dev, steps: int, warmup: int, peak: float) -> dict:
         fc.weight.copy_(wc)
     fused = MXFPLinearPTQ.from_linear(fc, MXFP8_E4M3_fn, MXFP8_E4M3_fn, None, "XqWqB", "fused")
     sep = MXFPLinearPTQ.from_linear(fc, MXFP8_E4M3_fn, MXFP8_E4M3_fn, None, "XqWqB", "separate")
-    t_fused = graph_time(lambda: fused(xc), reps)
-    t_sep = graph_time(lambda: sep(xc), max(3, reps // 2))
-    # the kernel once more after the layers: its time moves by a few per cent with what ran just before; report the better
-    # of the two medians and keep both
+    # the kernel, the fused layer and the separate layer once more in turn (graphs replayed round-robin): a time moves by
+    # several per cent with what ran just before it.  The kernel keeps the better of its two medians; both are reported.
     t_gemm_first = t_gemm
-    t_gemm_again = graph_time(lambda: G.mx_gemm(a, b, torch.bfloat16, out=o), max(reps, 20), rounds=9)
+    turn = graph_time_interleaved({"gemm": lambda: G.mx_gemm(a, b, torch.bfloat16, out=o), "fused": lambda: fused(xc),
+                                   "separate": lambda: sep(xc)}, max(5, reps // 2))
+    t_gemm_again, t_fused, t_sep = turn["gemm"], turn["fused"], turn["separate"]
     t_gemm = min(t_gemm_first, t_gemm_again)
     G.check_status(dev)
     rel = ((fused(xc).float() - sep(xc).float()).abs().mean() / sep(xc).float().abs().mean()).item()

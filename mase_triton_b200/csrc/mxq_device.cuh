@@ -64,6 +64,14 @@ __device__ __forceinline__ void store_pack(void* p, const Pack<BYTES>& r) {
     else if constexpr (BYTES == 8) __stcs(reinterpret_cast<uint2*>(p), make_uint2(r.w[0], r.w[1]));
     else __stcs(reinterpret_cast<unsigned int*>(p), r.w[0]);
 }
+// the same with the default cache policy: for data the next kernel reads right away (a GEMM operand), which should
+// stay in L2 instead of being marked for early eviction
+template <int BYTES>
+__device__ __forceinline__ void store_pack_keep(void* p, const Pack<BYTES>& r) {
+    if constexpr (BYTES == 16) *reinterpret_cast<uint4*>(p) = make_uint4(r.w[0], r.w[1], r.w[2], r.w[3]);
+    else if constexpr (BYTES == 8) *reinterpret_cast<uint2*>(p) = make_uint2(r.w[0], r.w[1]);
+    else *reinterpret_cast<unsigned int*>(p) = r.w[0];
+}
 // raw element i of a pack whose elements are ESZ bytes wide
 template <int ESZ, int BYTES>
 __device__ __forceinline__ uint32_t pack_get(const Pack<BYTES>& p, int i) {

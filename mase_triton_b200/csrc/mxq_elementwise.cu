@@ -919,7 +919,7 @@ __global__ void __launch_bounds__(kThreads) minifloat_hwpack_kernel(const void* 
         if (bad) mag = (mag >= (2u << f.fb())) ? mag - (1u << f.fb()) : (mag + ((mag >> 1) & 1u)) >> 1;
         pack_set<1>(out, i, mag | (code[i] & 0x80u));
     }
-    store_pack<V>(hw_codes + idx * V, out);
+    store_pack_keep<V>(hw_codes + idx * V, out);
     if ((lane & (G - 1)) == 0) hw_sf[sf_chunk_offset((uint32_t)(idx / G), geom)] = (uint8_t)(bad ? 128u : 127u);
 }
 
@@ -1043,7 +1043,7 @@ __global__ void __launch_bounds__(kThreads) mx_quant_pack_flat_kernel(const void
                 for (int i = 0; i < V / 4; ++i) o.w[i] = halve_codes4<F{}.fb()>(o.w[i]);
                 if (sbyte < 255u) sbyte += 1u;
             }
-            if (vec < n_vec) store_pack<V>(hw_codes + vec * V, o);
+            if (vec < n_vec) store_pack_keep<V>(hw_codes + vec * V, o);
         } else {
             // four code bytes -> two bytes of nibbles (element 2i in the low nibble of byte i)
             uint32_t nib = 0u;
