@@ -222,6 +222,18 @@ int mxq_mx_gemm(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw_format, co
                 const void* bias, int64_t M, int64_t N, int64_t K, int* status, void* stream);
 
 /*
+ * mxq_mx_gemm with an MXFP-quantised bias (layer types *Bq, src/mase_triton/mxfp/functional/linear.py:52-57):
+ * bias_elements [N] code bytes and bias_scales [N / 32] E8M0 bytes, as mxq_mxfp_extract writes them for the bias
+ * vector (32-element blocks, is_finite element format with exp_bits + frac_bits <= 7).  The epilogue decodes the
+ * code of every output column - the value and the rounding to out_dtype of mxq_mxfp_compose - and adds it:
+ * no separate dequantisation launch, no dense bias in memory.  N % 32 == 0.
+ */
+int mxq_mx_gemm_qbias(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw_format, const uint8_t* b_codes,
+                      const uint8_t* b_sf, int b_hw_format, int b_tile_rows, void* out, int out_dtype,
+                      const uint8_t* bias_scales, const uint8_t* bias_elements, int bias_exp_bits,
+                      int bias_frac_bits, int64_t M, int64_t N, int64_t K, int* status, void* stream);
+
+/*
  * ---- Dense storage of element codes ----
  * The reference keeps one MXFP element code per byte (`elements`, src/mase_triton/mxfp/fake.py:57-59;
  * the Parameter `w_elements` of MXFPLinearPTQ, src/mase_triton/mxfp/layers.py:66-80) although a code

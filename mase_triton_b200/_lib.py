@@ -34,6 +34,7 @@ SIGNATURES = {
     "mxq_mx_quantize_pack": [_p, _i, _i64, _i64, _i, _i, _p, _p, _p, _p],
     "mxq_minifloat_quantize_pack": [_p, _i, _i64, _i64, _i, _i, _i, _p, _p, _p, _p],
     "mxq_mx_gemm": [_p, _p, _i, _p, _p, _i, _i, _p, _i, _p, _i64, _i64, _i64, _p, _p],
+    "mxq_mx_gemm_qbias": [_p, _p, _i, _p, _p, _i, _i, _p, _i, _p, _p, _i, _i, _i64, _i64, _i64, _p, _p],
     "mxq_mx_gemm_gather": [_p, _p, _i, _p, _p, _i, _i, _p, _i, _i, _i64, _i64, _i, _p, _i64, _i64, _i64, _p, _p],
     "mxq_mx_linear": [_p, _i, _i64, _i64, _i, _i, _p, _p, _i, _i, _i64, _p, _i, _p, _p, _i64, _p, _p],
     "mxq_mx_linear_static": [_p, _i, _i64, _i64, _i, _i, _p, _p, _i, _i, _i64, _p, _i, _p, _p, _p],

@@ -190,7 +190,7 @@ template <> struct Staged<SRC_RAW> {};
 template <int DT, int MH, int SRC>
 __global__ void __launch_bounds__(THREADS, 1)
 dq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const WSource wsrc,
-               void* __restrict__ out, const void* __restrict__ bias, int M, int N, int K, int bn, uint32_t idesc, int* status,
+               void* __restrict__ out, const BiasRef bias, int M, int N, int K, int bn, uint32_t idesc, int* status,
                const __grid_constant__ OutMaps omaps, int tma_out) {
     using C = Cfg<MH>;
     constexpr int STAGES = C::STAGES;

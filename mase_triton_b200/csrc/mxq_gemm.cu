@@ -147,7 +147,7 @@ template <int OUT_DT, int MH, int EPI, bool MXF4 = false>
 __global__ void __launch_bounds__(kernel_threads<EPI>(), 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, void* __restrict__ out,
-               const void* __restrict__ bias, int M, int N, int K, int bn, uint32_t idesc_base, int* status,
+               const BiasRef bias, int M, int N, int K, int bn, uint32_t idesc_base, int* status,
                const __grid_constant__ OutSpec outs, const __grid_constant__ OutMaps omaps, const __grid_constant__ FwdMaps fmaps) {
     using C = Cfg<MH, MXF4>;
     constexpr int STAGES = C::STAGES;
@@ -607,7 +607,7 @@ static bool make_operand_map(CUtensorMap* map, const void* codes, int64_t rows, 
 // outs == nullptr: plain epilogue into `out`; otherwise the gather-fused epilogue into outs->ptr[]
 template <int OUT_DT, int MH, int EPI, bool MXF4 = false>
 static int launch_gemm(const uint8_t* a_codes, const uint8_t* b_codes, const uint8_t* sfa, const uint8_t* sfb, void* out,
-                       const void* bias, int M, int N, int K, int bn, uint32_t idesc, int* status, cudaStream_t st, const OutSpec* outs,
+                       const BiasRef& bias, int M, int N, int K, int bn, uint32_t idesc, int* status, cudaStream_t st, const OutSpec* outs,
                        const OutMaps& omaps, const FwdMaps& fmaps) {
     using C = Cfg<MH, MXF4>;
     constexpr int SMEM = kernel_smem<EPI, MH, MXF4>();
@@ -632,7 +632,7 @@ static int launch_gemm(const uint8_t* a_codes, const uint8_t* b_codes, const uin
 // output the asynchronous epilogue can describe.
 template <int OUT_DT>
 static int launch_gemm_mxf4(const uint8_t* a_codes, const uint8_t* b_codes, const uint8_t* sfa, const uint8_t* sfb, void* out,
-                            const void* bias, int M, int N, int K, int bn, int* status, cudaStream_t st) {
+                            const BiasRef& bias, int M, int N, int K, int bn, int* status, cudaStream_t st) {
     OutMaps omaps{};
     FwdMaps fmaps{};
     if (!make_out_maps(&omaps, out, M, N, N, OUT_DT)) return MXQ_ESIZE;
@@ -664,7 +664,7 @@ static bool make_gather_maps(const OutSpec& outs, int M, int N, int bn, int dt, 
 
 template <int OUT_DT>
 static int launch_gemm_dt(const uint8_t* a_codes, const uint8_t* b_codes, const uint8_t* sfa, const uint8_t* sfb, void* out,
-                          const void* bias, int M, int N, int K, int bn, uint32_t idesc, int* status, cudaStream_t st,
+                          const BiasRef& bias, int M, int N, int K, int bn, uint32_t idesc, int* status, cudaStream_t st,
                           const OutSpec* outs = nullptr) {
     OutMaps omaps{};
     FwdMaps fmaps{};
@@ -774,9 +774,9 @@ extern "C" int mxq_mx_pack_operand_native(const uint8_t* scales, const uint8_t* 
     return rc;
 }
 
-extern "C" int mxq_mx_gemm(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw_format, const uint8_t* b_codes,
-                           const uint8_t* b_sf, int b_hw_format, int b_tile_rows, void* out, int out_dtype, const void* bias,
-                           int64_t M, int64_t N, int64_t K, int* status, void* stream) {
+static int mx_gemm_impl(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw_format, const uint8_t* b_codes, const uint8_t* b_sf,
+                        int b_hw_format, int b_tile_rows, void* out, int out_dtype, const tc::BiasRef& bias, int64_t M, int64_t N, int64_t K,
+                        int* status, void* stream) {
     if (M <= 0 || N <= 0 || K <= 0 || K % 32 != 0 || M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return MXQ_EINVAL;
     if (!a_codes || !a_sf || !b_codes || !b_sf || !out) return MXQ_EINVAL;
     if (a_hw_format == gemm::HW_E2M1 && b_hw_format == gemm::HW_E2M1) {
@@ -803,6 +803,22 @@ extern "C" int mxq_mx_gemm(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw
     if (out_dtype == MXQ_BF16) return gemm::launch_gemm_dt<MXQ_BF16>(a_codes, b_codes, a_sf, b_sf, out, bias, (int)M, (int)N, (int)K, bn, idesc, status, st);
     if (out_dtype == MXQ_F16) return gemm::launch_gemm_dt<MXQ_F16>(a_codes, b_codes, a_sf, b_sf, out, bias, (int)M, (int)N, (int)K, bn, idesc, status, st);
     return MXQ_EINVAL;
+}
+
+extern "C" int mxq_mx_gemm(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw_format, const uint8_t* b_codes,
+                           const uint8_t* b_sf, int b_hw_format, int b_tile_rows, void* out, int out_dtype, const void* bias,
+                           int64_t M, int64_t N, int64_t K, int* status, void* stream) {
+    return mx_gemm_impl(a_codes, a_sf, a_hw_format, b_codes, b_sf, b_hw_format, b_tile_rows, out, out_dtype, tc::BiasRef(bias), M, N, K, status, stream);
+}
+
+extern "C" int mxq_mx_gemm_qbias(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw_format, const uint8_t* b_codes,
+                                 const uint8_t* b_sf, int b_hw_format, int b_tile_rows, void* out, int out_dtype,
+                                 const uint8_t* bias_scales, const uint8_t* bias_elements, int bias_exp_bits, int bias_frac_bits,
+                                 int64_t M, int64_t N, int64_t K, int* status, void* stream) {
+    if (!bias_scales || !bias_elements || N % 32 != 0) return MXQ_EINVAL;
+    if (bias_exp_bits < 1 || bias_frac_bits < 1 || bias_exp_bits + bias_frac_bits > 7) return MXQ_EINVAL;
+    return mx_gemm_impl(a_codes, a_sf, a_hw_format, b_codes, b_sf, b_hw_format, b_tile_rows, out, out_dtype,
+                        tc::BiasRef(bias_elements, bias_scales, bias_exp_bits, bias_frac_bits), M, N, K, status, stream);
 }
 
 extern "C" int mxq_mx_gemm_gather(const uint8_t* a_codes, const uint8_t* a_sf, int a_hw_format, const uint8_t* b_codes,

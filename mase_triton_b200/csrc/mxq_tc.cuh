@@ -11,6 +11,7 @@
 #include <mutex>
 
 #include "../../include/mxq.h"
+#include "mxq_codec.h"
 #include "mxq_internal.h"
 
 namespace mxq {
@@ -136,24 +137,45 @@ __device__ __forceinline__ void tile_coords(int t, int MT, int NT, int& mt, int&
 }
 
 // `out` is a row-major matrix with leading dimension ld; the tile's columns start at column `shift` of it.
+// The bias an epilogue adds: N values of the output dtype, or -- `scales` set -- an MXFP-quantised bias as the reference
+// stores it (N element-code bytes + one E8M0 scale per 32, src/mase_triton/mxfp/layers.py:85-95), decoded per column
+// with the arithmetic and the rounding of compose_mxfp_tensor to the output dtype (src/mase_triton/mxfp/fake.py:62-79).
+struct BiasRef {
+    const void* ptr;
+    const uint8_t* scales;
+    int eb, fb;
+    __host__ __device__ BiasRef(const void* p = nullptr) : ptr(p), scales(nullptr), eb(0), fb(0) {}
+    __host__ __device__ BiasRef(const uint8_t* codes, const uint8_t* s, int e, int f) : ptr(codes), scales(s), eb(e), fb(f) {}
+};
+
+template <int OUT_DT>
+__device__ __forceinline__ float bias_at(const BiasRef& bias, int col) {
+    if (bias.scales != nullptr) {
+        const uint32_t code = reinterpret_cast<const uint8_t*>(bias.ptr)[col];
+        const uint32_t sb = bias.scales[col >> 5];
+        const float v = __uint_as_float(mx_decode(code, __uint_as_float(sb == 0u ? 0x00400000u : (sb << 23)), FmtRT{bias.eb, bias.fb, 1, 0}));
+        if constexpr (OUT_DT == MXQ_F32) return v;
+        else if constexpr (OUT_DT == MXQ_BF16) return __bfloat162float(__float2bfloat16_rn(v));
+        else return __half2float(__float2half_rn(v));
+    }
+    if constexpr (OUT_DT == MXQ_F32) return reinterpret_cast<const float*>(bias.ptr)[col];
+    else if constexpr (OUT_DT == MXQ_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias.ptr)[col]);
+    else return __half2float(reinterpret_cast<const __half*>(bias.ptr)[col]);
+}
+
 // W = 32 or 16: columns held in r[0..W)
 template <int OUT_DT, int W>
-__device__ __forceinline__ void store_chunk(void* __restrict__ out, const void* __restrict__ bias, const uint32_t (&r)[32],
+__device__ __forceinline__ void store_chunk(void* __restrict__ out, const BiasRef& bias, const uint32_t (&r)[32],
                                             int row, int col0, int M, int N, int64_t ld, int64_t shift) {
     if (row >= M || col0 >= N) return;
     float v[W];
 #pragma unroll
     for (int i = 0; i < W; ++i) v[i] = __uint_as_float(r[i]);
     const bool whole = (col0 + W <= N);
-    if (bias != nullptr) {
+    if (bias.ptr != nullptr) {
 #pragma unroll
-        for (int i = 0; i < W; ++i) {
-            if (whole || col0 + i < N) {
-                if constexpr (OUT_DT == MXQ_F32) v[i] += reinterpret_cast<const float*>(bias)[col0 + i];
-                else if constexpr (OUT_DT == MXQ_BF16) v[i] += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[col0 + i]);
-                else v[i] += __half2float(reinterpret_cast<const __half*>(bias)[col0 + i]);
-            }
-        }
+        for (int i = 0; i < W; ++i)
+            if (whole || col0 + i < N) v[i] += bias_at<OUT_DT>(bias, col0 + i);
     }
     if constexpr (OUT_DT == MXQ_F32) {
         float* o = reinterpret_cast<float*>(out) + (size_t)row * ld + shift + col0;
@@ -202,21 +224,15 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 // 16 columns x 32 rows, unswizzled (16-bit outputs whose tile width is an odd multiple of 16)
 struct OutMaps { CUtensorMap main, tail; };
 
-template <int OUT_DT>
-__device__ __forceinline__ float bias_at(const void* bias, int col) {
-    if constexpr (OUT_DT == MXQ_F32) return reinterpret_cast<const float*>(bias)[col];
-    else if constexpr (OUT_DT == MXQ_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[col]);
-    else return __half2float(reinterpret_cast<const __half*>(bias)[col]);
-}
 
 // one chunk (W = 32 or 16 accumulator columns of this lane's row) -> staging slot -> TMA store at (col0, row0 + lane)
 template <int OUT_DT, int W>
-__device__ __forceinline__ void emit_chunk_tma(const uint32_t (&r)[32], const void* bias, int col0, int row0, int N, uint8_t* slot,
+__device__ __forceinline__ void emit_chunk_tma(const uint32_t (&r)[32], const BiasRef& bias, int col0, int row0, int N, uint8_t* slot,
                                                const OutMaps& maps, int lane) {
     float v[W];
 #pragma unroll
     for (int i = 0; i < W; ++i) v[i] = __uint_as_float(r[i]);
-    if (bias != nullptr) {
+    if (bias.ptr != nullptr) {
 #pragma unroll
         for (int i = 0; i < W; ++i) if (col0 + i < N) v[i] += bias_at<OUT_DT>(bias, col0 + i);
     }
@@ -269,7 +285,7 @@ __device__ __forceinline__ void emit_chunk_tma(const uint32_t (&r)[32], const vo
 // quadrant; `slots` = this warp's EPI_SLOT_BYTES of staging (1024-byte aligned); `turn` alternates the two slots.
 // Arrives on `release_bar` right after the last tensor-memory read.
 template <int OUT_DT>
-__device__ __forceinline__ void drain_accumulator_tma(uint32_t taddr, int n_chunks, bool tail16, int first, int step, const void* bias,
+__device__ __forceinline__ void drain_accumulator_tma(uint32_t taddr, int n_chunks, bool tail16, int first, int step, const BiasRef& bias,
                                                       int col_base, int row0, int M, int N, uint8_t* slots, uint32_t& turn, const OutMaps& maps,
                                                       uint32_t release_bar, int lane) {
     constexpr bool TWO_SLOTS = OUT_DT != MXQ_F32;

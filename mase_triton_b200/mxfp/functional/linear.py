@@ -41,7 +41,7 @@ def block_scaled_ok(x: Tensor, x_meta: MXFPMeta | None, w_tensor_meta: MXFPTenso
 
 
 def _fused_linear(x: Tensor, x_meta: MXFPMeta | None, w: Tensor | None, w_scales: Tensor | None, w_elements: Tensor | None,
-                  w_tensor_meta: MXFPTensorMeta | None, bias: Tensor | None, kind) -> Tensor:
+                  w_tensor_meta: MXFPTensorMeta | None, bias: Tensor | None, kind, bias_q=None) -> Tensor:
     """``backend="fused"``: every layer type runs a hand-written tensor-core GEMM of this library.
 
     * ``XqWq`` with 32-element blocks and is_finite elements: both operands stay quantised, block-scaled
@@ -60,7 +60,14 @@ def _fused_linear(x: Tensor, x_meta: MXFPMeta | None, w: Tensor | None, w_scales
     if kind.x_quantised and kind.w_quantised and block_scaled_ok(x, x_meta, w_tensor_meta):
         wq = _gemm.packed_weight(w_scales, w_elements, w_shape, w_tensor_meta.meta, rows=x.numel() // K,
                                  nibbles=_gemm.fp4_pair(x_meta, w_tensor_meta.meta, K))
+        if bias_q is not None and _gemm.bias_codes_ok(bias_q[0], bias_q[1], bias_q[2].meta, w_shape[0], getattr(torch, bias_q[2].dtype), x.dtype):
+            # the bias stays quantised too: its codes are decoded in the GEMM's epilogue
+            return _gemm.mx_linear(x, x_meta, wq, None, bias_q=(bias_q[0], bias_q[1], bias_q[2].meta))
+        if bias_q is not None:
+            bias = compose_mxfp_tensor(*bias_q)
         return _gemm.mx_linear(x, x_meta, wq, bias)
+    if bias_q is not None:
+        bias = compose_mxfp_tensor(*bias_q)
     reason = tc_linear.why_not(x, K)
     if reason is not None:
         raise NotImplementedError(f"backend='fused' is not implemented for this call: {reason}; use backend='separate'")
@@ -91,13 +98,16 @@ def mxfp_linear(
 ) -> Tensor:
     kind = parse_layer_type(layer_type)
     check_backend(backend)
+    if backend == "fused":
+        # the reference only uses bias codes when a plain bias is passed as well (then the codes win); the fused route
+        # hands them on as codes so that the block-scaled GEMM can decode them in its epilogue
+        bias_q = (b_scales, b_elements, b_tensor_meta) if (kind.b_quantised and b is not None) else None
+        return _fused_linear(x, x_meta, w, w_scales, w_elements, w_tensor_meta, None if kind.b_quantised else b, kind, bias_q)
     if kind.b_quantised:
         # the reference only dequantises bias codes when a plain bias is passed as well
         bias = compose_mxfp_tensor(b_scales, b_elements, b_tensor_meta) if b is not None else None
     else:
         bias = b
-    if backend == "fused":
-        return _fused_linear(x, x_meta, w, w_scales, w_elements, w_tensor_meta, bias, kind)
     if kind.x_quantised:
         x = quantize_dequantize(x, block_dim=-1, mxfp_meta=x_meta)       # same bits as extract + compose
     weight = compose_mxfp_tensor(w_scales, w_elements, w_tensor_meta) if kind.w_quantised else w

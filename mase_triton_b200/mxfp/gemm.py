@@ -274,15 +274,36 @@ def packed_weight(w_scales: Tensor, w_elements: Tensor, shape: tuple[int, int], 
     return cached[1]
 
 
+def bias_codes_ok(b_scales: Tensor | None, b_elements: Tensor | None, b_meta: MXFPMeta | None, n: int, bias_dtype, out_dtype) -> bool:
+    """Whether the GEMM's epilogue can decode this quantised bias itself: 32-element blocks, an is_finite element
+    format, ``n`` a multiple of 32, and a bias that dequantises to the output dtype (so the rounding is the compose
+    kernel's)."""
+    return (b_scales is not None and b_elements is not None and supported(b_meta) and n % 32 == 0 and b_elements.numel() == n
+            and bias_dtype == out_dtype)
+
+
 def mx_gemm(a: PackedOperand, b: PackedOperand, out_dtype: torch.dtype, bias: Tensor | None = None,
-            out: Tensor | None = None) -> Tensor:
-    """``a [M,K] @ b[N,K]^T (+ bias)`` on the tensor cores; returns ``[M, N]`` of ``out_dtype``."""
+            out: Tensor | None = None, bias_q: tuple[Tensor, Tensor, MXFPMeta] | None = None) -> Tensor:
+    """``a [M,K] @ b[N,K]^T (+ bias)`` on the tensor cores; returns ``[M, N]`` of ``out_dtype``.
+    ``bias_q = (scales, elements, meta)``: an MXFP-quantised bias decoded by the epilogue (instead of ``bias``)."""
     assert a.K == b.K and out_dtype in _lib.DTYPE_ID and a.operand == OPERAND_A and b.operand == OPERAND_B
     assert a.hw_format <= 1 or (a.hw_format == 5 and b.hw_format == 5), "a packed 4-bit left operand needs a packed 4-bit right one"
     dev = a.codes.device
     _raise_if_failed(dev)
     if out is None:
         out = torch.empty((a.rows, b.rows), dtype=out_dtype, device=dev)
+    if bias_q is not None:
+        assert bias is None, "pass the bias either dense or as codes"
+        q_scales, q_elements, q_meta = bias_q
+        q_scales, q_elements = q_scales.contiguous(), q_elements.contiguous()
+        assert q_elements.numel() == b.rows and q_scales.numel() == b.rows // 32 and supported(q_meta)
+        with torch.cuda.device(dev):
+            rc = _lib.load().mxq_mx_gemm_qbias(a.codes.data_ptr(), a.sf.data_ptr(), a.hw_format, b.codes.data_ptr(), b.sf.data_ptr(),
+                                               b.hw_format, b.tile_rows, out.data_ptr(), _lib.DTYPE_ID[out_dtype],
+                                               q_scales.data_ptr(), q_elements.data_ptr(), q_meta.element_exp_bits, q_meta.element_frac_bits,
+                                               a.rows, b.rows, a.K, status_word(dev).data_ptr(), _lib.stream_ptr(dev))
+        _lib.check(rc, "mxq_mx_gemm_qbias")
+        return out
     if bias is not None:
         bias = bias.to(out_dtype).contiguous()
         assert bias.numel() == b.rows
@@ -333,7 +354,8 @@ def _scratch(device: torch.device, nbytes: int) -> Tensor:
     return buf
 
 
-def mx_linear(x: Tensor, x_meta: MXFPMeta, w: PackedOperand, bias: Tensor | None = None, out: Tensor | None = None) -> Tensor:
+def mx_linear(x: Tensor, x_meta: MXFPMeta, w: PackedOperand, bias: Tensor | None = None, out: Tensor | None = None,
+              bias_q: tuple[Tensor, Tensor, MXFPMeta] | None = None) -> Tensor:
     """``quantise(x) @ w^T (+ bias)``.  Round-to-nearest activations go through the single C entry point
     ``mxq_mx_linear`` (quantisation, packing and the tensor-core GEMM enqueued back to back on the
     current stream); the other rounding modes are quantised by the extract kernel, which implements
@@ -345,6 +367,11 @@ def mx_linear(x: Tensor, x_meta: MXFPMeta, w: PackedOperand, bias: Tensor | None
         x = x.float()
     x2 = x.reshape(-1, w.K).contiguous()
     M, dev = x2.shape[0], x2.device
+    if bias_q is not None:
+        # a quantised bias: the activation is packed by its own kernel, the GEMM's epilogue decodes the bias codes
+        nib = w.hw_format == 5 and is_e2m1(x_meta) and w.K % 256 == 0
+        y = mx_gemm(pack_activation(x2, x_meta, nibbles=nib), w, x2.dtype, out=out, bias_q=bias_q)
+        return y.reshape(*x.shape[:-1], w.rows)
     if w.hw_format == 5 and is_e2m1(x_meta) and w.K % 256 == 0 and x_meta.round_mode != "rn":
         # MXFP4 x MXFP4 with the weight kept as packed nibbles: the activation is packed the same way (kind::mxf4);
         # round to nearest goes through the single C entry point below, which does the same

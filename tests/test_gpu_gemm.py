@@ -303,3 +303,32 @@ def test_one_pass_nibble_pack_equals_two_step(lib, dtype, rows, K):
         finite_rows = torch.isfinite(x.float()).reshape(rows, K // 32, 32).all(dim=2).repeat_interleave(16, dim=1)
         assert torch.equal(one.codes[finite_rows], two.codes[finite_rows]), "codes differ"
         assert torch.equal(one.sf, two.sf), "scale chunks differ"
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("b_meta", [MXFP8_E4M3_fn, OCP_MXFP6_E3M2, OCP_MXFP4_E2M1], ids=lambda m: m.tag)
+def test_quantised_bias_is_decoded_in_the_epilogue(lib, dtype, b_meta):
+    """Layer type XqWqBq called with a plain bias and bias codes (the case in which the reference uses the codes,
+    src/mase_triton/mxfp/functional/linear.py:52-57): the fused backend hands the codes to the GEMM, whose epilogue decodes
+    them; the result is the one obtained by dequantising the bias first, bit for bit."""
+    from mase_triton_b200.mxfp.functional.cast import extract_mxfp_components, compose_mxfp_tensor
+
+    torch.manual_seed(7)
+    M, N, K = 300, 992, 256
+    x = torch.randn(M, K, device=DEV).to(dtype)
+    w = (0.05 * torch.randn(N, K, device=DEV)).to(dtype)
+    bias = (3.0 * torch.randn(N, device=DEV)).to(dtype)
+    w_scales, w_elements, w_tm = extract_mxfp_components(w, -1, OCP_MXFP6_E3M2)
+    b_scales, b_elements, b_tm = extract_mxfp_components(bias, -1, b_meta)
+    y = MX.mxfp_linear(x, MXFP8_E4M3_fn, None, w_scales, w_elements, w_tm, bias, b_scales, b_elements, b_tm, "XqWqBq", "fused")
+    G.check_status(DEV)
+    bias_dq = compose_mxfp_tensor(b_scales, b_elements, b_tm)
+    want = MX.mxfp_linear(x, MXFP8_E4M3_fn, None, w_scales, w_elements, w_tm, bias_dq, None, None, None, "XqWqB", "fused")
+    G.check_status(DEV)
+    assert torch.equal(y, want)
+    sep = MX.mxfp_linear(x, MXFP8_E4M3_fn, None, w_scales, w_elements, w_tm, bias, b_scales, b_elements, b_tm, "XqWqBq", "separate")
+    assert within_tolerance(y, sep.float())
+    # the GEMM entry by itself
+    a = G.quantize_pack(x, MXFP8_E4M3_fn)
+    wq = G.pack_operand(w_scales, w_elements, N, K, OCP_MXFP6_E3M2, G.OPERAND_B)
+    assert torch.equal(G.mx_gemm(a, wq, dtype, bias_q=(b_scales, b_elements, b_meta)), G.mx_gemm(a, wq, dtype, bias=bias_dq))
