@@ -58,6 +58,7 @@ __device__ __forceinline__ void ew_tile(const char* __restrict__ src, char* __re
 template <class KIn, class KOut, int V, int U, bool PLAIN, class Op>
 __global__ void __launch_bounds__(kThreads) ew_vec_kernel(const void* __restrict__ in, void* __restrict__ out,
                                                           int64_t n_vec, Op op) {
+    grid_dependency_sync();
     const int64_t first = (int64_t)blockIdx.x * (kThreads * U) + threadIdx.x;
     const char* src = reinterpret_cast<const char*>(in) + first * (V * KIn::size);
     char* dst = reinterpret_cast<char*>(out) + first * (V * KOut::size);
@@ -108,7 +109,8 @@ static int launch_ew(const void* in, void* out, int64_t n, Op op, cudaStream_t s
     const int64_t n_vec = aligned ? n / V : 0;
     if (n_vec > 0) {
         const int64_t grid = (n_vec + kThreads * U - 1) / (kThreads * U);
-        ew_vec_kernel<KIn, KOut, V, U, PLAIN, Op><<<(unsigned)grid, kThreads, 0, st>>>(in, out, n_vec, op);
+        const cudaError_t e = launch_overlapped(ew_vec_kernel<KIn, KOut, V, U, PLAIN, Op>, (unsigned)grid, kThreads, st, in, out, n_vec, op);
+        if (e != cudaSuccess) { set_last_cuda_error(e); return MXQ_ELAUNCH; }
     }
     const int64_t first = n_vec * V;
     if (first < n) {
@@ -653,6 +655,7 @@ template <class KIn, class F, int U, int MODE>
 __global__ void __launch_bounds__(kThreads) mxfp_b32_quant_kernel(const void* __restrict__ x, uint8_t* __restrict__ scales,
                                                                   uint8_t* __restrict__ elements, void* __restrict__ out,
                                                                   int64_t n_vec, F f) {
+    grid_dependency_sync();
     constexpr int V = 16 / KIn::size;
     const int64_t first = (int64_t)blockIdx.x * (kThreads * U) + threadIdx.x;
     const char* src = reinterpret_cast<const char*>(x) + first * 16;
@@ -671,6 +674,7 @@ template <class KOut, class F, int U>
 __global__ void __launch_bounds__(kThreads) mxfp_b32_compose_kernel(const uint8_t* __restrict__ scales,
                                                                     const uint8_t* __restrict__ elements,
                                                                     void* __restrict__ out, int64_t n_vec, F f) {
+    grid_dependency_sync();
     constexpr int V = 16 / KOut::size;    // 4 or 8 elements per lane per access
     constexpr int G = 32 / V;
     const int64_t tile = (int64_t)blockIdx.x * (kThreads * U) + threadIdx.x;
@@ -812,9 +816,10 @@ static int mxfp_quant_dispatch(const void* x, int x_dtype, uint8_t* scales, uint
                     constexpr int U = 4;
                     const int64_t n_vec = n / V;
                     const int64_t grid = (n_vec + kThreads * U - 1) / (kThreads * U);
-                    mxfp_b32_quant_kernel<KIn, decltype(f), U, WRITE_CODES ? MODE_CODES : MODE_QDQ><<<(unsigned)grid, kThreads, 0, st>>>(
-                        x, scales, elements, out, n_vec, f);
-                    rc = check_launch();
+                    const cudaError_t e = launch_overlapped(mxfp_b32_quant_kernel<KIn, decltype(f), U, WRITE_CODES ? MODE_CODES : MODE_QDQ>,
+                                                            (unsigned)grid, kThreads, st, x, scales, elements, out, n_vec, f);
+                    if (e != cudaSuccess) set_last_cuda_error(e);
+                    rc = e == cudaSuccess ? check_launch() : MXQ_ELAUNCH;
                 });
             };
             if constexpr (WRITE_CODES) go(KF32{});
@@ -874,7 +879,9 @@ extern "C" int mxq_mxfp_compose(const uint8_t* scales, const uint8_t* elements, 
                 constexpr int U = 4;
                 const int64_t n_vec = n / V;
                 const int64_t grid = (n_vec + kThreads * U - 1) / (kThreads * U);
-                mxfp_b32_compose_kernel<KOut, decltype(f), U><<<(unsigned)grid, kThreads, 0, st>>>(scales, elements, out, n_vec, f);
+                const cudaError_t e = launch_overlapped(mxfp_b32_compose_kernel<KOut, decltype(f), U>, (unsigned)grid, kThreads, st, scales, elements,
+                                                        out, n_vec, f);
+                if (e != cudaSuccess) set_last_cuda_error(e);
                 rc = check_launch();
             });
         }
